@@ -1,0 +1,184 @@
+"""Common machinery of the distributed optimizers.
+
+Construction mirrors ``dl_code/pcode/create_optimizer.py:13-52``: one param-group per
+parameter tensor carrying ``name``, ``weight_decay`` (0 when the name contains ``"bn"``),
+``param_size`` and ``nelement``; ``lr`` / ``momentum`` / ``nesterov`` from the config.
+``step(timer=..., scheduler=...)`` returns the number of bits transmitted, as in the
+reference (e.g. ``dl_code/pcode/optim/sgd.py:67-122``).
+
+Unlike the reference, all algorithm state (x_hat, s, replicas, error memories, step
+counters) is part of ``state_dict()`` so a resumed run continues the same trajectory.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Dict, Optional
+
+import torch
+from torch.optim.optimizer import Optimizer
+
+from ..compress.reference import make_codec
+from ..parallel.comm import CentralizedAggregation, DecentralizedAggregation
+from .arena import FlatArena
+
+
+class _NullTimer:
+    @contextlib.contextmanager
+    def __call__(self, *a, **k):
+        yield
+
+
+def build_param_groups(model, weight_decay: float):
+    groups = []
+    for name, p in model.named_parameters():
+        if not p.requires_grad:
+            continue
+        groups.append(
+            {
+                "params": [p],
+                "name": name,
+                "weight_decay": weight_decay if "bn" not in name else 0.0,
+                "param_size": p.size(),
+                "nelement": p.nelement(),
+            }
+        )
+    return groups
+
+
+class DistributedOptimizer(Optimizer):
+    #: labels of the timer scopes this algorithm emits (observability contract).
+    timer_labels = ()
+
+    def __init__(self, model, conf, graph, group=None):
+        groups = build_param_groups(model, conf.weight_decay)
+        defaults = dict(
+            lr=conf.lr,
+            momentum=conf.momentum_factor,
+            dampening=0,
+            weight_decay=conf.weight_decay,
+            nesterov=conf.use_nesterov,
+        )
+        if conf.use_nesterov and conf.momentum_factor <= 0:
+            raise ValueError("Nesterov momentum requires a momentum and zero dampening")
+        super().__init__(groups, defaults)
+        self.conf = conf
+        self.graph = graph
+        self.rank = graph.rank
+        self.n_nodes = graph.n_nodes
+        self.neighbors_info: Dict[int, float] = graph.get_neighborhood()
+        self.param_names = list(enumerate(g["name"] for g in self.param_groups))
+        self.arena = FlatArena([(g["name"], g["params"][0]) for g in self.param_groups])
+        self.seg = self.arena.seg
+        self.device = self.arena.device
+        self.wd_vec = self.arena.per_element([g["weight_decay"] for g in self.param_groups])
+        self.momentum_buf: Optional[torch.Tensor] = None  # flat, created on first use
+        self.local_index = 0  # number of completed step() calls
+        self.n_bits = 0
+        self.world_aggregator = CentralizedAggregation(
+            self.rank, graph.ranks, {r: 1.0 / graph.n_nodes for r in graph.ranks}, group
+        )
+        self.decentralized_aggregator = DecentralizedAggregation(self.rank, self.neighbors_info, group)
+        self._epoch_override = None
+
+    # ---- hyper-parameters ------------------------------------------------------------
+    @property
+    def lr(self) -> float:
+        return float(self.param_groups[0]["lr"])
+
+    @property
+    def momentum(self) -> float:
+        return float(self.param_groups[0]["momentum"])
+
+    @property
+    def nesterov(self) -> bool:
+        return bool(self.param_groups[0]["nesterov"])
+
+    def make_codec(self, compress_ratio=None):
+        c = self.conf
+        return make_codec(
+            self.seg,
+            c.comm_op,
+            c.compress_ratio if compress_ratio is None else compress_ratio,
+            c.quantize_level,
+            getattr(c, "qsgd_levels", None),
+            c.is_biased,
+            getattr(c, "random_k_seed", 1234),
+        )
+
+    def epoch_of(self, kargs) -> float:
+        sch = kargs.get("scheduler")
+        if sch is not None and hasattr(sch, "epoch_"):
+            return float(sch.epoch_)
+        return float(kargs.get("epoch", 0.0))
+
+    @staticmethod
+    def timer_of(kargs):
+        t = kargs.get("timer")
+        return t if t is not None else _NullTimer()
+
+    # ---- local momentum-SGD direction ---------------------------------------------------
+    def local_direction(self) -> torch.Tensor:
+        """d' of ``apply_gradient`` on the flat buffers (``dl_code/pcode/optim/utils.py:13-47``):
+        d = g + wd x; buf = d on the first call, mu buf + d later; d' = d + mu buf | buf.
+        Consumes (zeroes) the gradient buffer."""
+        a = self.arena
+        d = torch.addcmul(a.g, self.wd_vec, a.x)
+        mu = self.momentum
+        if mu != 0:
+            if self.momentum_buf is None:
+                self.momentum_buf = d.clone()
+            else:
+                self.momentum_buf.mul_(mu).add_(d)
+            d = d.add(self.momentum_buf, alpha=mu) if self.nesterov else self.momentum_buf.clone()
+        a.g.zero_()
+        return d
+
+    def zero_grad(self, set_to_none: bool = False):
+        # gradients alias the arena; they are cleared when consumed by step().
+        self.arena.g.zero_()
+
+    # ---- checkpointing ---------------------------------------------------------------
+    def algo_state(self) -> dict:
+        return {}
+
+    def load_algo_state(self, state: dict):
+        pass
+
+    def state_dict(self):
+        groups = []
+        for i, g in enumerate(self.param_groups):
+            gg = {k: v for k, v in g.items() if k != "params"}
+            gg["params"] = [i]
+            gg["param_size"] = tuple(g["param_size"])
+            groups.append(gg)
+        state = {}
+        if self.momentum_buf is not None:
+            for i, sl in enumerate(self.seg.slices()):
+                state[i] = {
+                    "momentum_buffer": self.momentum_buf[sl].detach().clone().view(self.param_groups[i]["param_size"])
+                }
+        algo = {k: (v.detach().clone() if torch.is_tensor(v) else v) for k, v in self.algo_state().items()}
+        algo["local_index"] = self.local_index
+        return {"state": state, "param_groups": groups, "algo_state": algo}
+
+    def load_state_dict(self, sd):
+        for g, lg in zip(self.param_groups, sd["param_groups"]):
+            for k in ("lr", "momentum", "dampening", "weight_decay", "nesterov"):
+                if k in lg:
+                    g[k] = lg[k]
+        self.wd_vec = self.arena.per_element([g["weight_decay"] for g in self.param_groups])
+        st = sd.get("state", {})
+        if st:
+            self.momentum_buf = torch.zeros_like(self.arena.x)
+            for i, sl in enumerate(self.seg.slices()):
+                ent = st.get(i, st.get(str(i)))
+                if ent is not None and "momentum_buffer" in ent:
+                    self.momentum_buf[sl].copy_(ent["momentum_buffer"].reshape(-1))
+        algo = dict(sd.get("algo_state", {}))
+        self.local_index = int(algo.pop("local_index", 0))
+        self.load_algo_state(algo)
+        self.arena.rebind()
+
+    def finalize(self):
+        """Complete any communication still in flight (end of training / before a checkpoint)."""
+        return None

@@ -1,0 +1,132 @@
+"""CHOCO-SGD (memory-efficient form), the algorithm this framework is built around.
+
+State per rank: ``x_hat`` (own public copy) and ``s = sum_j w_ij x_hat_j``, both zero at
+start.  One step (``dl_code/pcode/optim/parallel_choco_v.py:104-155``)::
+
+    x   <- x - lr d'                           local momentum-SGD step
+    (the exchange of the previous step must have been applied to x_hat, s)
+    x   <- x + gamma (s - x_hat)               consensus
+    q_i  = Q(x - x_hat)                        per-tensor compression
+    exchange q with the graph neighbours
+    x_hat <- x_hat + q_i ;  s <- s + sum_j w_ij q_j     (j runs over neighbours and self)
+
+``step()`` returns the bits of the *previous* exchange (``:113,155``).
+
+Two execution paths share this class:
+
+* ``impl="torch"`` - flat PyTorch ops + ``torch.distributed`` send/recv.  Runs on CPU/Gloo,
+  is the ``--gossip_impl nccl`` baseline on GPUs, and the readable statement of the math.
+* ``impl="fused"`` - the hand-written sm_100a kernels (``ops/gossip.py``): SGD, consensus,
+  compression and the NVLink push to the neighbours' mailboxes happen inside the kernels;
+  no ``torch.distributed`` call and no separate elementwise kernel is on that path.
+
+Both the reference's ``parallel_choco`` (gossip in a helper *process*) and
+``parallel_choco_v`` (helper *thread*) select this class: the overlap they implement on
+the host is expressed here with CUDA streams / deferred completion instead.
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import DistributedOptimizer
+
+
+class ChocoSGD(DistributedOptimizer):
+    timer_labels = (
+        "sync.apply_grad",
+        "sync.finish_sync",
+        "sync.recover_hat_params",
+        "sync.update_flatten_params",
+        "sync.update_local_model",
+        "sync.start_sync",
+    )
+
+    def __init__(self, model, conf, graph, group=None, impl="auto", engine=None):
+        super().__init__(model, conf, graph, group)
+        self.consensus_stepsize = float(conf.consensus_stepsize)
+        self.codec = self.make_codec()
+        self.x_hat = torch.zeros_like(self.arena.x)
+        self.s = torch.zeros_like(self.arena.x)
+        self.gossip_step = 0  # index of the next exchange
+        self._pending = None  # (pending exchange, step index, own payload)
+        self._pending_bits = 0
+        self.overlap = bool(getattr(conf, "overlap_gossip", True))
+        want = getattr(conf, "gossip_impl", "auto") if impl == "auto" else impl
+        if want == "auto":
+            want = "fused" if (self.device.type == "cuda" and engine is not False) else "torch"
+        if want == "nccl":
+            want = "torch"
+        self.impl = want
+        self.engine = None
+        if self.impl == "fused":
+            if engine is None or engine is False:
+                from ..ops.gossip import ChocoEngine
+
+                engine = ChocoEngine.for_optimizer(self, group)
+            self.engine = engine
+
+    # ---- torch path ----------------------------------------------------------------------
+    def _finish_sync(self):
+        if self._pending is None:
+            return
+        pending, step = self._pending
+        received = pending.wait()
+        for rank, weight in self.neighbors_info.items():
+            payload = received[rank]
+            if self.codec.is_sparse:
+                pos, val = self.codec.sparse(payload, step, rank)
+                if rank == self.rank:
+                    self.x_hat.index_add_(0, pos, val)
+                self.s.index_add_(0, pos, val, alpha=weight)
+            else:
+                q = self.codec.decompress(payload, step, rank)
+                if rank == self.rank:
+                    self.x_hat.add_(q)
+                self.s.add_(q, alpha=weight)
+        self._pending = None
+        self.n_bits = self._pending_bits
+
+    def _step_torch(self, timer, ep):
+        a = self.arena
+        with timer("sync.apply_grad", epoch=ep):
+            a.x.add_(self.local_direction(), alpha=-self.lr)
+        with timer("sync.finish_sync", epoch=ep):
+            self._finish_sync()
+        with timer("sync.update_flatten_params", epoch=ep):
+            a.x.add_(self.s - self.x_hat, alpha=self.consensus_stepsize)
+        with timer("sync.start_sync", epoch=ep):
+            payload = self.codec.compress(a.x - self.x_hat, self.gossip_step, self.rank)
+            self._pending = (self.decentralized_aggregator.start(payload), self.gossip_step)
+            self._pending_bits = self.codec.n_bits()
+            self.gossip_step += 1
+            if not self.overlap:
+                self._finish_sync()
+        return self.n_bits
+
+    # ---- public ------------------------------------------------------------------------------
+    def step(self, closure=None, **kargs):
+        timer, ep = self.timer_of(kargs), self.epoch_of(kargs)
+        self.local_index += 1
+        if self.impl == "fused":
+            with timer("sync.gossip_fused", epoch=ep):
+                bits = self.engine.step(self)
+            return bits
+        return self._step_torch(timer, ep)
+
+    def finalize(self):
+        if self.impl == "fused":
+            self.engine.flush(self)
+        else:
+            self._finish_sync()
+
+    def algo_state(self):
+        self.finalize()
+        return {"x_hat": self.x_hat, "s": self.s, "gossip_step": self.gossip_step}
+
+    def load_algo_state(self, st):
+        if "x_hat" in st:
+            self.x_hat.copy_(st["x_hat"])
+            self.s.copy_(st["s"])
+            self.gossip_step = int(st.get("gossip_step", 0))
+            if self.engine is not None:
+                self.engine.reset_step(self.gossip_step)

@@ -1,0 +1,40 @@
+"""Centralized (all-reduce) SGD and decentralized D-PSGD.
+
+``complete`` topology: gradients are averaged over all ranks, then one local
+momentum-SGD step (``dl_code/pcode/optim/sgd.py:68-92``).  Any other topology: local step
+first, then full-precision gossip averaging ``x_i <- sum_j w_ij x_j`` with the graph
+neighbours (``:93-121``)."""
+from __future__ import annotations
+
+import torch
+
+from .base import DistributedOptimizer
+
+
+class SGD(DistributedOptimizer):
+    timer_labels = ("sync.get_data", "sync.sync", "sync.unflatten_grad", "sync.apply_grad", "sync.update_model")
+
+    def __init__(self, model, conf, graph, group=None, is_centralized=None):
+        super().__init__(model, conf, graph, group)
+        self.is_centralized = (conf.graph_topology == "complete") if is_centralized is None else is_centralized
+
+    def step(self, closure=None, **kargs):
+        timer, a = self.timer_of(kargs), self.arena
+        ep = self.epoch_of(kargs)
+        self.local_index += 1
+        if self.is_centralized:
+            with timer("sync.sync", epoch=ep):
+                if self.n_nodes > 1:
+                    a.g.copy_(self.world_aggregator._agg(a.g, op="avg"))
+            with timer("sync.apply_grad", epoch=ep):
+                a.x.add_(self.local_direction(), alpha=-self.lr)
+        else:
+            with timer("sync.apply_grad", epoch=ep):
+                a.x.add_(self.local_direction(), alpha=-self.lr)
+            with timer("sync.sync", epoch=ep):
+                if self.n_nodes > 1:
+                    mixed = self.decentralized_aggregator._agg(a.x, op="weighted")
+                    with timer("sync.update_model", epoch=ep):
+                        a.x.copy_(mixed)
+        self.n_bits = 32 * self.seg.n_elements
+        return self.n_bits
