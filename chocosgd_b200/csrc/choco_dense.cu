@@ -1,0 +1,326 @@
+// CHOCO-SGD step with QSGD stochastic quantization: two kernels per training step.
+//
+//   choco_dense_prep   (decode of step t-1, fused as in the sign kernel)  ->  local SGD step
+//                      -> consensus -> d = x - x_hat into the scratch buffer; per-chunk sum of
+//                      squares; the last CTA of a segment publishes ||d_seg||_2 (own outbox
+//                      + neighbours' mailboxes, NVLink stores)
+//   choco_qsgd_pack    level = floor(s |d| / norm) + [u < frac], u from a counter hash of
+//                      (seed, step, position); levels and signs are bit-sliced with warp
+//                      ballots: every group of 32 positions becomes nbits + 1 words, stored to
+//                      the outbox and pushed into each neighbour's mailbox; the last CTA raises
+//                      the flags and advances the step counter
+//
+// Quantizer: dl_code/pcode/utils/sparsification.py:87-98 (which ships the de-quantized fp32
+// tensor; here (nbits + 1) bits per element travel).  A zero tensor quantizes to zeros.
+#include "common.cuh"
+
+#define MODE_DECODE 1
+
+__device__ __forceinline__ float qsgd_scale_of(int n, int s, int biased) {
+  if (!biased) return 1.f;
+  const float a = (float)n / ((float)s * (float)s), b = sqrtf((float)n) / (float)s;
+  return 1.f / (fminf(a, b) + 1.f);
+}
+
+// value of element `bit` of a 32-position group given its plane words
+__device__ __forceinline__ float qsgd_value(const uint32_t* planes, int nbits, int bit, float unit) {
+  uint32_t lv = 0;
+  for (int b = 0; b < nbits; ++b) lv |= ((planes[b] >> bit) & 1u) << b;
+  const float mag = unit * (float)lv;
+  return ((planes[nbits] >> bit) & 1u) ? -mag : mag;
+}
+
+// codec: 0 = qsgd (fused decode + L2 norm), 1 = top-k (first radix histogram), 2 = random-k
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_dense_prep_kernel(const ChocoParams* __restrict__ params,
+                                                                       int mode, int codec) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const int chunk = blockIdx.x;
+  __shared__ float red[32];
+  __shared__ int sh_flag;
+  __shared__ uint32_t sh_hist[2048];
+
+  const int seg = tb.chunk_seg[chunk];
+  const int start = tb.chunk_start[chunk];
+  const int valid = tb.chunk_valid[chunk];
+  const int span = (valid + 31) & ~31;
+  const int seg_n = tb.seg_size[seg];
+  const uint32_t t = p.step[0];
+  const int PW = p.payload_words, body = p.body_off;
+  const int n_peers = p.n_peers;
+  const int nbits = p.qsgd_nbits, pl = nbits + 1;
+
+  const bool do_decode = codec == 0 && (mode & MODE_DECODE) && t > 0 && p.step[2] < t;
+  if (codec != 0 && t > 0 && p.step[2] < t && threadIdx.x == 0 && chunk == 0)
+    report(p.status, CHOCO_BAD_STEP, -1, (int)t);
+  if (do_decode) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      for (int k = 0; k < n_peers; ++k)
+        if (!wait_flag_ge(p.my_flag[k], t, p.wait_budget_ns)) {
+          report(p.status, CHOCO_TIMEOUT, p.peer_rank[k], (int)t - 1);
+          ok = 0;
+          break;
+        }
+      sh_flag = ok;
+    }
+    __syncthreads();
+    if (!sh_flag) return;
+  }
+  if (codec == 1) {
+    for (int i = threadIdx.x; i < 2048; i += CHOCO_THREADS) sh_hist[i] = 0;
+    __syncthreads();
+  }
+
+  const int par_prev = (t - 1) & 1, par_cur = t & 1;
+  float unit_own = 0.f, unit_peer[CHOCO_MAX_PEERS];
+  if (do_decode) {
+    const float sc = qsgd_scale_of(seg_n, p.qsgd_s, p.qsgd_biased);
+    unit_own = (sc * __uint_as_float(__ldcg(p.outbox + par_prev * PW + seg))) / (float)p.qsgd_s;
+    for (int k = 0; k < n_peers; ++k)
+      unit_peer[k] =
+          p.w_peer[k] * ((sc * __uint_as_float(__ldcg(p.my_inbox[k] + par_prev * PW + seg))) / (float)p.qsgd_s);
+  }
+
+  const float lr = p.hyper[HYP_LR], mu = p.hyper[HYP_MOMENTUM], gamma = p.hyper[HYP_GAMMA];
+  const bool nesterov = p.hyper[HYP_NESTEROV] != 0.f;
+  const float gscale = p.hyper[HYP_GSCALE];
+  const bool mom_init = p.step[1] != 0;
+  const float wd = tb.seg_wd[seg];
+
+  float sq = 0.f;
+  for (int base = threadIdx.x * 4; base < span; base += CHOCO_THREADS * 4) {
+    const int pos = start + base;
+    const int group = pos >> 5, bit0 = pos & 31;
+    const float4 xh = *reinterpret_cast<const float4*>(p.x_hat + pos);
+    const float4 sv = *reinterpret_cast<const float4*>(p.s + pos);
+    float xh_a[4] = {xh.x, xh.y, xh.z, xh.w}, s_a[4] = {sv.x, sv.y, sv.z, sv.w};
+    if (do_decode) {
+      uint32_t planes[33];
+      const uint32_t* src = p.outbox + par_prev * PW + body + group * pl;
+      for (int b = 0; b < pl; ++b) planes[b] = __ldcg(src + b);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (base + e < valid) {
+          const float q = qsgd_value(planes, nbits, bit0 + e, unit_own);
+          xh_a[e] += q;
+          s_a[e] += p.w_self * q;
+        }
+      for (int k = 0; k < n_peers; ++k) {
+        const uint32_t* ps = p.my_inbox[k] + par_prev * PW + body + group * pl;
+        for (int b = 0; b < pl; ++b) planes[b] = __ldcg(ps + b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (base + e < valid) s_a[e] += qsgd_value(planes, nbits, bit0 + e, unit_peer[k]);
+      }
+      *reinterpret_cast<float4*>(p.x_hat + pos) = make_float4(xh_a[0], xh_a[1], xh_a[2], xh_a[3]);
+      *reinterpret_cast<float4*>(p.s + pos) = make_float4(s_a[0], s_a[1], s_a[2], s_a[3]);
+    }
+    const float4 xv = *reinterpret_cast<const float4*>(p.x + pos);
+    const float4 gv = load_grad4(p, seg, pos, base, valid);
+    float x_a[4] = {xv.x, xv.y, xv.z, xv.w}, g_a[4] = {gv.x, gv.y, gv.z, gv.w};
+    float m_a[4] = {0.f, 0.f, 0.f, 0.f}, d_a[4] = {0.f, 0.f, 0.f, 0.f};
+    if (mu != 0.f && mom_init) {
+      const float4 mv = *reinterpret_cast<const float4*>(p.m + pos);
+      m_a[0] = mv.x; m_a[1] = mv.y; m_a[2] = mv.z; m_a[3] = mv.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (base + e < valid) {
+        const float d = sgd_direction(x_a[e], g_a[e] * gscale, m_a[e], wd, mu, nesterov, mom_init);
+        float xn = fmaf(-lr, d, x_a[e]);
+        xn = fmaf(gamma, s_a[e] - xh_a[e], xn);
+        x_a[e] = xn;
+        const float diff = xn - xh_a[e];
+        d_a[e] = diff;
+        sq = fmaf(diff, diff, sq);
+        if (codec == 1) atomicAdd(&sh_hist[(__float_as_uint(diff) & 0x7FFFFFFFu) >> 20], 1u);
+      }
+    *reinterpret_cast<float4*>(p.x + pos) = make_float4(x_a[0], x_a[1], x_a[2], x_a[3]);
+    if (mu != 0.f) *reinterpret_cast<float4*>(p.m + pos) = make_float4(m_a[0], m_a[1], m_a[2], m_a[3]);
+    clear_grad4(p, pos);
+    *reinterpret_cast<float4*>(p.scratch_d + pos) = make_float4(d_a[0], d_a[1], d_a[2], d_a[3]);
+  }
+
+  if (codec == 1) {
+    __syncthreads();
+    uint32_t* gh = p.hist + (size_t)seg * CHOCO_HIST_WORDS;
+    for (int i = threadIdx.x; i < 2048; i += CHOCO_THREADS)
+      if (sh_hist[i]) atomicAdd(gh + i, sh_hist[i]);
+  }
+  if (codec == 0) {
+    const float tot = block_sum(sq, red);
+    if (threadIdx.x == 0) {
+      p.partial[chunk] = tot;
+      __threadfence();
+      sh_flag = (atomicAdd(p.seg_count + seg, 1u) == (uint32_t)tb.seg_n_chunks[seg] - 1);
+      if (sh_flag) __threadfence();
+    }
+    __syncthreads();
+    if (sh_flag) {
+      const int c0 = tb.seg_first_chunk[seg], nc = tb.seg_n_chunks[seg];
+      float acc = 0.f;
+      for (int c = threadIdx.x; c < nc; c += CHOCO_THREADS) acc += __ldcg(p.partial + c0 + c);
+      const float norm = sqrtf(block_sum(acc, red));
+      if (threadIdx.x == 0) {
+        const uint32_t nb = __float_as_uint(norm);
+        p.outbox[par_cur * PW + seg] = nb;
+        for (int k = 0; k < n_peers; ++k) p.peer_inbox[k][par_cur * PW + seg] = nb;
+        p.seg_count[seg] = 0;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.done_count + 1, 1u) == (uint32_t)tb.n_chunks - 1) {
+      p.done_count[1] = 0;
+      if (do_decode) p.step[2] = t;
+      p.step[1] = 1;
+    }
+  }
+}
+
+extern "C" int choco_dense_prep(const void* params_dev, int n_chunks, int n_ranks, int mode, int codec,
+                                cudaStream_t stream) {
+  dim3 grid(n_chunks, n_ranks);
+  choco_dense_prep_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev),
+                                                             mode, codec);
+  return (int)cudaGetLastError();
+}
+
+// ---- QSGD quantize + bit-slice + push ------------------------------------------------------
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_kernel(const ChocoParams* __restrict__ params) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const int chunk = blockIdx.x;
+  const int seg = tb.chunk_seg[chunk];
+  const int start = tb.chunk_start[chunk];
+  const int valid = tb.chunk_valid[chunk];
+  const int span = (valid + 31) & ~31;
+  const uint32_t t = p.step[0];
+  const int PW = p.payload_words, body = p.body_off;
+  const int par_cur = t & 1;
+  const int nbits = p.qsgd_nbits, pl = nbits + 1;
+  const int lane = threadIdx.x & 31;
+  const float norm = __uint_as_float(__ldcg(p.outbox + par_cur * PW + seg));
+  const float s_f = (float)p.qsgd_s;
+  const uint32_t ubase = uniform_base(p.seed, t);
+
+  // one warp per group of 32 positions (lane = position inside the group)
+  for (int base = (threadIdx.x >> 5) * 32; base < span; base += CHOCO_THREADS) {
+    const int pos = start + base + lane;
+    const bool ok = base + lane < valid;
+    const float d = ok ? p.scratch_d[pos] : 0.f;
+    uint32_t lv = 0;
+    if (ok && norm > 0.f) {
+      const float lvl = (s_f * fabsf(d)) / norm;
+      const float fl = floorf(lvl);
+      const float u = counter_uniform(ubase, (uint32_t)pos);
+      lv = (uint32_t)fl + ((u < (lvl - fl)) ? 1u : 0u);
+    }
+    uint32_t mine = 0;
+    for (int b = 0; b < nbits; ++b) {
+      const uint32_t w = __ballot_sync(0xffffffffu, (lv >> b) & 1u);
+      if (lane == b) mine = w;
+    }
+    const uint32_t sgn = __ballot_sync(0xffffffffu, ok && d < 0.f);
+    if (lane == nbits) mine = sgn;
+    if (lane < pl) {
+      const int off = par_cur * PW + body + ((start + base) >> 5) * pl + lane;
+      p.outbox[off] = mine;
+      for (int k = 0; k < p.n_peers; ++k) p.peer_inbox[k][off] = mine;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(p.done_count, 1u) == (uint32_t)tb.n_chunks - 1) {
+      __threadfence_system();
+      p.done_count[0] = 0;
+      for (int k = 0; k < p.n_peers; ++k) st_release_sys(p.peer_flag[k], t + 1);
+      __threadfence();
+      p.step[0] = t + 1;
+    }
+  }
+}
+
+extern "C" int choco_qsgd_pack(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
+  dim3 grid(n_chunks, n_ranks);
+  choco_qsgd_pack_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  return (int)cudaGetLastError();
+}
+
+// decode-only (flush after the last training step): x_hat, s += payloads of step t-1
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_decode_kernel(const ChocoParams* __restrict__ params) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const int chunk = blockIdx.x;
+  __shared__ int sh_flag;
+  const int seg = tb.chunk_seg[chunk];
+  const int start = tb.chunk_start[chunk];
+  const int valid = tb.chunk_valid[chunk];
+  const int span = (valid + 31) & ~31;
+  const uint32_t t = p.step[0];
+  const bool do_decode = t > 0 && p.step[2] < t;
+  const int PW = p.payload_words, body = p.body_off, n_peers = p.n_peers;
+  const int nbits = p.qsgd_nbits, pl = nbits + 1;
+  if (do_decode) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      for (int k = 0; k < n_peers; ++k)
+        if (!wait_flag_ge(p.my_flag[k], t, p.wait_budget_ns)) {
+          report(p.status, CHOCO_TIMEOUT, p.peer_rank[k], (int)t - 1);
+          ok = 0;
+          break;
+        }
+      sh_flag = ok;
+    }
+    __syncthreads();
+    if (!sh_flag) return;
+    const int par_prev = (t - 1) & 1;
+    const float sc = qsgd_scale_of(tb.seg_size[seg], p.qsgd_s, p.qsgd_biased);
+    const float unit_own = (sc * __uint_as_float(__ldcg(p.outbox + par_prev * PW + seg))) / (float)p.qsgd_s;
+    for (int base = threadIdx.x * 4; base < span; base += CHOCO_THREADS * 4) {
+      const int pos = start + base, group = pos >> 5, bit0 = pos & 31;
+      const float4 xh = *reinterpret_cast<const float4*>(p.x_hat + pos);
+      const float4 sv = *reinterpret_cast<const float4*>(p.s + pos);
+      float xh_a[4] = {xh.x, xh.y, xh.z, xh.w}, s_a[4] = {sv.x, sv.y, sv.z, sv.w};
+      uint32_t planes[33];
+      const uint32_t* src = p.outbox + par_prev * PW + body + group * pl;
+      for (int b = 0; b < pl; ++b) planes[b] = __ldcg(src + b);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (base + e < valid) {
+          const float q = qsgd_value(planes, nbits, bit0 + e, unit_own);
+          xh_a[e] += q;
+          s_a[e] += p.w_self * q;
+        }
+      for (int k = 0; k < n_peers; ++k) {
+        const float unit =
+            p.w_peer[k] * ((sc * __uint_as_float(__ldcg(p.my_inbox[k] + par_prev * PW + seg))) / (float)p.qsgd_s);
+        const uint32_t* ps = p.my_inbox[k] + par_prev * PW + body + group * pl;
+        for (int b = 0; b < pl; ++b) planes[b] = __ldcg(ps + b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (base + e < valid) s_a[e] += qsgd_value(planes, nbits, bit0 + e, unit);
+      }
+      *reinterpret_cast<float4*>(p.x_hat + pos) = make_float4(xh_a[0], xh_a[1], xh_a[2], xh_a[3]);
+      *reinterpret_cast<float4*>(p.s + pos) = make_float4(s_a[0], s_a[1], s_a[2], s_a[3]);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.done_count + 1, 1u) == (uint32_t)tb.n_chunks - 1) {
+      p.done_count[1] = 0;
+      if (do_decode) p.step[2] = t;
+    }
+  }
+}
+
+extern "C" int choco_qsgd_decode(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
+  dim3 grid(n_chunks, n_ranks);
+  choco_qsgd_decode_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  return (int)cudaGetLastError();
+}

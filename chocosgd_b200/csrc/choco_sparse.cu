@@ -1,0 +1,384 @@
+// CHOCO-SGD with sparsifying compressors (top-k, random-k): selection, compaction and push.
+//
+// top-k (per parameter tensor, exact k, ties to the lowest index, output ordered by index):
+//   the keys are the bit patterns of |d| (monotone as unsigned integers); a 3-digit radix
+//   select (11 + 11 + 9 bits) narrows the k-th largest key:
+//     choco_dense_prep(codec=1)  histogram of digit 1 while d is produced
+//     choco_topk_hist(pass=2|3)  histogram of the next digit among keys matching the prefix
+//     choco_topk_count           threshold key known -> per-chunk (#greater, #equal)
+//     choco_topk_emit            ordered compaction of (index, value) pairs into the own
+//                                outbox AND the neighbours' mailboxes (NVLink stores); last CTA
+//                                raises the flags
+//   replaces per-tensor torch.topk + gather + cat (dl_code/pcode/utils/sparsification.py:18-31,
+//   dl_code/pcode/optim/parallel_choco_v.py:229-269).
+// random-k: the k indices of a tensor are the first k images of a keyed Feistel permutation
+//   of [0, n), a function of (seed, step, tensor): only values travel.
+// decode: one launch per source payload (indices inside one payload are distinct, so no
+//   atomics are needed and the result is bitwise reproducible).
+#include "common.cuh"
+
+__device__ __forceinline__ uint32_t key_of(float d) { return __float_as_uint(d) & 0x7FFFFFFFu; }
+
+// Among `nbins` counts (global memory), find the bin B with  #(bins > B) < k <= #(bins >= B).
+// Returns B and k_rem = k - #(bins > B) to every thread.  nbins is 2048 or 512.
+__device__ void find_bucket(const uint32_t* __restrict__ hist, int nbins, uint32_t k, uint32_t* sh /*[256+2]*/,
+                            uint32_t& bucket, uint32_t& k_rem) {
+  const int per = nbins / CHOCO_THREADS;  // 8 or 2
+  uint32_t local[8];
+  uint32_t sum = 0;
+  for (int j = 0; j < per; ++j) {
+    local[j] = __ldcg(hist + threadIdx.x * per + j);
+    sum += local[j];
+  }
+  __syncthreads();
+  sh[threadIdx.x] = sum;
+  __syncthreads();
+  // inclusive suffix sums over the 256 thread sums (Hillis-Steele)
+  for (int off = 1; off < CHOCO_THREADS; off <<= 1) {
+    uint32_t v = (threadIdx.x + off < CHOCO_THREADS) ? sh[threadIdx.x + off] : 0u;
+    __syncthreads();
+    sh[threadIdx.x] += v;
+    __syncthreads();
+  }
+  uint32_t above = (threadIdx.x + 1 < CHOCO_THREADS) ? sh[threadIdx.x + 1] : 0u;  // bins of higher threads
+  __syncthreads();
+  for (int j = per - 1; j >= 0; --j) {
+    if (above < k && k <= above + local[j]) {
+      sh[CHOCO_THREADS] = threadIdx.x * per + j;
+      sh[CHOCO_THREADS + 1] = k - above;
+    }
+    above += local[j];
+  }
+  __syncthreads();
+  bucket = sh[CHOCO_THREADS];
+  k_rem = sh[CHOCO_THREADS + 1];
+  __syncthreads();
+}
+
+// pass 2: digit-2 histogram of keys whose digit 1 equals the selected bucket
+// pass 3: digit-3 histogram of keys whose digits 1 and 2 equal the selected buckets
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_hist_kernel(const ChocoParams* __restrict__ params,
+                                                                      int pass) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const int chunk = blockIdx.x;
+  __shared__ uint32_t sh[CHOCO_THREADS + 2];
+  __shared__ uint32_t sh_hist[2048];
+  const int seg = tb.chunk_seg[chunk];
+  const int start = tb.chunk_start[chunk];
+  const int valid = tb.chunk_valid[chunk];
+  const uint32_t k = (uint32_t)tb.seg_k[seg];
+  uint32_t* gh = p.hist + (size_t)seg * CHOCO_HIST_WORDS;
+  uint32_t b1, k1, b2 = 0, k2 = 0;
+  find_bucket(gh, 2048, k, sh, b1, k1);
+  if (pass == 3) find_bucket(gh + 2048, 2048, k1, sh, b2, k2);
+  const int nb = pass == 2 ? 2048 : 512;
+  for (int i = threadIdx.x; i < nb; i += CHOCO_THREADS) sh_hist[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < valid; i += CHOCO_THREADS) {
+    const uint32_t key = key_of(p.scratch_d[start + i]);
+    if ((key >> 20) == b1) {
+      if (pass == 2) atomicAdd(&sh_hist[(key >> 9) & 2047u], 1u);
+      else if (((key >> 9) & 2047u) == b2) atomicAdd(&sh_hist[key & 511u], 1u);
+    }
+  }
+  __syncthreads();
+  uint32_t* out = gh + (pass == 2 ? 2048 : 4096);
+  for (int i = threadIdx.x; i < nb; i += CHOCO_THREADS)
+    if (sh_hist[i]) atomicAdd(out + i, sh_hist[i]);
+}
+
+extern "C" int choco_topk_hist(const void* params_dev, int n_chunks, int n_ranks, int pass, cudaStream_t stream) {
+  dim3 grid(n_chunks, n_ranks);
+  choco_topk_hist_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev), pass);
+  return (int)cudaGetLastError();
+}
+
+// threshold key and per-chunk counts
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_count_kernel(const ChocoParams* __restrict__ params) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const int chunk = blockIdx.x;
+  __shared__ uint32_t sh[CHOCO_THREADS + 2];
+  __shared__ float red[32];
+  const int seg = tb.chunk_seg[chunk];
+  const int start = tb.chunk_start[chunk];
+  const int valid = tb.chunk_valid[chunk];
+  const uint32_t k = (uint32_t)tb.seg_k[seg];
+  const uint32_t* gh = p.hist + (size_t)seg * CHOCO_HIST_WORDS;
+  uint32_t b1, k1, b2, k2, b3, k3;
+  find_bucket(gh, 2048, k, sh, b1, k1);
+  find_bucket(gh + 2048, 2048, k1, sh, b2, k2);
+  find_bucket(gh + 4096, 512, k2, sh, b3, k3);
+  const uint32_t thr = (b1 << 20) | (b2 << 9) | b3;
+  uint32_t gt = 0, eq = 0;
+  for (int i = threadIdx.x; i < valid; i += CHOCO_THREADS) {
+    const uint32_t key = key_of(p.scratch_d[start + i]);
+    gt += key > thr;
+    eq += key == thr;
+  }
+  // exact integer block sums through the float reducer would lose bits: use shuffles on ints
+  for (int o = 16; o > 0; o >>= 1) {
+    gt += __shfl_xor_sync(0xffffffffu, gt, o);
+    eq += __shfl_xor_sync(0xffffffffu, eq, o);
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) {
+    sh[(threadIdx.x >> 5) * 2] = gt;
+    sh[(threadIdx.x >> 5) * 2 + 1] = eq;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t g = 0, e = 0;
+    for (int w = 0; w < CHOCO_THREADS / 32; ++w) {
+      g += sh[w * 2];
+      e += sh[w * 2 + 1];
+    }
+    p.chunk_cnt[chunk * 2] = g;
+    p.chunk_cnt[chunk * 2 + 1] = e;
+    if (chunk == tb.seg_first_chunk[seg]) {
+      p.sel[seg * 4] = thr;
+      p.sel[seg * 4 + 1] = k3;  // how many keys equal to thr are kept (lowest indices first)
+    }
+  }
+  (void)red;
+}
+
+extern "C" int choco_topk_count(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
+  dim3 grid(n_chunks, n_ranks);
+  choco_topk_count_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  return (int)cudaGetLastError();
+}
+
+// publish helper shared by the emit kernels: last CTA raises the flags and advances the step
+__device__ __forceinline__ void publish_if_last(const ChocoParams& p, uint32_t n_ctas, uint32_t t) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(p.done_count, 1u) == n_ctas - 1) {
+      __threadfence_system();
+      p.done_count[0] = 0;
+      for (int k = 0; k < p.n_peers; ++k) st_release_sys(p.peer_flag[k], t + 1);
+      __threadfence();
+      p.step[0] = t + 1;
+    }
+  }
+}
+
+// ordered compaction: payload = [sum_k int32 indices][sum_k fp32 values]
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const ChocoParams* __restrict__ params) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const int chunk = blockIdx.x;
+  __shared__ uint32_t sh[CHOCO_THREADS + 2];
+  __shared__ uint32_t sh_base[2];
+  const int seg = tb.chunk_seg[chunk];
+  const int start = tb.chunk_start[chunk];
+  const int valid = tb.chunk_valid[chunk];
+  const int seg_start = tb.seg_start[seg];
+  const uint32_t t = p.step[0];
+  const int PW = p.payload_words, par_cur = t & 1;
+  const int sum_k = PW / 2;
+  const uint32_t thr = p.sel[seg * 4], need_eq = p.sel[seg * 4 + 1];
+  const int c0 = tb.seg_first_chunk[seg];
+
+  // totals of the preceding chunks of this segment
+  uint32_t gt_b = 0, eq_b = 0;
+  for (int c = c0 + threadIdx.x; c < chunk; c += CHOCO_THREADS) {
+    gt_b += __ldcg(p.chunk_cnt + c * 2);
+    eq_b += __ldcg(p.chunk_cnt + c * 2 + 1);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    gt_b += __shfl_xor_sync(0xffffffffu, gt_b, o);
+    eq_b += __shfl_xor_sync(0xffffffffu, eq_b, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sh[(threadIdx.x >> 5) * 2] = gt_b;
+    sh[(threadIdx.x >> 5) * 2 + 1] = eq_b;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t g = 0, e = 0;
+    for (int w = 0; w < CHOCO_THREADS / 32; ++w) {
+      g += sh[w * 2];
+      e += sh[w * 2 + 1];
+    }
+    sh_base[0] = g;
+    sh_base[1] = e;
+  }
+  __syncthreads();
+  uint32_t G = sh_base[0], E = sh_base[1];  // running counts before the current tile
+  const int koff = tb.seg_koff[seg];
+  uint32_t* out_idx = p.outbox + par_cur * PW;
+  uint32_t* out_val = out_idx + sum_k;
+
+  const int n_tiles = (valid + CHOCO_THREADS - 1) / CHOCO_THREADS;
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int i = tile * CHOCO_THREADS + threadIdx.x;
+    float d = 0.f;
+    uint32_t is_gt = 0, is_eq = 0;
+    if (i < valid) {
+      d = p.scratch_d[start + i];
+      const uint32_t key = key_of(d);
+      is_gt = key > thr;
+      is_eq = key == thr;
+    }
+    // exclusive block scan of (gt, eq) packed as 16 + 16 bits (a tile holds 256 elements)
+    uint32_t v = is_gt | (is_eq << 16);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    uint32_t inc = v;
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += n;
+    }
+    __syncthreads();
+    if (lane == 31) sh[wid] = inc;
+    __syncthreads();
+    uint32_t warp_off = 0, tile_tot = 0;
+    for (int w = 0; w < CHOCO_THREADS / 32; ++w) {
+      const uint32_t s = sh[w];
+      if (w < wid) warp_off += s;
+      tile_tot += s;
+    }
+    const uint32_t exc = warp_off + inc - v;
+    const uint32_t g_before = G + (exc & 0xFFFFu), e_before = E + (exc >> 16);
+    const bool take = is_gt || (is_eq && e_before < need_eq);
+    if (take) {
+      const uint32_t slot = koff + g_before + (e_before < need_eq ? e_before : need_eq);
+      const uint32_t idx = (uint32_t)(start + i - seg_start);
+      const uint32_t vb = __float_as_uint(d);
+      out_idx[slot] = idx;
+      out_val[slot] = vb;
+      for (int k = 0; k < p.n_peers; ++k) {
+        uint32_t* pi = p.peer_inbox[k] + par_cur * PW;
+        pi[slot] = idx;
+        pi[sum_k + slot] = vb;
+      }
+    }
+    G += tile_tot & 0xFFFFu;
+    E += tile_tot >> 16;
+  }
+  // the first chunk of a segment clears the segment's histograms for the next step
+  if (chunk == c0) {
+    uint32_t* gh = p.hist + (size_t)seg * CHOCO_HIST_WORDS;
+    for (int i = threadIdx.x; i < CHOCO_HIST_WORDS; i += CHOCO_THREADS) gh[i] = 0;
+  }
+  publish_if_last(p, (uint32_t)tb.n_chunks, t);
+}
+
+extern "C" int choco_topk_emit(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
+  dim3 grid(n_chunks, n_ranks);
+  choco_topk_emit_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  return (int)cudaGetLastError();
+}
+
+__device__ __forceinline__ int segment_of_entry(const SegTable& tb, int e) {
+  int lo = 0, hi = tb.n_segments - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (tb.seg_koff[mid] <= e) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// random-k: payload = [sum_k fp32 values]; entry e of tensor `seg` is element perm(e - koff)
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_randk_emit_kernel(const ChocoParams* __restrict__ params) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const uint32_t t = p.step[0];
+  const int PW = p.payload_words, par_cur = t & 1;
+  const int sum_k = PW;
+  for (int e = blockIdx.x * CHOCO_THREADS + threadIdx.x; e < sum_k; e += gridDim.x * CHOCO_THREADS) {
+    const int seg = segment_of_entry(tb, e);
+    const uint32_t n = (uint32_t)tb.seg_size[seg];
+    uint32_t keys[4];
+#pragma unroll
+    for (uint32_t r = 0; r < 4; ++r) keys[r] = feistel_key(p.seed, t, (uint32_t)seg, r);
+    const uint32_t idx = feistel_perm((uint32_t)(e - tb.seg_koff[seg]), n, feistel_half_bits(n), keys);
+    const uint32_t vb = __float_as_uint(p.scratch_d[tb.seg_start[seg] + idx]);
+    p.outbox[par_cur * PW + e] = vb;
+    for (int k = 0; k < p.n_peers; ++k) p.peer_inbox[k][par_cur * PW + e] = vb;
+  }
+  publish_if_last(p, gridDim.x, t);
+}
+
+extern "C" int choco_randk_emit(const void* params_dev, int n_blocks, int n_ranks, cudaStream_t stream) {
+  dim3 grid(n_blocks, n_ranks);
+  choco_randk_emit_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  return (int)cudaGetLastError();
+}
+
+// Bounded wait for the neighbours' flags of step t-1 (one CTA per logical rank).
+__global__ void choco_wait_flags_kernel(const ChocoParams* __restrict__ params) {
+  const ChocoParams& p = params[blockIdx.x];
+  const uint32_t t = p.step[0];
+  if (t == 0 || p.step[2] >= t) return;
+  const int k = threadIdx.x;
+  if (k < p.n_peers && !wait_flag_ge(p.my_flag[k], t, p.wait_budget_ns))
+    report(p.status, CHOCO_TIMEOUT, p.peer_rank[k], (int)t - 1);
+}
+
+extern "C" int choco_wait_flags(const void* params_dev, int n_ranks, cudaStream_t stream) {
+  choco_wait_flags_kernel<<<n_ranks, 32, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  return (int)cudaGetLastError();
+}
+
+// Apply one source payload of step t-1:  src < 0: own (x_hat += v, s += w_ii v);  src = k: s += w_ik v.
+// codec 1 = top-k (indices in the payload), 2 = random-k (indices regenerated from the sender's seed).
+// mark_done: this is the last source; record that step t-1 has been applied.
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_decode_kernel(const ChocoParams* __restrict__ params,
+                                                                          int src, int codec, int mark_done) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const uint32_t t = p.step[0];
+  if (t == 0 || p.step[2] >= t || p.status[0] != CHOCO_OK) return;
+  if (src >= p.n_peers) return;  // this logical rank has fewer neighbours than the launch covers
+  (void)mark_done;
+  const int PW = p.payload_words, par_prev = (t - 1) & 1;
+  const int sum_k = codec == 1 ? PW / 2 : PW;
+  const uint32_t* pay = (src < 0 ? p.outbox : p.my_inbox[src]) + par_prev * PW;
+  const float w = src < 0 ? p.w_self : p.w_peer[src];
+  const int src_rank = src < 0 ? p.rank : p.peer_rank[src];
+  const uint32_t seed = p.seed - 7919u * (uint32_t)p.rank + 7919u * (uint32_t)src_rank;
+  for (int e = blockIdx.x * CHOCO_THREADS + threadIdx.x; e < sum_k; e += gridDim.x * CHOCO_THREADS) {
+    const int seg = segment_of_entry(tb, e);
+    uint32_t idx;
+    float v;
+    if (codec == 1) {
+      idx = __ldcg(pay + e);
+      v = __uint_as_float(__ldcg(pay + sum_k + e));
+      if (idx >= (uint32_t)tb.seg_size[seg]) {  // corrupt payload: record and skip
+        report(p.status, CHOCO_BAD_STEP, src_rank, (int)t - 1);
+        continue;
+      }
+    } else {
+      const uint32_t n = (uint32_t)tb.seg_size[seg];
+      uint32_t keys[4];
+#pragma unroll
+      for (uint32_t r = 0; r < 4; ++r) keys[r] = feistel_key(seed, t - 1, (uint32_t)seg, r);
+      idx = feistel_perm((uint32_t)(e - tb.seg_koff[seg]), n, feistel_half_bits(n), keys);
+      v = __uint_as_float(__ldcg(pay + e));
+    }
+    const int pos = tb.seg_start[seg] + (int)idx;
+    if (src < 0) p.x_hat[pos] += v;
+    p.s[pos] += w * v;
+  }
+}
+
+__global__ void choco_mark_decoded_kernel(const ChocoParams* __restrict__ params) {
+  const ChocoParams& p = params[blockIdx.x];
+  const uint32_t t = p.step[0];
+  if (threadIdx.x == 0 && t > 0 && p.step[2] < t && p.status[0] == CHOCO_OK) p.step[2] = t;
+}
+
+extern "C" int choco_sparse_decode(const void* params_dev, int n_blocks, int n_ranks, int src, int codec,
+                                   cudaStream_t stream) {
+  const ChocoParams* p = reinterpret_cast<const ChocoParams*>(params_dev);
+  if (src == 1000) {  // all sources applied: record it
+    choco_mark_decoded_kernel<<<n_ranks, 32, 0, stream>>>(p);
+    return (int)cudaGetLastError();
+  }
+  dim3 grid(n_blocks, n_ranks);
+  choco_sparse_decode_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(p, src, codec, 0);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,58 @@
+"""Layer factory shared by all model definitions.
+
+Models never instantiate ``torch.nn`` compute layers directly: they ask this module, which
+returns the framework's layer classes (``ops/nn.py``).  Those run the hand-written sm_100a
+kernels when the native path is enabled and the tensors live on a CUDA device, and the
+plain PyTorch ops otherwise (CPU tests, unsupported shapes)."""
+from __future__ import annotations
+
+import math
+
+import torch.nn as nn
+
+from ..ops import nn as native_nn
+
+Conv2d = native_nn.Conv2d
+BatchNorm2d = native_nn.BatchNorm2d
+BatchNorm1d = nn.BatchNorm1d
+Linear = native_nn.Linear
+ReLU = nn.ReLU
+MaxPool2d = nn.MaxPool2d
+AvgPool2d = nn.AvgPool2d
+Dropout = nn.Dropout
+Embedding = nn.Embedding
+LSTM = native_nn.LSTM
+
+
+def conv3x3(in_planes, out_planes, stride=1):
+    return Conv2d(in_planes, out_planes, kernel_size=3, stride=stride, padding=1, bias=False)
+
+
+def he_init(module: nn.Module, zero_linear_bias: bool = False):
+    """conv ~ N(0, sqrt(2 / (kh kw c_out))), BN gamma = 1 beta = 0
+    (``dl_code/pcode/models/resnet.py:130-140``)."""
+    for m in module.modules():
+        if isinstance(m, nn.Conv2d):
+            n = m.kernel_size[0] * m.kernel_size[1] * m.out_channels
+            m.weight.data.normal_(0, math.sqrt(2.0 / n))
+        elif isinstance(m, nn.BatchNorm2d):
+            m.weight.data.fill_(1)
+            m.bias.data.zero_()
+        elif zero_linear_bias and isinstance(m, nn.Linear) and m.bias is not None:
+            m.bias.data.zero_()
+
+
+def num_classes_of(dataset: str) -> int:
+    if dataset in ("cifar10", "svhn", "mnist", "stl10") or dataset.startswith("synthetic_cifar10"):
+        return 10
+    if dataset == "cifar100":
+        return 100
+    if "imagenet" in dataset:
+        return 1000
+    if dataset.startswith("synthetic"):
+        return 10
+    raise ValueError(f"unknown dataset {dataset!r}")
+
+
+def is_small_input(dataset: str) -> bool:
+    return "imagenet" not in dataset or "downsampled" in dataset

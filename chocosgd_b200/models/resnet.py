@@ -1,0 +1,136 @@
+"""ResNets for CIFAR-sized inputs (6n+2 layers) and ImageNet (18/34/50/101/152).
+
+Architecture and parameter names follow ``dl_code/pcode/models/resnet.py:16-294`` (so the
+``"bn" in name`` weight-decay rule and checkpoints carry over): CIFAR nets use widths
+16/32/64 with ``(size-2)/6`` blocks per stage and bottlenecks from size 44; stride-2 stages
+have a 1x1-conv + BN shortcut; AvgPool(8) + Linear."""
+from __future__ import annotations
+
+import torch.nn as nn
+
+from . import layers as L
+
+
+class BasicBlock(nn.Module):
+    expansion = 1
+
+    def __init__(self, in_planes, out_planes, stride=1, downsample=None):
+        super().__init__()
+        self.conv1 = L.conv3x3(in_planes, out_planes, stride)
+        self.bn1 = L.BatchNorm2d(out_planes)
+        self.relu = L.ReLU(inplace=True)
+        self.conv2 = L.conv3x3(out_planes, out_planes)
+        self.bn2 = L.BatchNorm2d(out_planes)
+        self.downsample = downsample
+        self.stride = stride
+
+    def forward(self, x):
+        residual = x if self.downsample is None else self.downsample(x)
+        out = self.relu(self.bn1(self.conv1(x)))
+        out = self.bn2(self.conv2(out))
+        return self.relu(out + residual)
+
+
+class Bottleneck(nn.Module):
+    expansion = 4
+
+    def __init__(self, in_planes, out_planes, stride=1, downsample=None):
+        super().__init__()
+        self.conv1 = L.Conv2d(in_planes, out_planes, kernel_size=1, bias=False)
+        self.bn1 = L.BatchNorm2d(out_planes)
+        self.conv2 = L.Conv2d(out_planes, out_planes, kernel_size=3, stride=stride, padding=1, bias=False)
+        self.bn2 = L.BatchNorm2d(out_planes)
+        self.conv3 = L.Conv2d(out_planes, out_planes * 4, kernel_size=1, bias=False)
+        self.bn3 = L.BatchNorm2d(out_planes * 4)
+        self.relu = L.ReLU(inplace=True)
+        self.downsample = downsample
+        self.stride = stride
+
+    def forward(self, x):
+        residual = x if self.downsample is None else self.downsample(x)
+        out = self.relu(self.bn1(self.conv1(x)))
+        out = self.relu(self.bn2(self.conv2(out)))
+        out = self.bn3(self.conv3(out))
+        return self.relu(out + residual)
+
+
+class _ResNetBase(nn.Module):
+    def _make_block(self, block_fn, planes, block_num, stride=1):
+        downsample = None
+        if stride != 1 or self.inplanes != planes * block_fn.expansion:
+            downsample = nn.Sequential(
+                L.Conv2d(self.inplanes, planes * block_fn.expansion, kernel_size=1, stride=stride, bias=False),
+                L.BatchNorm2d(planes * block_fn.expansion),
+            )
+        blocks = [block_fn(self.inplanes, planes, stride, downsample)]
+        self.inplanes = planes * block_fn.expansion
+        blocks += [block_fn(self.inplanes, planes) for _ in range(1, block_num)]
+        return nn.Sequential(*blocks)
+
+
+class ResNetCifar(_ResNetBase):
+    def __init__(self, dataset, resnet_size):
+        super().__init__()
+        if resnet_size % 6 != 2:
+            raise ValueError("resnet_size must be 6n + 2:", resnet_size)
+        n = (resnet_size - 2) // 6
+        block_fn = Bottleneck if resnet_size >= 44 else BasicBlock
+        self.dataset = dataset
+        self.num_classes = L.num_classes_of(dataset)
+        self.inplanes = 16
+        self.conv1 = L.Conv2d(3, 16, kernel_size=3, stride=1, padding=1, bias=False)
+        self.bn1 = L.BatchNorm2d(16)
+        self.relu = L.ReLU(inplace=True)
+        self.layer1 = self._make_block(block_fn, 16, n)
+        self.layer2 = self._make_block(block_fn, 32, n, stride=2)
+        self.layer3 = self._make_block(block_fn, 64, n, stride=2)
+        self.avgpool = L.AvgPool2d(kernel_size=8)
+        self.fc = L.Linear(64 * block_fn.expansion, self.num_classes)
+        L.he_init(self)
+
+    def forward(self, x):
+        x = self.relu(self.bn1(self.conv1(x)))
+        x = self.layer3(self.layer2(self.layer1(x)))
+        x = self.avgpool(x)
+        return self.fc(x.reshape(x.size(0), -1))
+
+
+class ResNetImagenet(_ResNetBase):
+    CONFIGS = {
+        18: (BasicBlock, [2, 2, 2, 2]),
+        34: (BasicBlock, [3, 4, 6, 3]),
+        50: (Bottleneck, [3, 4, 6, 3]),
+        101: (Bottleneck, [3, 4, 23, 3]),
+        152: (Bottleneck, [3, 8, 36, 3]),
+    }
+
+    def __init__(self, dataset, resnet_size):
+        super().__init__()
+        block_fn, nums = self.CONFIGS[resnet_size]
+        self.dataset = dataset
+        self.num_classes = L.num_classes_of(dataset)
+        self.inplanes = 64
+        self.conv1 = L.Conv2d(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
+        self.bn1 = L.BatchNorm2d(64)
+        self.relu = L.ReLU(inplace=True)
+        self.maxpool = L.MaxPool2d(kernel_size=3, stride=2, padding=1)
+        self.layer1 = self._make_block(block_fn, 64, nums[0])
+        self.layer2 = self._make_block(block_fn, 128, nums[1], stride=2)
+        self.layer3 = self._make_block(block_fn, 256, nums[2], stride=2)
+        self.layer4 = self._make_block(block_fn, 512, nums[3], stride=2)
+        self.avgpool = L.AvgPool2d(kernel_size=7, stride=1)
+        self.fc = L.Linear(512 * block_fn.expansion, self.num_classes)
+        L.he_init(self)
+
+    def forward(self, x):
+        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+        x = self.avgpool(x)
+        return self.fc(x.reshape(x.size(0), -1))
+
+
+def resnet(conf):
+    size = int(conf.arch.replace("resnet", ""))
+    if "imagenet" in conf.data and "downsampled" not in conf.data:
+        return ResNetImagenet(conf.data, size)
+    return ResNetCifar(conf.data, size)

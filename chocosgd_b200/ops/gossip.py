@@ -1,0 +1,385 @@
+"""Fused CHOCO-SGD engine: launches the hand-written gossip kernels.
+
+``ChocoEngine`` owns everything the kernels need besides the optimizer's flat buffers:
+the chunk / segment tables, the device-resident hyper-parameters and step counters, the
+outbox, the peer-mapped mailbox and the ``ChocoParams`` blocks in device memory.  One
+engine drives one logical rank per GPU in production (``for_optimizer``) or all logical
+ranks of a graph on one GPU (``LoopbackWorld``, used to test the very same kernels without
+NVLink).
+
+Per training step the engine launches (everything on the current stream, capturable in a
+CUDA graph because the step index and learning rate live in device memory):
+
+=========  ====================================================================================
+sign       1 kernel  ``choco_sign_step`` (decode t-1, SGD, consensus, compress, push, publish)
+qsgd       2 kernels ``choco_dense_prep`` + ``choco_qsgd_pack``
+top-k      wait + (deg+1) sparse decodes + prep + 2 histogram passes + count + emit
+random-k   wait + (deg+1) sparse decodes + prep + emit
+=========  ====================================================================================
+
+No ``torch.distributed`` call and no stand-alone elementwise kernel is on this path
+(the reference: ``dl_code/pcode/optim/parallel_choco_v.py:104-155``, ~65-161 per-tensor op
+sequences plus three flatten/unflatten copies and ``isend``/``irecv`` per step).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..compress.reference import qsgd_levels_from, qsgd_nbits
+from ..compress.segments import Segments
+from ..parallel.symm import DistributedMailbox, LoopbackMailbox, MailboxView
+from ..utils.error_handler import GossipTimeout
+from . import _lib
+
+MODE_DECODE, MODE_PUSH = 1, 2
+CODEC_ID = {"sign": 3, "quantize_qsgd": 0, "compress_top_k": 1, "compress_random_k": 2}
+HYP_LR, HYP_MOMENTUM, HYP_GAMMA, HYP_NESTEROV, HYP_GSCALE, HYP_N = 0, 1, 2, 3, 4, 8
+
+
+def pick_chunk_elems(total: int) -> int:
+    if total <= (1 << 22):
+        return 1024
+    if total <= (1 << 26):
+        return 4096
+    return 8192
+
+
+class SegTables:
+    """Host-built chunk / segment tables, uploaded once."""
+
+    def __init__(self, seg: Segments, weight_decay: Sequence[float], ks: Optional[Sequence[int]], device,
+                 chunk_elems: Optional[int] = None):
+        self.seg = seg
+        ce = chunk_elems or pick_chunk_elems(seg.total)
+        chunk_seg, chunk_start, chunk_valid, first, count = [], [], [], [], []
+        for t, (off, n) in enumerate(zip(seg.offsets, seg.sizes)):
+            first.append(len(chunk_seg))
+            done = 0
+            while done < n:
+                v = min(ce, n - done)
+                chunk_seg.append(t)
+                chunk_start.append(off + done)
+                chunk_valid.append(v)
+                done += v
+            count.append(len(chunk_seg) - first[-1])
+        ks = list(ks) if ks is not None else [0] * seg.n_segments
+        koff = np.concatenate([[0], np.cumsum(ks)[:-1]]) if ks else np.zeros(0)
+
+        def dev(a, dt):
+            return torch.as_tensor(np.asarray(a, dtype=dt), device=device)
+
+        self.chunk_elems = ce
+        self.n_chunks = len(chunk_seg)
+        self.sum_k = int(sum(ks))
+        self.t = {
+            "chunk_seg": dev(chunk_seg, np.int32),
+            "chunk_start": dev(chunk_start, np.int32),
+            "chunk_valid": dev(chunk_valid, np.int32),
+            "seg_start": dev(seg.offsets, np.int32),
+            "seg_size": dev(seg.sizes, np.int32),
+            "seg_first_chunk": dev(first, np.int32),
+            "seg_n_chunks": dev(count, np.int32),
+            "seg_wd": dev(list(weight_decay), np.float32),
+            "seg_k": dev(ks, np.int32),
+            "seg_koff": dev(koff, np.int32),
+        }
+
+    def fill(self, c: _lib.SegTableC):
+        for k, v in self.t.items():
+            setattr(c, k, v.data_ptr())
+        c.n_chunks, c.n_segments = self.n_chunks, self.seg.n_segments
+        c.chunk_elems, c.total = self.chunk_elems, self.seg.total
+
+
+class RankBuffers:
+    """Flat state of one logical rank (all fp32, length ``seg.total``)."""
+
+    def __init__(self, x, g, m, x_hat, s):
+        self.x, self.g, self.m, self.x_hat, self.s = x, g, m, x_hat, s
+
+
+def payload_layout(comm_op: str, seg: Segments, sum_k: int, nbits: int):
+    """-> (payload_words, body_off)."""
+    header = (seg.n_segments + 31) // 32 * 32
+    if comm_op is None:
+        return 32, 0
+    if comm_op == "sign":
+        return header + seg.total // 32, header
+    if comm_op == "quantize_qsgd":
+        return header + (seg.total // 32) * (nbits + 1), header
+    if comm_op == "compress_top_k":
+        return 2 * sum_k, 0
+    if comm_op == "compress_random_k":
+        return sum_k, 0
+    raise NotImplementedError(comm_op)
+
+
+class ChocoEngine:
+    def __init__(
+        self,
+        ranks: List[int],
+        buffers: Dict[int, RankBuffers],
+        neighborhoods: Dict[int, Dict[int, float]],
+        seg: Segments,
+        weight_decay: Sequence[float],
+        comm_op: str,
+        mailbox,
+        device,
+        compress_ratio: Optional[float] = None,
+        quantize_level: Optional[int] = None,
+        qsgd_levels: Optional[int] = None,
+        is_biased: bool = False,
+        seed: int = 1234,
+        wait_budget_ms: float = 2000.0,
+        chunk_elems: Optional[int] = None,
+    ):
+        if comm_op is not None and comm_op not in CODEC_ID:
+            raise NotImplementedError(f"fused gossip kernels do not cover comm_op={comm_op!r}")
+        self.lib = _lib.load()
+        self.device = torch.device(device)
+        # comm_op None: local fused SGD only (no payloads, no mailbox traffic)
+        self.comm_op, self.codec = comm_op, CODEC_ID.get(comm_op, -1)
+        self.ranks, self.buffers, self.seg = list(ranks), buffers, seg
+        self.n_local = len(self.ranks)
+        ks = seg.keep_counts(compress_ratio) if (comm_op and "compress" in comm_op) else None
+        self.tables = SegTables(seg, weight_decay, ks, self.device, chunk_elems)
+        self.s_levels = qsgd_levels_from(quantize_level, qsgd_levels) if comm_op == "quantize_qsgd" else 1
+        self.nbits = qsgd_nbits(self.s_levels) if comm_op == "quantize_qsgd" else 0
+        self.payload_words, self.body_off = payload_layout(comm_op, seg, self.tables.sum_k, self.nbits)
+        self.mailbox = mailbox(self.payload_words) if callable(mailbox) else mailbox
+        peers_max = max(len([j for j in neighborhoods[r] if j != r]) for r in self.ranks)
+        if peers_max > _lib.MAX_PEERS:
+            raise ValueError(f"a rank has {peers_max} neighbours; the fused kernels support {_lib.MAX_PEERS}")
+        self.max_peers = peers_max
+        same = all(len([j for j in neighborhoods[r] if j != r]) == peers_max for r in self.ranks)
+        self.peers_hint = peers_max if (same and peers_max in (0, 1, 2, 4, 7)) else -1
+
+        T, nc, dev = seg.n_segments, self.tables.n_chunks, self.device
+        z = lambda n, dt: torch.zeros(n, dtype=dt, device=dev)
+        self.hyper = z(HYP_N, torch.float32)
+        self.hyper_host = torch.zeros(HYP_N, dtype=torch.float32)
+        if dev.type == "cuda":
+            self.hyper_host = self.hyper_host.pin_memory()
+        self.hyper_host[HYP_GSCALE] = 1.0
+        self._hyper_sent = None
+        self.per_rank = {}
+        blocks = []
+        sparse = self.codec in (1, 2)
+        for r in self.ranks:
+            b = buffers[r]
+            res = {
+                "step": z(4, torch.int32),
+                "seg_count": z(T, torch.int32),
+                "done_count": z(4, torch.int32),
+                "partial": z(nc, torch.float32),
+                "status": z(4, torch.int32),
+                "outbox": z(2 * self.payload_words, torch.int32),
+                "scratch_d": z(seg.total, torch.float32) if self.codec != 3 else None,
+                "hist": z(T * self.lib.choco_hist_words(), torch.int32) if self.codec == 1 else None,
+                "chunk_cnt": z(2 * nc, torch.int32) if self.codec == 1 else None,
+                "sel": z(4 * T, torch.int32) if self.codec == 1 else None,
+            }
+            self.per_rank[r] = res
+            view: MailboxView = self.mailbox.view(r)
+            nb = neighborhoods[r]
+            c = _lib.ChocoParamsC()
+            c.x, c.g, c.m, c.x_hat, c.s = (t.data_ptr() for t in (b.x, b.g, b.m, b.x_hat, b.s))
+            c.scratch_d = res["scratch_d"].data_ptr() if res["scratch_d"] is not None else 0
+            c.outbox = res["outbox"].data_ptr()
+            for k, j in enumerate(view.peers):
+                c.peer_inbox[k], c.peer_flag[k] = view.peer_inbox[k], view.peer_flag[k]
+                c.my_inbox[k], c.my_flag[k] = view.my_inbox[k], view.my_flag[k]
+                c.w_peer[k] = float(nb[j])
+                c.peer_rank[k] = int(j)
+            c.hyper = self.hyper.data_ptr()
+            for name in ("step", "seg_count", "done_count", "partial", "status"):
+                setattr(c, name, res[name].data_ptr())
+            for name in ("hist", "chunk_cnt", "sel"):
+                setattr(c, name, res[name].data_ptr() if res[name] is not None else 0)
+            c.wait_budget_ns = int(wait_budget_ms * 1e6)
+            self.tables.fill(c.tab)
+            c.w_self = float(nb[r])
+            c.n_peers = len(view.peers)
+            c.payload_words, c.body_off, c.rank = self.payload_words, self.body_off, int(r)
+            c.seed = (int(seed) + 7919 * int(r)) & 0xFFFFFFFF
+            c.qsgd_s, c.qsgd_nbits, c.qsgd_biased = int(self.s_levels), int(self.nbits), int(bool(is_biased))
+            blocks.append(c)
+        self._structs = blocks
+        self._grad_tables = {}
+        raw = np.frombuffer(b"".join(bytes(c) for c in blocks), dtype=np.uint8).copy()
+        self.params = torch.from_numpy(raw).to(dev)
+        self._pp = ctypes.c_void_p(self.params.data_ptr())
+        self._steps = 0
+        self.sparse = sparse
+        self.entry_blocks = max(1, min(1184, (self.tables.sum_k + 255) // 256)) if sparse else 1
+
+    # ---- construction helpers --------------------------------------------------------------
+    @classmethod
+    def for_optimizer(cls, opt, group=None):
+        """Engine of one rank of a distributed run (one process per GPU)."""
+        conf, graph = opt.conf, opt.graph
+        if opt.momentum_buf is None:
+            opt.momentum_buf = torch.zeros_like(opt.arena.x)
+        bufs = {graph.rank: RankBuffers(opt.arena.x, opt.arena.g, opt.momentum_buf, opt.x_hat, opt.s)}
+        nbh = {graph.rank: graph.get_neighborhood()}
+        wd = [g["weight_decay"] for g in opt.param_groups]
+        if graph.n_nodes > 1:
+            mailbox = lambda pw: DistributedMailbox(graph, pw, opt.device, group)
+        else:
+            mailbox = lambda pw: LoopbackMailbox({graph.rank: []}, pw, opt.device)
+        return cls(
+            [graph.rank], bufs, nbh, opt.seg, wd, conf.comm_op, mailbox, opt.device,
+            compress_ratio=conf.compress_ratio, quantize_level=conf.quantize_level,
+            qsgd_levels=getattr(conf, "qsgd_levels", None), is_biased=conf.is_biased,
+            seed=getattr(conf, "random_k_seed", 1234), wait_budget_ms=getattr(conf, "wait_budget_ms", 2000.0),
+        )
+
+    def set_grad_pointers(self, rank, grads: Optional[Sequence[torch.Tensor]]):
+        """Let the kernels read each tensor's gradient where autograd left it (one contiguous,
+        16-byte aligned fp32 tensor per parameter) instead of a packed flat buffer.
+        ``None`` switches back to the flat gradient."""
+        i = self.ranks.index(rank)
+        if grads is None:
+            self._grad_tables.pop(rank, None)
+            self._structs[i].seg_g = 0
+        else:
+            assert len(grads) == self.seg.n_segments
+            for gt, n in zip(grads, self.seg.sizes):
+                assert gt.is_contiguous() and gt.dtype == torch.float32 and gt.numel() == n
+                assert gt.data_ptr() % 16 == 0
+            table = torch.tensor([gt.data_ptr() for gt in grads], dtype=torch.int64).to(self.device)
+            self._grad_tables[rank] = (table, list(grads))
+            self._structs[i].seg_g = table.data_ptr()
+        raw = np.frombuffer(b"".join(bytes(c) for c in self._structs), dtype=np.uint8).copy()
+        self.params.copy_(torch.from_numpy(raw), non_blocking=False)
+
+    # ---- hyper-parameters ---------------------------------------------------------------------
+    def set_hyper(self, lr, momentum, gamma, nesterov):
+        key = (float(lr), float(momentum), float(gamma), bool(nesterov))
+        if key == self._hyper_sent:
+            return
+        h = self.hyper_host
+        h[HYP_LR], h[HYP_MOMENTUM], h[HYP_GAMMA], h[HYP_NESTEROV] = key[0], key[1], key[2], 1.0 if key[3] else 0.0
+        # slots 0..3 only: slot 4 (gradient scale) is written by the clipping kernel
+        self.hyper[:4].copy_(h[:4], non_blocking=True)
+        if self._hyper_sent is None:
+            self.hyper[4:].copy_(h[4:], non_blocking=True)
+        self._hyper_sent = key
+
+    # ---- launches ---------------------------------------------------------------------------------
+    def _chk(self, code, what):
+        _lib.check(code, what)
+
+    def launch_step(self, stream=None):
+        """All kernels of one CHOCO step on ``stream`` (default: current)."""
+        L, pp, nc, nr = self.lib, self._pp, self.tables.n_chunks, self.n_local
+        sp = _lib.stream_ptr(stream)
+        if self.codec == 3:
+            self._chk(L.choco_sign_step(pp, nc, nr, MODE_DECODE | MODE_PUSH, self.peers_hint, sp), "choco_sign_step")
+        elif self.codec == 0:
+            self._chk(L.choco_dense_prep(pp, nc, nr, MODE_DECODE, 0, sp), "choco_dense_prep")
+            self._chk(L.choco_qsgd_pack(pp, nc, nr, sp), "choco_qsgd_pack")
+        else:
+            self._launch_sparse_decode(sp)
+            self._chk(L.choco_dense_prep(pp, nc, nr, 0, self.codec, sp), "choco_dense_prep")
+            if self.codec == 1:
+                self._chk(L.choco_topk_hist(pp, nc, nr, 2, sp), "choco_topk_hist2")
+                self._chk(L.choco_topk_hist(pp, nc, nr, 3, sp), "choco_topk_hist3")
+                self._chk(L.choco_topk_count(pp, nc, nr, sp), "choco_topk_count")
+                self._chk(L.choco_topk_emit(pp, nc, nr, sp), "choco_topk_emit")
+            else:
+                self._chk(L.choco_randk_emit(pp, self.entry_blocks, nr, sp), "choco_randk_emit")
+        self._steps += 1
+
+    def _launch_sparse_decode(self, sp):
+        L, pp, nr = self.lib, self._pp, self.n_local
+        self._chk(L.choco_wait_flags(pp, nr, sp), "choco_wait_flags")
+        for src in range(-1, self.max_peers):
+            self._chk(L.choco_sparse_decode(pp, self.entry_blocks, nr, src, self.codec, sp), "choco_sparse_decode")
+        self._chk(L.choco_sparse_decode(pp, 1, nr, 1000, self.codec, sp), "choco_mark_decoded")
+
+    def launch_decode(self, stream=None):
+        """Apply the payloads of the last push to x_hat / s (end of training, checkpoints)."""
+        L, pp, nc, nr = self.lib, self._pp, self.tables.n_chunks, self.n_local
+        sp = _lib.stream_ptr(stream)
+        if self.codec == 3:
+            self._chk(L.choco_sign_step(pp, nc, nr, MODE_DECODE, self.peers_hint, sp), "choco_sign_decode")
+        elif self.codec == 0:
+            self._chk(L.choco_qsgd_decode(pp, nc, nr, sp), "choco_qsgd_decode")
+        else:
+            self._launch_sparse_decode(sp)
+
+    def launch_sgd_only(self, apply=True, stream=None):
+        self._chk(
+            self.lib.fused_sgd_step(self._pp, self.tables.n_chunks, self.n_local, 1 if apply else 0,
+                                    _lib.stream_ptr(stream)),
+            "fused_sgd_step",
+        )
+
+    # ---- optimizer-facing API ----------------------------------------------------------------------
+    def step(self, opt):
+        self.set_hyper(opt.lr, opt.momentum, opt.consensus_stepsize, opt.nesterov)
+        self.launch_step()
+        bits = opt.n_bits
+        opt.n_bits = opt.codec.n_bits()
+        opt.gossip_step += 1
+        return bits
+
+    def flush(self, opt=None):
+        self.launch_decode()
+        self.check()
+
+    def reset_step(self, step: int):
+        for r in self.ranks:
+            st = self.per_rank[r]["step"]
+            st[0], st[2] = int(step), int(step)
+            st[1] = 1 if step > 0 else 0
+
+    def check(self):
+        """Read the status words (synchronises); raise on a timed-out wait."""
+        for r in self.ranks:
+            code, peer, step, _ = self.per_rank[r]["status"].tolist()
+            if code != 0:
+                raise GossipTimeout(code, peer, step)
+
+    def step_index(self, rank=None) -> int:
+        r = self.ranks[0] if rank is None else rank
+        return int(self.per_rank[r]["step"][0])
+
+    def close(self):
+        if hasattr(self.mailbox, "close"):
+            self.mailbox.close()
+
+
+class LoopbackWorld:
+    """All ``n`` logical ranks of a graph on ONE GPU: the production kernels run with
+    gridDim.y = n and "peer" pointers that are local, so flags, parities, payload layouts and
+    the arithmetic are exercised without NVLink.  State tensors are ``[n, total]``."""
+
+    def __init__(self, w: np.ndarray, seg: Segments, x0: torch.Tensor, comm_op: str, weight_decay, device="cuda",
+                 **codec_kw):
+        n = w.shape[0]
+        self.n, self.seg, self.device = n, seg, torch.device(device)
+        mk = lambda: torch.zeros(n, seg.total, dtype=torch.float32, device=self.device)
+        self.x, self.g, self.m, self.x_hat, self.s = mk(), mk(), mk(), mk(), mk()
+        self.x.copy_(x0.to(self.device) if x0.dim() == 2 else x0.to(self.device).repeat(n, 1))
+        nbh = {i: {j: float(w[i, j]) for j in range(n) if (w[i, j] != 0 or j == i)} for i in range(n)}
+        peers = {i: [j for j in nbh[i] if j != i] for i in range(n)}
+        bufs = {i: RankBuffers(self.x[i], self.g[i], self.m[i], self.x_hat[i], self.s[i]) for i in range(n)}
+        wd = weight_decay if hasattr(weight_decay, "__len__") else [weight_decay] * seg.n_segments
+        self.engine = ChocoEngine(
+            list(range(n)), bufs, nbh, seg, wd, comm_op, lambda pw: LoopbackMailbox(peers, pw, self.device),
+            self.device, **codec_kw,
+        )
+
+    def step(self, grads: torch.Tensor, lr, momentum, gamma, nesterov):
+        self.g.copy_(grads.to(self.device))
+        self.engine.set_hyper(lr, momentum, gamma, nesterov)
+        self.engine.launch_step()
+
+    def flush(self):
+        self.engine.flush()

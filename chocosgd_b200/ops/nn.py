@@ -1,0 +1,59 @@
+"""Layer classes used by the model zoo.
+
+Each class is a drop-in subclass of the ``torch.nn`` layer (same parameters, same
+``state_dict`` keys).  ``set_native(True)`` routes the forward/backward of supported
+shapes on CUDA tensors to the hand-written kernels; everything else (CPU, unsupported
+shapes, ``set_native(False)``) runs the stock PyTorch op, which also serves as the numerics
+reference in the tests."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+_NATIVE = {"linear": False, "conv": False, "lstm": False}
+
+
+def set_native(enabled: bool = True, which=("linear", "conv", "lstm")):
+    for k in which:
+        _NATIVE[k] = bool(enabled)
+
+
+def native_enabled(kind: str) -> bool:
+    return _NATIVE[kind]
+
+
+class Linear(nn.Linear):
+    def forward(self, x):
+        if _NATIVE["linear"] and x.is_cuda and x.dtype == torch.float32:
+            from .gemm import linear_native, linear_supported
+
+            if linear_supported(x, self.weight):
+                return linear_native(x, self.weight, self.bias)
+        return F.linear(x, self.weight, self.bias)
+
+
+class Conv2d(nn.Conv2d):
+    def forward(self, x):
+        if _NATIVE["conv"] and x.is_cuda:
+            from .conv import conv2d_native, conv_supported
+
+            if conv_supported(self, x):
+                return conv2d_native(self, x)
+        return super().forward(x)
+
+
+class BatchNorm2d(nn.BatchNorm2d):
+    pass
+
+
+class LSTM(nn.LSTM):
+    def forward(self, input, hx=None):
+        if _NATIVE["lstm"] and input.is_cuda and input.dtype == torch.float32:
+            from .lstm import lstm_native, lstm_supported
+
+            if lstm_supported(self, input):
+                return lstm_native(self, input, hx)
+        if input.is_cuda:
+            self.flatten_parameters()
+        return super().forward(input, hx)

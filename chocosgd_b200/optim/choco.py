@@ -103,14 +103,32 @@ class ChocoSGD(DistributedOptimizer):
                 self._finish_sync()
         return self.n_bits
 
+    # ---- fused path: host part / device part (the latter is what a CUDA graph captures) -------
+    @property
+    def capturable(self) -> bool:
+        return self.impl == "fused"
+
+    def prepare_step(self):
+        """Host side of a fused step: refresh the device-resident hyper-parameters, account bits."""
+        self.local_index += 1
+        self.engine.set_hyper(self.lr, self.momentum, self.consensus_stepsize, self.nesterov)
+        bits, self.n_bits = self.n_bits, self.codec.n_bits()
+        self.gossip_step += 1
+        return bits
+
+    def launch(self, stream=None):
+        """Device side of a fused step: the gossip kernels, nothing else."""
+        self.engine.launch_step(stream)
+
     # ---- public ------------------------------------------------------------------------------
     def step(self, closure=None, **kargs):
         timer, ep = self.timer_of(kargs), self.epoch_of(kargs)
-        self.local_index += 1
         if self.impl == "fused":
             with timer("sync.gossip_fused", epoch=ep):
-                bits = self.engine.step(self)
+                bits = self.prepare_step()
+                self.launch()
             return bits
+        self.local_index += 1
         return self._step_torch(timer, ep)
 
     def finalize(self):

@@ -17,10 +17,43 @@ class SGD(DistributedOptimizer):
     def __init__(self, model, conf, graph, group=None, is_centralized=None):
         super().__init__(model, conf, graph, group)
         self.is_centralized = (conf.graph_topology == "complete") if is_centralized is None else is_centralized
+        # single node on a GPU: the whole update is one fused kernel (capturable in a CUDA graph)
+        self.engine = None
+        want = getattr(conf, "gossip_impl", "auto")
+        if self.n_nodes == 1 and self.device.type == "cuda" and want != "nccl":
+            from ..ops.gossip import ChocoEngine, RankBuffers
+            from ..parallel.symm import LoopbackMailbox
+
+            self.momentum_buf = torch.zeros_like(self.arena.x)
+            z = torch.zeros(32, device=self.device)
+            bufs = {self.rank: RankBuffers(self.arena.x, self.arena.g, self.momentum_buf, z, z)}
+            self.engine = ChocoEngine(
+                [self.rank], bufs, {self.rank: {self.rank: 1.0}}, self.seg,
+                [g["weight_decay"] for g in self.param_groups], None,
+                lambda pw: LoopbackMailbox({self.rank: []}, pw, self.device), self.device,
+            )
+
+    @property
+    def capturable(self) -> bool:
+        return self.engine is not None
+
+    def prepare_step(self):
+        self.local_index += 1
+        self.engine.set_hyper(self.lr, self.momentum, 0.0, self.nesterov)
+        self.n_bits = 32 * self.seg.n_elements
+        return self.n_bits
+
+    def launch(self, stream=None):
+        self.engine.launch_sgd_only(True, stream)
 
     def step(self, closure=None, **kargs):
         timer, a = self.timer_of(kargs), self.arena
         ep = self.epoch_of(kargs)
+        if self.engine is not None:
+            with timer("sync.apply_grad", epoch=ep):
+                bits = self.prepare_step()
+                self.launch()
+            return bits
         self.local_index += 1
         if self.is_centralized:
             with timer("sync.sync", epoch=ep):

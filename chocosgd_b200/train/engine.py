@@ -1,0 +1,195 @@
+"""One training step as a replayable unit.
+
+``TrainStep`` is the public call a user makes per batch::
+
+    step = TrainStep(model, criterion, optimizer, example_input, example_target)
+    loss = step(input_from_pinned_host_memory, target)        # device 0-d tensor
+
+With a capturable (fused) optimizer on CUDA the whole step - forward, loss, backward,
+gradient clipping, the fused SGD/gossip kernels, metric accumulation - is captured once in a
+CUDA graph and replayed; the host only copies the batch into static buffers, refreshes the
+device-resident learning rate when it changes, and launches the graph.  Gradients are not
+packed: the update kernels read each tensor's gradient where autograd produced it, through a
+pointer table.  On CPU, or with an optimizer that communicates through ``torch.distributed``,
+the same object runs eagerly.
+
+The reference's loop does this on the host every step with per-tensor launches and three
+``.item()`` synchronisations (``dl_code/pcode/distributed_running_cv.py:42-62,154-161``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops.sgd import grad_clip_
+
+
+class TrainStep:
+    def __init__(
+        self,
+        model,
+        criterion,
+        optimizer,
+        example_input: torch.Tensor,
+        example_target: torch.Tensor,
+        metrics=None,
+        use_cuda_graph: bool = True,
+        clip_grad_norm: Optional[float] = None,
+        hidden=None,
+        amp_dtype: Optional[torch.dtype] = None,
+        warmup_iters: int = 3,
+        channels_last: bool = False,
+    ):
+        self.model, self.criterion, self.opt, self.metrics = model, criterion, optimizer, metrics
+        self.device = optimizer.device
+        self.clip = clip_grad_norm
+        self.amp_dtype = amp_dtype
+        self.channels_last = channels_last
+        self.is_cuda = self.device.type == "cuda"
+        self.fused = bool(getattr(optimizer, "capturable", False))
+        self.use_graph = bool(use_cuda_graph and self.is_cuda and self.fused)
+        self.static_input = torch.zeros(example_input.shape, dtype=example_input.dtype, device=self.device)
+        if channels_last and self.static_input.dim() == 4:
+            self.static_input = self.static_input.contiguous(memory_format=torch.channels_last)
+        self.static_target = torch.zeros(example_target.shape, dtype=example_target.dtype, device=self.device)
+        self.hidden = hidden  # tuple of static tensors for recurrent models
+        self.loss = torch.zeros((), dtype=torch.float32, device=self.device)
+        n_perf = len(metrics.metric_names) if metrics is not None else 0
+        self.perf = torch.zeros(n_perf, dtype=torch.float32, device=self.device)
+        self.graph = None
+        self.h2d_bytes = example_input.numel() * example_input.element_size() + (
+            example_target.numel() * example_target.element_size())
+        self._warm = 0
+        self._warmup_iters = warmup_iters
+        self.kernel_launches_per_step = None
+
+    # ---- the step body (captured or eager) ------------------------------------------------------
+    def _forward_backward(self):
+        params = self.opt.arena.params
+        if self.fused:
+            for p in params:
+                p.grad = None  # autograd then hands over its own gradient tensors (no accumulate kernels)
+        ctx = torch.autocast("cuda", dtype=self.amp_dtype) if self.amp_dtype is not None else _null()
+        with ctx:
+            if self.hidden is not None:
+                h = tuple(t.detach() for t in self.hidden)
+                out, new_h = self.model(self.static_input, h)
+                loss = self.criterion(out.reshape(-1, out.size(-1)), self.static_target.reshape(-1))
+            else:
+                out = self.model(self.static_input)
+                loss = self.criterion(out, self.static_target)
+        loss.backward()
+        with torch.no_grad():
+            if self.hidden is not None:
+                for dst, src in zip(self.hidden, new_h):
+                    dst.copy_(src.detach())
+            self.loss.copy_(loss.detach().float())
+            if self.metrics is not None:
+                tgt = self.static_target.reshape(-1) if self.hidden is not None else self.static_target
+                o = out.reshape(-1, out.size(-1)) if self.hidden is not None else out
+                perf = self.metrics.evaluate(loss, o.float(), tgt)
+                self.perf.copy_(torch.stack([p.float() for p in perf]))
+        return loss
+
+    def prime(self):
+        """Build the CUDA graph (runs ``warmup_iters`` + 1 real training steps on the data
+        currently in the static buffers)."""
+        if not self.use_graph or self.graph is not None:
+            return 0
+        # the table must exist (with its final address) before capture: create it from
+        # placeholder gradients, capture, then point it at the captured gradients
+        eng = self.opt.engine
+        eng.set_grad_pointers(self.opt.rank, [torch.zeros_like(p) for p in self.opt.arena.params])
+        table = eng._grad_tables[self.opt.rank][0]
+        self._grad_ptrs_dirty = True
+        n = self._capture_with_table(table)
+        return n
+
+    def _capture_with_table(self, table):
+        eng = self.opt.engine
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(self._warmup_iters):
+                self.opt.prepare_step()
+                self._forward_backward()
+                self._fill_table(table)
+                if self.clip is not None:
+                    grad_clip_(eng, self.clip)
+                self.opt.launch()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        for p in self.opt.arena.params:
+            p.grad = None
+        self.graph = torch.cuda.CUDAGraph()
+        self.opt.prepare_step()
+        with torch.cuda.graph(self.graph):
+            self._forward_backward()
+            if self.clip is not None:
+                grad_clip_(eng, self.clip)
+            self.opt.launch()
+        self._captured_grads = [p.grad for p in self.opt.arena.params]
+        self._fill_table(table)
+        torch.cuda.synchronize()
+        self.graph.replay()  # the captured step has not run yet: run it once (prepare_step was accounted above)
+        return self._warmup_iters + 1
+
+    def _fill_table(self, table):
+        grads = [p.grad for p in self.opt.arena.params]
+        for gt in grads:
+            assert gt is not None and gt.is_contiguous() and gt.data_ptr() % 16 == 0
+        host = torch.tensor([gt.data_ptr() for gt in grads], dtype=torch.int64)
+        table.copy_(host)
+        self._table_keepalive = grads
+
+    # ---- public call -----------------------------------------------------------------------------
+    def load_batch(self, inp: torch.Tensor, tgt: torch.Tensor):
+        self.static_input.copy_(inp, non_blocking=True)
+        self.static_target.copy_(tgt, non_blocking=True)
+
+    def __call__(self, inp: Optional[torch.Tensor] = None, tgt: Optional[torch.Tensor] = None, **step_kw):
+        """Run one training step; returns the loss as a 0-d device tensor (no host sync)."""
+        if inp is not None:
+            self.load_batch(inp, tgt)
+        if self.use_graph:
+            if self.graph is None:
+                self.prime()
+                return self.loss
+            self.opt.prepare_step()
+            self.graph.replay()
+            return self.loss
+        if self.fused:
+            eng = self.opt.engine
+            self.opt.prepare_step()
+            self._forward_backward()
+            if getattr(self, "_eager_table", None) is None:
+                eng.set_grad_pointers(self.opt.rank, [p.grad for p in self.opt.arena.params])
+                self._eager_table = eng._grad_tables[self.opt.rank][0]
+            else:
+                self._fill_table(self._eager_table)
+            if self.clip is not None:
+                grad_clip_(eng, self.clip)
+            self.opt.launch()
+            return self.loss
+        # eager path with a torch.distributed / CPU optimizer: gradients alias the flat arena
+        self.opt.arena.rebind() if self.opt.arena.params[0].grad is None else None
+        self._forward_backward()
+        if self.clip is not None:
+            g = self.opt.arena.g
+            norm = g.norm()
+            g.mul_(torch.clamp(self.clip / (norm + 1e-6), max=1.0))
+        self.opt.step(**step_kw)
+        return self.loss
+
+    @property
+    def n_bits(self):
+        return self.opt.n_bits
+
+
+class _null:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *a):
+        return False
