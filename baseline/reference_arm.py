@@ -1,0 +1,110 @@
+"""Reference arm of the benchmark: the UNMODIFIED reference code installed under
+``baseline/_ref`` (its ``pcode`` package), driven through its own public classes.
+
+What runs: ``pcode.models.resnet`` (ResNet-20), ``pcode.create_optimizer.define_optimizer``
+with ``--optimizer parallel_choco_v``, the reference compressors / aggregators / topology,
+and the body of its training iteration (``dl_code/pcode/distributed_running_cv.py:42-62``:
+host->device copy, zero_grad, forward, loss, metrics with their ``.item()`` reads, backward,
+``optimizer.step(timer=..., scheduler=...)``).  Nothing from ``chocosgd_b200`` is imported.
+
+Harness glue that is not reference code (each item is a documented deviation):
+* ``bit2byte`` (an external C++ extension the reference imports, not in its tree) is
+  replaced by a pure-PyTorch module with the same two functions;
+* ``dl_code/main.py`` cannot run offline (torchtext / spacy / datasets), so the loop body
+  is driven directly with synthetic CIFAR-shaped batches;
+* ``parallel_choco_v`` instead of ``parallel_choco`` (the latter hard-codes an MPI group);
+* ring needs n > 2 in the reference: n = 1, 2 use its ``complete`` graph, whose matrix
+  equals the ring rule there ([1] and 1/2 everywhere);
+* ``track_time`` off (its timer synchronises the device around every scope).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import torch
+import torch.distributed as dist
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.path.join(HERE, "_ref")
+
+
+def install_bit2byte_shim():
+    b = types.ModuleType("bit2byte")
+
+    def packing(src):  # int32 [32, M] of signs -> int32 [M]
+        out = torch.zeros(src.shape[1], dtype=torch.int64, device=src.device)
+        for i in range(32):
+            out |= (src[i] < 0).to(torch.int64) << i
+        out = torch.where(out >= 2 ** 31, out - 2 ** 32, out)
+        return out.to(torch.int32)
+
+    def unpacking(src, dst):  # int32 [M] -> values {0, 2} in dst [32, M]
+        s = src.to(torch.int64) & 0xFFFFFFFF
+        for i in range(32):
+            dst[i] = (2 * ((s >> i) & 1)).to(torch.int32)
+        return dst
+
+    b.packing, b.unpacking = packing, unpacking
+    sys.modules["bit2byte"] = b
+
+
+def available():
+    return os.path.isdir(os.path.join(REF, "pcode"))
+
+
+def build(rank, world, comm_op, batch_size, device):
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    install_bit2byte_shim()
+    import pcode.create_metrics as create_metrics
+    import pcode.create_optimizer as create_optimizer
+    import pcode.models as models
+    import pcode.utils.topology as topology
+    from pcode.utils.timer import Timer
+
+    topo = "ring" if world > 2 else "complete"
+    conf = argparse.Namespace(
+        arch="resnet20", data="cifar10", optimizer="parallel_choco_v", comm_op=comm_op,
+        compress_ratio=0.99, quantize_level=4, is_biased=True, backend="nccl", use_ipc=False,
+        consensus_stepsize=0.5, comm_device="cuda", weight_decay=1e-4, lr=0.1, momentum_factor=0.9,
+        use_nesterov=True, epoch_=0.5, local_index=0, distributed=True, graph_topology=topo,
+        n_mpi_process=world, n_sub_process=1, on_cuda=True, batch_size=batch_size,
+    )
+    conf.graph = topology.define_graph_topology(
+        topo, world=",".join(["0"] * world), n_mpi_process=world, n_sub_process=1, comm_device="cuda",
+        on_cuda=True, rank=rank,
+    )
+    torch.manual_seed(6)
+    model = models.resnet(conf).to(device)
+    optimizer = create_optimizer.define_optimizer(conf, model)
+    metrics = create_metrics.Metrics(model, task="classification")
+    timer = Timer(verbosity_level=0, on_cuda=True)
+    criterion = torch.nn.CrossEntropyLoss(reduction="mean")
+    return conf, model, optimizer, metrics, timer, criterion
+
+
+def train_iteration(conf, model, optimizer, metrics, timer, criterion, inp_host, tgt_host, step):
+    """One iteration of the reference's CV loop."""
+    model.train()
+    conf.local_index = step + 1
+    conf.epoch_ = (step + 1) / 391.0
+    _input, _target = inp_host.cuda(non_blocking=True), tgt_host.cuda(non_blocking=True)
+    optimizer.zero_grad()
+    output = model(_input)
+    loss = criterion(output, _target)
+    try:
+        perf = metrics.evaluate(loss, output, _target)  # .item() per metric, as in the reference
+    except RuntimeError:
+        # the reference flattens a transposed tensor with .view(-1), which torch >= 1.7
+        # rejects for top-5; same numbers, same two .item() reads, with .reshape(-1)
+        _, pred = output.topk(5, 1, True, True)
+        correct = pred.t().eq(_target.view(1, -1).expand_as(pred.t()))
+        perf = [correct[:k].reshape(-1).float().sum(0, keepdim=True).mul_(100.0 / _target.size(0)).item()
+                for k in (1, 5)]
+    loss_v = loss.item()
+    loss.backward()
+    optimizer.step(timer=timer, scheduler=None)
+    return loss_v, perf

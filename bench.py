@@ -1,0 +1,277 @@
+"""Headline benchmark: ResNet-20 (CIFAR shape, batch 128 per GPU, fp32) trained with
+CHOCO-SGD on a ring, images/s over all GPUs.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...             # the unmodified reference
+
+For N > 1 launch one rank per GPU with ``python -m torch.distributed.run``.  Rank 0 prints
+one JSON line.  Synthetic data (N(0,1) images, uniform labels), random-init weights.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH = 128
+N_HOST_BATCHES = 16
+QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=200)
+    p.add_argument("--warmup", type=int, default=20)
+    p.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    p.add_argument("--comm_op", default="compress_top_k",
+                   choices=("compress_top_k", "sign", "quantize_qsgd", "compress_random_k"))
+    p.add_argument("--no_graph", action="store_true")
+    p.add_argument("--native_layers", default="auto", choices=("auto", "on", "off"))
+    return p.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    def __init__(self, enabled, gpu_index):
+        self.proc, self.path = None, None
+        if not enabled:
+            return
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(gpu_index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                for name, v in zip(names, f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+def init_dist(n):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1 or n > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def host_batches(rank):
+    g = torch.Generator().manual_seed(1000 + rank)
+    xs = [torch.randn(BATCH, 3, 32, 32, generator=g).pin_memory() for _ in range(N_HOST_BATCHES)]
+    ys = [torch.randint(0, 10, (BATCH,), generator=g).pin_memory() for _ in range(N_HOST_BATCHES)]
+    return xs, ys
+
+
+def barrier_sync(world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms, world):
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return ms
+
+
+def timed(fn, steps, world):
+    """K calls of fn(i) bracketed by barrier + synchronize, CUDA events, max over ranks."""
+    barrier_sync(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    barrier_sync(world)
+    return max_over_ranks(ms, world)
+
+
+def run_ours(args, rank, world, local):
+    from chocosgd_b200.config import get_args
+    from chocosgd_b200.models import define_model
+    from chocosgd_b200.optim import define_optimizer
+    from chocosgd_b200.parallel.topology import Graph
+    from chocosgd_b200.train.engine import TrainStep
+    from chocosgd_b200.train.metrics import Metrics
+    from chocosgd_b200.ops import nn as native_nn
+
+    device = torch.device("cuda", local)
+    argv = ["--arch", "resnet20", "--data", "cifar10", "--optimizer", "parallel_choco_v", "--comm_op", args.comm_op,
+            "--graph_topology", "ring", "--n_mpi_process", str(world), "--lr", "0.1", "--momentum_factor", "0.9",
+            "--use_nesterov", "True", "--weight_decay", "1e-4", "--consensus_stepsize", "0.5",
+            "--batch_size", str(BATCH), "--gossip_impl", "fused"]
+    if "compress" in args.comm_op:
+        argv += ["--compress_ratio", "0.99"]
+    if args.comm_op == "quantize_qsgd":
+        argv += ["--quantize_level", "4", "--is_biased", "True"]
+    conf = get_args(argv)
+    graph = Graph("ring", world, rank)
+    torch.manual_seed(6)
+    torch.backends.cudnn.benchmark = True
+    if args.native_layers == "on":
+        native_nn.set_native(True)
+    model = define_model(conf, graph, device=device, verbose=False)
+    optimizer = define_optimizer(conf, model, graph)
+    metrics = Metrics(model)
+    criterion = torch.nn.CrossEntropyLoss()
+    xs, ys = host_batches(rank)
+    step = TrainStep(model, criterion, optimizer, xs[0], ys[0], metrics=metrics, use_cuda_graph=not args.no_graph)
+    model.train()
+    loss_host = torch.zeros(args.steps + args.warmup + 8, dtype=torch.float32).pin_memory()
+
+    # warm-up: graph capture + W untimed steps through the public call
+    for i in range(max(args.warmup, 3)):
+        step(xs[i % N_HOST_BATCHES], ys[i % N_HOST_BATCHES])
+    torch.cuda.synchronize()
+    optimizer.engine.check()
+
+    # (1) device-timed steps: the batch is already in the static device buffers
+    sampler = ClockSampler(rank == 0, local)
+    dev_ms = timed(lambda i: step(), args.steps, world)
+
+    # (2) end to end through the public API: pinned host batch -> device, step, loss -> host
+    def e2e(i):
+        loss = step(xs[i % N_HOST_BATCHES], ys[i % N_HOST_BATCHES])
+        loss_host[i:i + 1].copy_(loss.reshape(1), non_blocking=True)
+
+    e2e_ms = timed(e2e, args.steps, world)
+    clocks = sampler.stop()
+    optimizer.finalize()
+    optimizer.engine.check()
+    losses = loss_host[:args.steps]
+    assert torch.isfinite(losses).all(), "training diverged"
+    launches = optimizer.engine.launches_per_step * args.steps
+    return dev_ms, e2e_ms, clocks, launches, float(losses[-1]), step.h2d_bytes, {
+        "graph": step.use_graph, "native_layers": args.native_layers,
+        "kernels_per_step": optimizer.engine.launches_per_step}
+
+
+def run_reference(args, rank, world, local):
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ref
+
+    if not ref.available():
+        return None
+    device = torch.device("cuda", local)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    torch.backends.cudnn.benchmark = True
+    state = ref.build(rank, world, args.comm_op, BATCH, device)
+    xs, ys = host_batches(rank)
+    out = {}
+
+    def it(i):
+        out["loss"], _ = ref.train_iteration(*state, xs[i % N_HOST_BATCHES], ys[i % N_HOST_BATCHES], it.n)
+        it.n += 1
+
+    it.n = 0
+    for i in range(max(args.warmup, 3)):
+        it(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(rank == 0, local)
+    ms = timed(it, args.steps, world)
+    clocks = sampler.stop()
+    return ms, ms, clocks, 0, out["loss"], BATCH * 3 * 32 * 32 * 4 + BATCH * 8, {}
+
+
+def main():
+    args = parse()
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
+        return
+    rank, world, local = init_dist(args.gpus)
+    if args.impl == "reference":
+        try:
+            res = run_reference(args, rank, world, local)
+        except Exception as e:  # the reference arm must never take the bench down
+            res = ("error", repr(e)[:300])
+        if res is None or res[0] == "error":
+            if rank == 0:
+                why = "reference not installed under baseline/_ref" if res is None else res[1]
+                print(json.dumps({"impl": "reference", "unavailable": why}))
+            return
+    else:
+        res = run_ours(args, rank, world, local)
+    dev_ms, e2e_ms, clocks, launches, last_loss, h2d, extra = res
+    if rank == 0:
+        imgs = BATCH * world * args.steps
+        line = {
+            "metric": "ResNet-20 CHOCO-ring images/s", "value": imgs / (dev_ms * 1e-3), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp32 (TF32 tensor-core convolutions, torch default)",
+            "data": "synthetic N(0,1) 32x32x3 images, uniform labels, random-init weights",
+            "impl": args.impl,
+            "config": {"model": "resnet20", "global_batch": BATCH * world, "seq_len": None,
+                       "parallelism": f"gossip-dp{world} ring", "optimizer": "CHOCO-SGD", "comm_op": args.comm_op,
+                       "compress_ratio": 0.99, "consensus_stepsize": 0.5, "nesterov": 0.9, "weight_decay": 1e-4,
+                       "l2": "per-step working set (activations + gradients, ~0.3 GB) exceeds the 126 MB L2",
+                       **extra},
+            "clocks": clocks,
+            "e2e": {"value": imgs / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches,
+            "last_loss": last_loss,
+        }
+        print(json.dumps(line))
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

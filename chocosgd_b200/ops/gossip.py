@@ -165,6 +165,7 @@ class ChocoEngine:
         if dev.type == "cuda":
             self.hyper_host = self.hyper_host.pin_memory()
         self.hyper_host[HYP_GSCALE] = 1.0
+        self.hyper.copy_(self.hyper_host)
         self._hyper_sent = None
         self.per_rank = {}
         blocks = []
@@ -266,18 +267,21 @@ class ChocoEngine:
         h[HYP_LR], h[HYP_MOMENTUM], h[HYP_GAMMA], h[HYP_NESTEROV] = key[0], key[1], key[2], 1.0 if key[3] else 0.0
         # slots 0..3 only: slot 4 (gradient scale) is written by the clipping kernel
         self.hyper[:4].copy_(h[:4], non_blocking=True)
-        if self._hyper_sent is None:
-            self.hyper[4:].copy_(h[4:], non_blocking=True)
         self._hyper_sent = key
 
     # ---- launches ---------------------------------------------------------------------------------
+    launches_per_step = 0
+    _n_launch = 0
+
     def _chk(self, code, what):
+        self._n_launch += 1
         _lib.check(code, what)
 
     def launch_step(self, stream=None):
         """All kernels of one CHOCO step on ``stream`` (default: current)."""
         L, pp, nc, nr = self.lib, self._pp, self.tables.n_chunks, self.n_local
         sp = _lib.stream_ptr(stream)
+        self._n_launch = 0
         if self.codec == 3:
             self._chk(L.choco_sign_step(pp, nc, nr, MODE_DECODE | MODE_PUSH, self.peers_hint, sp), "choco_sign_step")
         elif self.codec == 0:
@@ -294,6 +298,7 @@ class ChocoEngine:
             else:
                 self._chk(L.choco_randk_emit(pp, self.entry_blocks, nr, sp), "choco_randk_emit")
         self._steps += 1
+        self.launches_per_step = self._n_launch
 
     def _launch_sparse_decode(self, sp):
         L, pp, nr = self.lib, self._pp, self.n_local
@@ -319,6 +324,7 @@ class ChocoEngine:
                                     _lib.stream_ptr(stream)),
             "fused_sgd_step",
         )
+        self.launches_per_step = 1
 
     # ---- optimizer-facing API ----------------------------------------------------------------------
     def step(self, opt):

@@ -1,0 +1,115 @@
+"""Fused gossip kernels across real GPUs (one process per GPU, payloads pushed over NVLink
+into peer-mapped mailboxes) against the matrix-form simulator."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from dist_utils import free_port
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+class Tiny(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.fc1 = torch.nn.Linear(70, 50)
+        self.bn1 = torch.nn.BatchNorm1d(50)
+        self.fc2 = torch.nn.Linear(50, 30)
+
+
+def make_model():
+    torch.manual_seed(0)
+    return Tiny()
+
+
+def grad_flat(rank, step, seg):
+    g = torch.Generator().manual_seed(1000 * rank + step)
+    out = torch.zeros(seg.total)
+    for sl in seg.slices():
+        out[sl] = torch.randn(sl.stop - sl.start, generator=g)
+    return out
+
+
+def conf_for(comm_op, n):
+    from chocosgd_b200.config import get_args
+
+    argv = ["--optimizer", "parallel_choco_v", "--graph_topology", "ring", "--n_mpi_process", str(n), "--lr", "0.05",
+            "--momentum_factor", "0.9", "--use_nesterov", "True", "--weight_decay", "0.01",
+            "--consensus_stepsize", "0.4", "--gossip_impl", "fused", "--comm_op", comm_op, "--wait_budget_ms", "5000"]
+    if "compress" in comm_op:
+        argv += ["--compress_ratio", "0.9"]
+    if comm_op == "quantize_qsgd":
+        argv += ["--quantize_level", "4"]
+    return get_args(argv)
+
+
+def _worker(rank, world, port, comm_ops, steps, out):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from chocosgd_b200.optim import define_optimizer
+        from chocosgd_b200.parallel.topology import Graph
+
+        res = {}
+        for comm_op in comm_ops:
+            conf = conf_for(comm_op, world)
+            graph = Graph("ring", world, rank)
+            model = make_model().cuda()
+            opt = define_optimizer(conf, model, graph)
+            for t in range(steps):
+                opt.arena.g.copy_(grad_flat(rank, t, opt.seg))
+                opt.step()
+            opt.finalize()
+            torch.cuda.synchronize()
+            res[comm_op] = (opt.arena.x.cpu().numpy(), opt.x_hat.cpu().numpy(), opt.s.cpu().numpy())
+            dist.barrier()
+            opt.engine.close()
+        out[rank] = res
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_choco_over_nvlink_matches_simulator(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("not enough GPUs")
+    import torch.multiprocessing as mp
+
+    from chocosgd_b200.compress.reference import make_codec
+    from chocosgd_b200.optim.arena import FlatArena
+    from chocosgd_b200.parallel.topology import mixing_matrix
+    from chocosgd_b200.sim.matrix_form import Simulator
+
+    comm_ops = ["sign", "compress_top_k", "compress_random_k", "quantize_qsgd"]
+    steps = 6
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, comm_ops, steps, out)) for r in range(world)]
+    [p.start() for p in procs]
+    [p.join(600) for p in procs]
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    for comm_op in comm_ops:
+        conf = conf_for(comm_op, world)
+        arena = FlatArena(make_model().named_parameters())
+        seg = arena.seg
+        wd = [0.0 if "bn" in n else conf.weight_decay for n in seg.names]
+        codec = make_codec(seg, comm_op, conf.compress_ratio, conf.quantize_level, None, conf.is_biased, conf.random_k_seed)
+        sim = Simulator("choco", mixing_matrix("ring", world), arena.x.clone(), seg, codec, lr=conf.lr,
+                        consensus_stepsize=conf.consensus_stepsize, weight_decay=wd, momentum=0.9, nesterov=True)
+        for t in range(steps):
+            sim.step(lambda i, tt, x: grad_flat(i, tt, seg))
+        for r in range(world):
+            x, xh, s = out[r][comm_op]
+            if comm_op == "quantize_qsgd":
+                for a, b in ((x, sim.x[r].numpy()), (xh, sim.x_hat[r].numpy()), (s, sim.s[r].numpy())):
+                    assert (~np.isclose(a, b, rtol=1e-4, atol=1e-5)).mean() < 5e-3
+            else:
+                np.testing.assert_allclose(x, sim.x[r].numpy(), rtol=2e-5, atol=2e-6, err_msg=f"{comm_op} x rank {r}")
+                np.testing.assert_allclose(xh, sim.x_hat[r].numpy(), rtol=2e-5, atol=2e-6, err_msg=f"{comm_op} x_hat")
+                np.testing.assert_allclose(s, sim.s[r].numpy(), rtol=2e-5, atol=2e-6, err_msg=f"{comm_op} s")
