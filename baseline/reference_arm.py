@@ -15,7 +15,11 @@ Harness glue that is not reference code (each item is a documented deviation):
 * ``parallel_choco_v`` instead of ``parallel_choco`` (the latter hard-codes an MPI group);
 * ring needs n > 2 in the reference: n = 1, 2 use its ``complete`` graph, whose matrix
   equals the ring rule there ([1] and 1/2 everywhere);
-* ``track_time`` off (its timer synchronises the device around every scope).
+* ``track_time`` off (its timer synchronises the device around every scope);
+* unbatched NCCL ``isend`` + ``irecv`` on both ends of an edge block each other (observed
+  here: the 2-GPU run sat until the process-group timeout), so the module-level ``dist``
+  name of ``pcode.utils.communication`` is proxied to issue the same messages as one
+  ``batch_isend_irecv``; the reference source files are untouched.
 """
 from __future__ import annotations
 
@@ -51,25 +55,76 @@ def install_bit2byte_shim():
     sys.modules["bit2byte"] = b
 
 
+class _LazyReq:
+    def __init__(self, batch):
+        self.batch, self.req = batch, None
+
+    def wait(self):
+        self.batch.flush()
+        for r in self.req or ():
+            r.wait()
+
+
+class BatchedP2P:
+    """Stand-in for the ``dist`` name inside the reference's communication module.
+
+    The reference posts ``dist.isend`` then ``dist.irecv`` per neighbour
+    (``dl_code/pcode/utils/communication.py:259-262``).  With NCCL both ends of an edge
+    enqueue their send first and block each other.  This proxy forwards everything to
+    ``torch.distributed`` but queues those two calls and issues the SAME sends / receives
+    as one ``batch_isend_irecv`` when the first request is waited on."""
+
+    def __init__(self, real):
+        self._real, self._ops, self._reqs = real, [], []
+
+    def __getattr__(self, name):
+        return getattr(self._real, name)
+
+    def isend(self, tensor, dst, **kw):
+        return self._queue(self._real.isend, tensor, dst)
+
+    def irecv(self, tensor, src=None, **kw):
+        return self._queue(self._real.irecv, tensor, src)
+
+    def _queue(self, op, tensor, peer):
+        r = _LazyReq(self)
+        self._ops.append(self._real.P2POp(op, tensor, peer))
+        self._reqs.append(r)
+        return r
+
+    def flush(self):
+        if not self._ops:
+            return
+        ops, lazy = self._ops, self._reqs
+        self._ops, self._reqs = [], []
+        works = list(self._real.batch_isend_irecv(ops))  # NCCL returns one coalesced work
+        for l in lazy:
+            l.req = works
+
+
 def available():
     return os.path.isdir(os.path.join(REF, "pcode"))
 
 
-def build(rank, world, comm_op, batch_size, device):
+def build(rank, world, comm_op, batch_size, device, consensus_stepsize=0.5):
     if REF not in sys.path:
         sys.path.insert(0, REF)
     install_bit2byte_shim()
     import pcode.create_metrics as create_metrics
     import pcode.create_optimizer as create_optimizer
     import pcode.models as models
+    import pcode.utils.communication as communication
     import pcode.utils.topology as topology
     from pcode.utils.timer import Timer
+
+    if not isinstance(communication.dist, BatchedP2P):
+        communication.dist = BatchedP2P(dist)
 
     topo = "ring" if world > 2 else "complete"
     conf = argparse.Namespace(
         arch="resnet20", data="cifar10", optimizer="parallel_choco_v", comm_op=comm_op,
         compress_ratio=0.99, quantize_level=4, is_biased=True, backend="nccl", use_ipc=False,
-        consensus_stepsize=0.5, comm_device="cuda", weight_decay=1e-4, lr=0.1, momentum_factor=0.9,
+        consensus_stepsize=consensus_stepsize, comm_device="cuda", weight_decay=1e-4, lr=0.1, momentum_factor=0.9,
         use_nesterov=True, epoch_=0.5, local_index=0, distributed=True, graph_topology=topo,
         n_mpi_process=world, n_sub_process=1, on_cuda=True, batch_size=batch_size,
     )

@@ -24,6 +24,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 BATCH = 128
+# consensus step sizes inside the reference's tuning range [0.01, 0.5]; top-/random-1 % needs a small
+# one (chocosgd_b200.tools.tune_consensus_stepsize: 0.012 - 0.04 on rings of 2 - 8 nodes)
+GAMMA = {"compress_top_k": 0.02, "compress_random_k": 0.01, "sign": 0.45, "quantize_qsgd": 0.3}
 N_HOST_BATCHES = 16
 QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -99,7 +102,10 @@ def init_dist(n):
     if world > 1 or n > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+        import datetime
+
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local),
+                                timeout=datetime.timedelta(seconds=90))
     return rank, world, local
 
 
@@ -150,7 +156,7 @@ def run_ours(args, rank, world, local):
     device = torch.device("cuda", local)
     argv = ["--arch", "resnet20", "--data", "cifar10", "--optimizer", "parallel_choco_v", "--comm_op", args.comm_op,
             "--graph_topology", "ring", "--n_mpi_process", str(world), "--lr", "0.1", "--momentum_factor", "0.9",
-            "--use_nesterov", "True", "--weight_decay", "1e-4", "--consensus_stepsize", "0.5",
+            "--use_nesterov", "True", "--weight_decay", "1e-4", "--consensus_stepsize", str(GAMMA[args.comm_op]),
             "--batch_size", str(BATCH), "--gossip_impl", "fused"]
     if "compress" in args.comm_op:
         argv += ["--compress_ratio", "0.99"]
@@ -210,7 +216,7 @@ def run_reference(args, rank, world, local):
         os.environ.setdefault("MASTER_PORT", "29511")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
     torch.backends.cudnn.benchmark = True
-    state = ref.build(rank, world, args.comm_op, BATCH, device)
+    state = ref.build(rank, world, args.comm_op, BATCH, device, GAMMA[args.comm_op])
     xs, ys = host_batches(rank)
     out = {}
 
@@ -258,7 +264,7 @@ def main():
             "impl": args.impl,
             "config": {"model": "resnet20", "global_batch": BATCH * world, "seq_len": None,
                        "parallelism": f"gossip-dp{world} ring", "optimizer": "CHOCO-SGD", "comm_op": args.comm_op,
-                       "compress_ratio": 0.99, "consensus_stepsize": 0.5, "nesterov": 0.9, "weight_decay": 1e-4,
+                       "compress_ratio": 0.99, "consensus_stepsize": GAMMA[args.comm_op], "nesterov": 0.9, "weight_decay": 1e-4,
                        "l2": "per-step working set (activations + gradients, ~0.3 GB) exceeds the 126 MB L2",
                        **extra},
             "clocks": clocks,
