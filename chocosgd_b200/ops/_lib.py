@@ -125,6 +125,8 @@ def _declare(lib):
         "grad_clip_coef": [vp, i, i, f, vp, vp],
         "sign_pack": [vp, ll, vp, vp],
         "sign_unpack": [vp, ll, vp, f, vp],
+        "sign_l1_compress": [vp, ll, vp, vp, vp, vp],
+        "sign_l1_compress_noalloc": [vp, ll, vp, vp, vp],
         "symm_alloc": [POINTER(vp), ll],
         "symm_free": [vp],
         "symm_handle_size": [],
@@ -141,6 +143,8 @@ def _declare(lib):
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = i
+    lib.sign_l1_scratch_bytes.argtypes = [ll]
+    lib.sign_l1_scratch_bytes.restype = ll
     for name, args in {
         "cpu_sign_pack": [vp, ll, vp],
         "cpu_sign_unpack": [vp, ll, vp, f],

@@ -36,6 +36,20 @@ def sign_unpack(words: torch.Tensor, n: int, scale: float = 1.0) -> torch.Tensor
     return out
 
 
+def sign_l1_compress(x: torch.Tensor):
+    """Sign words and L1 norm of one CUDA fp32 tensor in a single kernel: ``(int32 words, 0-d norm)``."""
+    x = x.contiguous().view(-1)
+    assert x.is_cuda and x.dtype == torch.float32
+    n = x.numel()
+    lib = _lib.load()
+    words = torch.empty((n + 31) // 32, dtype=torch.int32, device=x.device)
+    norm = torch.empty(1, dtype=torch.float32, device=x.device)
+    scratch = torch.empty(lib.sign_l1_scratch_bytes(n) // 4, dtype=torch.int32, device=x.device)
+    _lib.check(lib.sign_l1_compress(_lib.ptr(x), n, _lib.ptr(words), _lib.ptr(norm), _lib.ptr(scratch),
+                                    _lib.stream_ptr()), "sign_l1_compress")
+    return words, norm[0]
+
+
 def cpu_top_k(x: torch.Tensor, k: int):
     x = x.contiguous().view(-1).to(torch.float32).cpu()
     idx = torch.empty(k, dtype=torch.int32)
