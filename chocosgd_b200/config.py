@@ -255,6 +255,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--synthetic_size", default=None, type=int,
                    help="number of samples of the synthetic dataset (data=synthetic_*)")
     p.add_argument("--use_cuda_graph", default=True, type=str2bool)
+    p.add_argument("--channels_last", default=True, type=str2bool,
+                   help="keep 4-d activations and convolution weights in NHWC / KRSC memory order on CUDA")
     p.add_argument("--overlap_gossip", default=True, type=str2bool)
     p.add_argument("--qsgd_levels", default=None, type=int,
                    help="explicit number of QSGD levels s (convex-code spelling); "

@@ -1,6 +1,8 @@
 """Model zoo and the ``define_model`` factory (``dl_code/pcode/create_model.py:8-102``)."""
 from __future__ import annotations
 
+import torch
+
 from .densenet import DenseNet, densenet
 from .lenet import LeNet, lenet
 from .mlp import MLP, mlp
@@ -57,6 +59,8 @@ def define_model(conf, graph=None, data_loader=None, device=None, consistent=Tru
         model = define_cv_model(conf)
     if device is not None:
         model = model.to(device)
+        if getattr(conf, "channels_last", False) and str(device).startswith("cuda") and "rnn_lm" not in conf.arch:
+            model = model.to(memory_format=torch.channels_last)
     if consistent:
         consistent_model(model, on_cuda=device is not None and str(device).startswith("cuda"))
     if verbose:

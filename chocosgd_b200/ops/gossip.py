@@ -250,7 +250,7 @@ class ChocoEngine:
         else:
             assert len(grads) == self.seg.n_segments
             for gt, n in zip(grads, self.seg.sizes):
-                assert gt.is_contiguous() and gt.dtype == torch.float32 and gt.numel() == n
+                assert gt.dtype == torch.float32 and gt.numel() == n
                 assert gt.data_ptr() % 16 == 0
             table = torch.tensor([gt.data_ptr() for gt in grads], dtype=torch.int64).to(self.device)
             self._grad_tables[rank] = (table, list(grads))

@@ -27,15 +27,29 @@ class FlatArena:
         self.seg = Segments.from_sizes([p.numel() for p in self.params], self.names)
         self.x = torch.zeros(self.seg.total, dtype=torch.float32, device=self.device)
         self.g = torch.zeros(self.seg.total, dtype=torch.float32, device=self.device)
-        for p, sl in zip(self.params, self.seg.slices()):
-            self.x[sl].copy_(p.data.reshape(-1).to(torch.float32))
+        # 4-d tensors that arrive in channels_last (NHWC / KRSC) format keep that memory order
+        # inside their segment: the flat slice is viewed [K, R, S, C] and permuted back to the
+        # logical [K, C, R, S] shape, so state_dict() values and shapes are unchanged.
+        self.channels_last = [
+            p.dim() == 4 and p.is_contiguous(memory_format=torch.channels_last) and not p.is_contiguous()
+            for p in self.params
+        ]
+        for p, sl, cl in zip(self.params, self.seg.slices(), self.channels_last):
+            self._view(self.x[sl], p.shape, cl).copy_(p.data.to(torch.float32))
         self.rebind()
+
+    @staticmethod
+    def _view(flat, shape, channels_last):
+        if not channels_last:
+            return flat.view(shape)
+        k, c, r, s = shape
+        return flat.view(k, r, s, c).permute(0, 3, 1, 2)
 
     def rebind(self):
         """(Re-)point ``p.data`` / ``p.grad`` at the flat buffers."""
-        for p, sl in zip(self.params, self.seg.slices()):
-            p.data = self.x[sl].view(p.shape)
-            p.grad = self.g[sl].view(p.shape)
+        for p, sl, cl in zip(self.params, self.seg.slices(), self.channels_last):
+            p.data = self._view(self.x[sl], p.shape, cl)
+            p.grad = self._view(self.g[sl], p.shape, cl)
 
     def adopt_x(self, new_x: torch.Tensor):
         """Replace the parameter storage (e.g. by a peer-mapped allocation)."""

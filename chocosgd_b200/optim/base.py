@@ -154,9 +154,9 @@ class DistributedOptimizer(Optimizer):
         state = {}
         if self.momentum_buf is not None:
             for i, sl in enumerate(self.seg.slices()):
-                state[i] = {
-                    "momentum_buffer": self.momentum_buf[sl].detach().clone().view(self.param_groups[i]["param_size"])
-                }
+                view = self.arena._view(self.momentum_buf[sl], self.param_groups[i]["param_size"],
+                                        self.arena.channels_last[i])
+                state[i] = {"momentum_buffer": view.detach().clone()}
         algo = {k: (v.detach().clone() if torch.is_tensor(v) else v) for k, v in self.algo_state().items()}
         algo["local_index"] = self.local_index
         return {"state": state, "param_groups": groups, "algo_state": algo}
@@ -173,7 +173,8 @@ class DistributedOptimizer(Optimizer):
             for i, sl in enumerate(self.seg.slices()):
                 ent = st.get(i, st.get(str(i)))
                 if ent is not None and "momentum_buffer" in ent:
-                    self.momentum_buf[sl].copy_(ent["momentum_buffer"].reshape(-1))
+                    self.arena._view(self.momentum_buf[sl], self.param_groups[i]["param_size"],
+                                     self.arena.channels_last[i]).copy_(ent["momentum_buffer"])
         algo = dict(sd.get("algo_state", {}))
         self.local_index = int(algo.pop("local_index", 0))
         self.load_algo_state(algo)

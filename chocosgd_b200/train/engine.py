@@ -39,12 +39,14 @@ class TrainStep:
         hidden=None,
         amp_dtype: Optional[torch.dtype] = None,
         warmup_iters: int = 3,
-        channels_last: bool = False,
+        channels_last: Optional[bool] = None,
     ):
         self.model, self.criterion, self.opt, self.metrics = model, criterion, optimizer, metrics
         self.device = optimizer.device
         self.clip = clip_grad_norm
         self.amp_dtype = amp_dtype
+        if channels_last is None:
+            channels_last = any(optimizer.arena.channels_last)
         self.channels_last = channels_last
         self.is_cuda = self.device.type == "cuda"
         self.fused = bool(getattr(optimizer, "capturable", False))
@@ -137,8 +139,9 @@ class TrainStep:
 
     def _fill_table(self, table):
         grads = [p.grad for p in self.opt.arena.params]
-        for gt in grads:
-            assert gt is not None and gt.is_contiguous() and gt.data_ptr() % 16 == 0
+        for gt, p in zip(grads, self.opt.arena.params):
+            # same memory order as the parameter's segment (dense, same strides)
+            assert gt is not None and gt.stride() == p.stride() and gt.data_ptr() % 16 == 0
         host = torch.tensor([gt.data_ptr() for gt in grads], dtype=torch.int64)
         table.copy_(host)
         self._table_keepalive = grads

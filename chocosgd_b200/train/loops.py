@@ -1,0 +1,214 @@
+"""Training / validation loops for vision and language models.
+
+Skeleton of ``dl_code/pcode/distributed_running_cv.py:23-258`` and
+``dl_code/pcode/distributed_running_nlp.py:23-242``: barrier per epoch, per batch
+``scheduler.step`` -> load batch -> forward / backward -> ``optimizer.step`` -> train record;
+at integer epochs divergence guard, validation (local model, and the world-averaged model
+with the L2 distance when ``--evaluate_consensus`` on a non-complete graph), checkpoint,
+optional consensus evaluation on the full training set, stop check; optional reshuffle.
+
+The hot path differs on purpose: one ``TrainStep`` call per batch (CUDA-graph replay with
+the fused optimizers), loss / accuracy stay on the device and are read back in bulk every
+``summary_freq`` steps instead of three ``.item()`` syncs per step."""
+from __future__ import annotations
+
+import copy
+import gc
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..data import define_dataset, load_data_batch
+from ..utils import checkpoint as ckpt
+from ..utils.auxiliary import get_model_difference
+from ..utils.error_handler import TrainingDiverged
+from ..utils.logging import display_best_test_stat, display_test_stat, display_training_stat
+from ..utils.stat_tracker import RuntimeTracker
+from .engine import TrainStep
+
+
+def _barrier():
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+
+
+class _PendingRecords:
+    """Per-step training records whose numbers are still on the device."""
+
+    def __init__(self):
+        self.meta, self.vals = [], []
+
+    def add(self, meta, loss, perf):
+        self.meta.append(meta)
+        self.vals.append(torch.cat([loss.reshape(1), perf.reshape(-1)]).clone())
+
+    def flush(self, logger, graph, tracker, names, display_every):
+        if not self.meta:
+            return
+        vals = torch.stack(self.vals).cpu()
+        for i, (meta, row) in enumerate(zip(self.meta, vals)):
+            tracker.update_metrics([float(v) for v in row], n_samples=meta["n"])
+            sch = meta["sched"]
+            display_training_stat(logger, graph, sch, tracker, meta["bits"],
+                                  display=(i == len(self.meta) - 1) or display_every)
+        self.meta, self.vals = [], []
+
+
+class _SchedView:
+    def __init__(self, s):
+        self.epoch_, self.local_index = s.epoch_, s.local_index
+
+
+def inference(model, criterion, metrics, _input, _target, tracker=None, hidden=None):
+    if hidden is not None:
+        output, hidden = model(_input, hidden)
+        loss = criterion(output.reshape(-1, output.size(-1)), _target.reshape(-1))
+        perf = metrics.evaluate(loss, output.reshape(-1, output.size(-1)), _target.reshape(-1))
+    else:
+        output = model(_input)
+        loss = criterion(output, _target)
+        perf = metrics.evaluate(loss, output, _target)
+    if tracker is not None:
+        tracker.update_metrics([loss.detach()] + [p for p in perf], n_samples=_input.size(0))
+    return loss, hidden
+
+
+def validate(conf, graph, run, model, optimizer, criterion, scheduler, metrics, data_loader, label="local_model",
+             force_evaluate_on_averaged_model=True, device=None, rank_slice=None):
+    is_nlp = "rnn_lm" in conf.arch
+
+    def _evaluate(_model, label):
+        tracker = RuntimeTracker(metrics.metric_names, on_cuda=graph.on_cuda, world_aggregator=optimizer.world_aggregator)
+        _model.eval()
+        hidden = _model.init_hidden(conf.batch_size) if is_nlp else None
+        with torch.no_grad():
+            for _input, _target in data_loader["val_loader"]:
+                if is_nlp:
+                    _input, _target = _input[:, rank_slice], _target[:, rank_slice]
+                    if _input.size(1) != conf.batch_size:
+                        continue
+                _input, _target = load_data_batch(device, _input, _target)
+                _, hidden = inference(_model, criterion, metrics, _input, _target, tracker, hidden)
+                if is_nlp:
+                    hidden = _model.repackage_hidden(hidden)
+        display_test_stat(run.logger, graph, scheduler, tracker, label)
+        return tracker.evaluate_global_metrics()
+
+    if (conf.graph_topology != "complete" and not conf.train_fast and conf.evaluate_consensus
+            and force_evaluate_on_averaged_model):
+        copied = copy.deepcopy(model)
+        optimizer.world_aggregator.agg_model(copied, op="avg")
+        _evaluate(copied, label="averaged_model")
+        run.logger.log_metric(
+            name="stat",
+            values={"rank": graph.rank, "epoch": scheduler.epoch_, "distance": get_model_difference(model, copied)},
+            tags={"split": "test", "type": "averaged_model"},
+        )
+    return _evaluate(model, label=label)
+
+
+def do_validate(conf, graph, run, model, optimizer, criterion, scheduler, metrics, data_loader, device, rank_slice=None):
+    print("Enter validation phase.")
+    optimizer.finalize()
+    performance = validate(conf, graph, run, model, optimizer, criterion, scheduler, metrics, data_loader,
+                           device=device, rank_slice=rank_slice)
+    perf0 = performance[0]
+    scheduler.best_tracker.update(perf0, scheduler.epoch_)
+    display_best_test_stat(run.logger, graph, scheduler)
+    if not conf.train_fast:
+        ckpt.save_to_checkpoint(
+            run,
+            {
+                "arch": conf.arch,
+                "current_epoch": scheduler.epoch,
+                "local_index": scheduler.local_index,
+                "best_perf": scheduler.best_tracker.best_perf,
+                "optimizer": optimizer.state_dict(),
+                "state_dict": model.state_dict(),
+            },
+            scheduler.best_tracker.is_best,
+            dirname=run.checkpoint_dir,
+            filename="checkpoint.pth.tar",
+            save_all=conf.save_all_models,
+        )
+    print("Finished validation.")
+    return performance
+
+
+def train_and_validate(conf, graph, run, model, criterion, scheduler, optimizer, metrics, data_loader, device=None):
+    """Run training until the stop criterion; returns the scheduler (with best_tracker)."""
+    is_nlp = "rnn_lm" in conf.arch
+    logger, timer = run.logger, run.timer
+    tracker_tr = RuntimeTracker(metrics.metric_names, on_cuda=graph.on_cuda, world_aggregator=optimizer.world_aggregator)
+    pending = _PendingRecords()
+    rank_slice = slice(graph.rank * conf.batch_size, (graph.rank + 1) * conf.batch_size) if is_nlp else None
+    step_fn, hidden = None, None
+    print("=> enter the training.\n")
+    while True:
+        _barrier()
+        for _input, _target in data_loader["train_loader"]:
+            model.train()
+            scheduler.step(optimizer)
+            with timer("load_data", epoch=scheduler.epoch_):
+                if is_nlp:
+                    _input, _target = _input[:, rank_slice], _target[:, rank_slice]
+                    if _input.size(0) != conf.rnn_bptt_len or _input.size(1) != conf.batch_size:
+                        continue  # ragged tail window
+                if step_fn is None or tuple(step_fn.static_input.shape) != tuple(_input.shape):
+                    if is_nlp:
+                        hidden = tuple(h.to(optimizer.device) for h in model.init_hidden(conf.batch_size))
+                    step_fn = TrainStep(
+                        model, criterion, optimizer, _input, _target, metrics=metrics,
+                        use_cuda_graph=conf.use_cuda_graph and _input.size(0) == (conf.rnn_bptt_len if is_nlp else conf.batch_size),
+                        clip_grad_norm=conf.rnn_clip if is_nlp else None, hidden=hidden,
+                        amp_dtype=torch.bfloat16 if conf.dtype == "bf16" else None,
+                    )
+            with timer("forward_pass", epoch=scheduler.epoch_):
+                loss = step_fn(_input, _target, timer=timer, scheduler=scheduler)
+            n_bits = optimizer.n_bits
+            pending.add({"n": _input.size(1) if is_nlp else _input.size(0), "bits": n_bits, "sched": _SchedView(scheduler)},
+                        loss, step_fn.perf)
+            if scheduler.local_index % conf.summary_freq == 0 or scheduler.epoch_ % 1 == 0 or scheduler.is_stop():
+                pending.flush(logger, graph, tracker_tr, metrics.metric_names, False)
+                if getattr(optimizer, "engine", None) is not None:
+                    optimizer.engine.check()
+            if scheduler.epoch_ % 1 == 0 or scheduler.is_stop():
+                avg = tracker_tr.stat["loss"].avg
+                if avg > 1e3 or math.isnan(avg):
+                    logger.save_json()
+                    raise TrainingDiverged(f"loss average {avg} at epoch {scheduler.epoch_}")
+                do_validate(conf, graph, run, model, optimizer, criterion, scheduler, metrics, data_loader, device,
+                            rank_slice)
+                tracker_tr.reset()
+                if (conf.evaluate_consensus or scheduler.is_stop()) and not conf.train_fast and not is_nlp:
+                    consensus_evaluation(conf, graph, run, model, optimizer, criterion, scheduler, metrics, device)
+                if scheduler.is_stop():
+                    logger.save_json()
+                    optimizer.finalize()
+                    return scheduler
+            if graph.rank == 0 and conf.display_tracked_time and scheduler.local_index % conf.summary_freq == 0:
+                print(timer.summary())
+        if conf.reshuffle_per_epoch:
+            print("\nReshuffle the dataset.")
+            del data_loader
+            gc.collect()
+            data_loader = define_dataset(conf, graph, run, device=device)
+
+
+def consensus_evaluation(conf, graph, run, model, optimizer, criterion, scheduler, metrics, device):
+    """Evaluate the local and the world-averaged model on the whole (unpartitioned) training set
+    (``dl_code/pcode/distributed_running_cv.py:81-126``)."""
+    full = conf.replace(partition_data=None)
+    from ..config import RunState
+
+    loaders = define_dataset(full, graph, RunState())
+    dl = {"val_loader": loaders["train_loader"]}
+    run.logger.log("eval the local model on full training data.")
+    validate(conf, graph, run, model, optimizer, criterion, scheduler, metrics, dl,
+             label="eval_local_model_on_full_training_data", force_evaluate_on_averaged_model=False, device=device)
+    run.logger.log("eval the averaged model on full training data.")
+    copied = copy.deepcopy(model)
+    optimizer.world_aggregator.agg_model(copied, op="avg")
+    validate(conf, graph, run, copied, optimizer, criterion, scheduler, metrics, dl,
+             label="eval_averaged_model_on_full_training_data", force_evaluate_on_averaged_model=False, device=device)
