@@ -1,0 +1,334 @@
+// TF32 GEMM on the 5th-generation tensor cores (sm_100a):  D[M,N] (+)= A . B^T (+ bias)
+//
+//   * operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle,
+//     no cluster multicast), 4-stage ring guarded by mbarriers;
+//   * one elected thread issues tcgen05.mma (cta_group::1, kind::tf32, M = 128, N = BN);
+//     the fp32 accumulator lives in tensor memory (TMEM), allocated by warp 0;
+//   * tcgen05.commit releases smem stages and finally signals the epilogue, which reads the
+//     accumulator with tcgen05.ld (warp w owns TMEM lanes 32w .. 32w+31 = output rows);
+//   * either operand may be K-major ([rows, K], K contiguous) or MN-major ([K, rows], rows
+//     contiguous), so forward (x W^T), input-gradient (dY W) and weight-gradient (dY^T x)
+//     GEMMs of a linear layer run without any transpose pass;
+//   * split-K (gridDim.z) with fp32 atomic accumulation for reductions over a long K with a
+//     small output (weight gradients).
+//
+// Every mbarrier wait is bounded: on expiry the CTA records an error code, skips to the
+// teardown (TMEM is always freed) and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define GEMM_BM 128
+#define GEMM_BK 32          // tf32 elements per k-block = 128 bytes = one swizzle row
+#define GEMM_STAGES 4
+#define GEMM_THREADS 192    // warps 0-3: epilogue (warp 0 also owns TMEM), warp 4: TMA, warp 5: MMA
+#define SPIN_LIMIT (1u << 22)
+
+#define GEMM_ERR_TIMEOUT 1
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// bounded parity wait; returns false when the limit is reached
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+    if (i > 1024) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// shared-memory matrix descriptor (sm100 format, 128-byte swizzle)
+// layout_type: 2 = 128-byte swizzle (16-byte units), 1 = 128-byte swizzle with 32-byte units, the
+// only layout the tensor core accepts for MN-major 32-bit operands
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type = 2) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmArgs {
+  float* d;            // [M, N] row-major, ldd elements per row
+  const float* bias;   // [N] or null
+  int* error;          // device word, set non-zero on a timed-out wait
+  int M, N, K, ldd;
+  int k_blocks_per_split;
+  int relu;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int A_BYTES = GEMM_BM * GEMM_BK * 4;  // 16 KiB
+  constexpr int B_BYTES = BN * GEMM_BK * 4;
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + GEMM_STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sB + GEMM_STAGES * B_BYTES);
+  uint64_t* empty = full + GEMM_STAGES;
+  uint64_t* acc_ready = empty + GEMM_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * GEMM_BM, n0 = blockIdx.y * BN;
+  const int total_kb = (g.K + GEMM_BK - 1) / GEMM_BK;
+  const int kb_begin = blockIdx.z * g.k_blocks_per_split;
+  int kb_end = kb_begin + g.k_blocks_per_split;
+  if (kb_end > total_kb) kb_end = total_kb;
+  const int n_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GEMM_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_ready, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (n_kb > 0) {
+    if (warp == 4 && lane == 0) {
+      // ---------------- TMA producer ----------------
+      for (int i = 0; i < n_kb; ++i) {
+        const int s = i % GEMM_STAGES;
+        if (i >= GEMM_STAGES && !mbar_wait(empty + s, ((i / GEMM_STAGES) - 1) & 1)) { *abort_flag = 1; break; }
+        if (*abort_flag) break;
+        const int k0 = (kb_begin + i) * GEMM_BK;
+        mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+        if (!A_MN) {
+          tma_load_2d(sA + s * A_BYTES, &map_a, full + s, k0, m0);
+        } else {
+          for (int j = 0; j < GEMM_BM / 32; ++j)
+            tma_load_2d(sA + s * A_BYTES + j * 4096, &map_a, full + s, m0 + 32 * j, k0);
+        }
+        if (!B_MN) {
+          tma_load_2d(sB + s * B_BYTES, &map_b, full + s, k0, n0);
+        } else {
+          for (int j = 0; j < BN / 32; ++j)
+            tma_load_2d(sB + s * B_BYTES + j * 4096, &map_b, full + s, n0 + 32 * j, k0);
+        }
+      }
+    } else if (warp == 5 && lane == 0) {
+      // ---------------- MMA issuer ----------------
+      // instruction descriptor: fp32 accumulate, tf32 x tf32, majorness bits, N >> 3, M >> 4
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GEMM_BM >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; ++i) {
+        const int s = i % GEMM_STAGES;
+        if (!mbar_wait(full + s, (i / GEMM_STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+        for (int k = 0; k < GEMM_BK / 8; ++k) {
+          // K-major: 32 bytes further inside the 128-byte row; MN-major: next 8 k-rows (two
+          // 4-row atoms, 512 bytes apart; 32-element MN blocks are 4096 bytes apart)
+          const uint64_t da = A_MN ? make_desc(a_addr + k * 1024, 4096, 512, 1) : make_desc(a_addr + k * 32, 16, 1024);
+          const uint64_t db = B_MN ? make_desc(b_addr + k * 1024, 4096, 512, 1) : make_desc(b_addr + k * 32, 16, 1024);
+          umma_tf32(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(empty + s);  // frees this stage once the MMAs above have read it
+      }
+      if (ok) tc_commit(acc_ready);
+    } else if (warp < 4) {
+      // ---------------- epilogue: TMEM -> registers -> global ----------------
+      bool ok = mbar_wait(acc_ready, 0);
+      if (!ok) *abort_flag = 1;
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        const int row = m0 + warp * 32 + lane;
+        const bool split = gridDim.z > 1;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          uint32_t r[16];
+          tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c, r);
+          if (row < g.M) {
+            float* out = g.d + (size_t)row * g.ldd + n0 + c;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int col = n0 + c + j;
+              if (col < g.N) {
+                float v = __uint_as_float(r[j]);
+                if (g.bias != nullptr && blockIdx.z == 0) v += g.bias[col];
+                if (split) atomicAdd(out + j, v);
+                else out[j] = g.relu ? fmaxf(v, 0.f) : v;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(g.error, GEMM_ERR_TIMEOUT);
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------- host side ----------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-d fp32 tensor map: inner (contiguous) extent `inner`, `outer` rows of `row_stride` elements
+static int make_map_2d(CUtensorMap* map, const void* base, long long inner, long long outer, long long row_stride,
+                       int box_inner, int box_outer, bool mn_major) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return -10;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_stride * 4) % 16 != 0) return -11;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)row_stride * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+static int* g_gemm_error[64];
+
+static int* gemm_error_word() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (g_gemm_error[dev] == nullptr) {
+    if (cudaMalloc(&g_gemm_error[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(g_gemm_error[dev], 0, sizeof(int));
+  }
+  return g_gemm_error[dev];
+}
+
+extern "C" int gemm_tf32_last_error() {
+  int* w = gemm_error_word();
+  int v = -1;
+  if (w != nullptr) cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int splits, cudaStream_t st) {
+  constexpr int smem = GEMM_STAGES * (GEMM_BM * GEMM_BK * 4 + BN * GEMM_BK * 4) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((g.M + GEMM_BM - 1) / GEMM_BM, (g.N + BN - 1) / BN, splits);
+  gemm_tf32_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, g);
+  return (int)cudaGetLastError();
+}
+
+template <int BN>
+static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
+                          int splits, cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_gemm<BN, false, false>(ma, mb, g, splits, st);
+  if (!a_mn && b_mn) return launch_gemm<BN, false, true>(ma, mb, g, splits, st);
+  if (a_mn && !b_mn) return launch_gemm<BN, true, false>(ma, mb, g, splits, st);
+  return launch_gemm<BN, true, true>(ma, mb, g, splits, st);
+}
+
+// D[M,N] = A . B^T (+ bias).  a_mn = 0: A is [M, K] (K contiguous, lda);  a_mn = 1: A is [K, M].
+// Same for B with N rows.  split_k > 1 accumulates with atomics into D, which the caller zeroed.
+extern "C" int gemm_tf32(const void* a, const void* b, void* d, const void* bias, int M, int N, int K, int lda, int ldb,
+                         int ldd, int a_mn, int b_mn, int split_k, int relu, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const int BN = N <= 32 ? 32 : (N <= 64 ? 64 : 128);
+  CUtensorMap ma, mb;
+  int rc = a_mn ? make_map_2d(&ma, a, M, K, lda, 32, GEMM_BK, true)
+                : make_map_2d(&ma, a, K, M, lda, GEMM_BK, GEMM_BM, false);
+  if (rc) return rc;
+  rc = b_mn ? make_map_2d(&mb, b, N, K, ldb, 32, GEMM_BK, true) : make_map_2d(&mb, b, K, N, ldb, GEMM_BK, BN, false);
+  if (rc) return rc;
+  GemmArgs g;
+  g.d = reinterpret_cast<float*>(d);
+  g.bias = reinterpret_cast<const float*>(bias);
+  g.error = gemm_error_word();
+  if (g.error == nullptr) return -13;
+  g.M = M; g.N = N; g.K = K; g.ldd = ldd; g.relu = relu;
+  const int total_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  int splits = split_k < 1 ? 1 : split_k;
+  if (splits > total_kb) splits = total_kb;
+  g.k_blocks_per_split = (total_kb + splits - 1) / splits;
+  splits = (total_kb + g.k_blocks_per_split - 1) / g.k_blocks_per_split;
+  if (BN == 32) return dispatch_major<32>(a_mn, b_mn, ma, mb, g, splits, stream);
+  if (BN == 64) return dispatch_major<64>(a_mn, b_mn, ma, mb, g, splits, stream);
+  return dispatch_major<128>(a_mn, b_mn, ma, mb, g, splits, stream);
+}
