@@ -166,8 +166,8 @@ def run_ours(args, rank, world, local):
     graph = Graph("ring", world, rank)
     torch.manual_seed(6)
     torch.backends.cudnn.benchmark = True
-    if args.native_layers == "on":
-        native_nn.set_native(True)
+    if args.native_layers != "off":
+        native_nn.set_native(True, which=native_nn.available_kinds())
     model = define_model(conf, graph, device=device, verbose=False)
     optimizer = define_optimizer(conf, model, graph)
     metrics = Metrics(model)

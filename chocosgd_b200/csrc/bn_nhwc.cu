@@ -1,0 +1,242 @@
+// Training-mode BatchNorm fused with the residual add and ReLU around it, NHWC fp32.
+//
+//   forward :  y = relu( (x - mean_c) * invstd_c * gamma_c + beta_c  [+ residual] )
+//   backward:  g = dy * [y > 0] ;  dbeta = sum g ;  dgamma = sum g * xhat ;
+//              dx = gamma invstd (g - dbeta / P - xhat dgamma / P) ;  dresidual = g
+//
+// Each direction is two kernels: a per-channel reduction over all P = N*H*W pixels (per-CTA
+// partials, the last CTA to arrive adds them in a fixed order in double precision and, in the
+// forward, updates the running statistics) and one elementwise pass.  That replaces the
+// library batch-norm kernel plus separate add / ReLU / ReLU-backward / add-backward kernels
+// (dl_code/pcode/models/resnet.py:37-56: conv -> bn -> relu, conv -> bn -> += residual -> relu).
+//
+// Layout: x is [P, C] with C contiguous, C a multiple of 4, C/4 a power of two <= 256.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define BN_THREADS 256
+
+struct BnArgs {
+  const float* x;        // [P, C]
+  const float* dy;       // backward: upstream gradient
+  const float* y;        // backward: forward output (ReLU mask)
+  const float* residual; // forward: optional
+  const float* gamma;
+  const float* beta;
+  float* out;            // forward: y ; backward: dx
+  float* out2;           // backward: dresidual (optional)
+  float* mean;           // [C] batch mean (saved)
+  float* invstd;         // [C] 1/sqrt(var + eps) (saved)
+  float* running_mean;   // optional
+  float* running_var;    // optional
+  float* dgamma;         // [C]
+  float* dbeta;          // [C]
+  float* partial;        // [grid][2 C] scratch
+  unsigned* counter;     // arrival counter (self-resetting)
+  int P, C, relu;
+  float eps, momentum;
+};
+
+// per-channel sums of (a, b) over this CTA's rows -> partial; last CTA finalises
+template <bool BACKWARD>
+__global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnArgs a) {
+  __shared__ float sh[BN_THREADS * 8];
+  __shared__ int last;
+  const int C = a.C, tpr = C >> 2;            // threads per row
+  const int rpb = BN_THREADS / tpr;            // rows per pass
+  const int col = (threadIdx.x % tpr) * 4, rsub = threadIdx.x / tpr;
+  const int rows_per_cta = (a.P + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int r1 = min(a.P, r0 + rows_per_cta);
+  float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+  float mu[4] = {0.f, 0.f, 0.f, 0.f}, is[4] = {1.f, 1.f, 1.f, 1.f};
+  if (BACKWARD) {
+    const float4 m = *reinterpret_cast<const float4*>(a.mean + col);
+    const float4 v = *reinterpret_cast<const float4*>(a.invstd + col);
+    mu[0] = m.x; mu[1] = m.y; mu[2] = m.z; mu[3] = m.w;
+    is[0] = v.x; is[1] = v.y; is[2] = v.z; is[3] = v.w;
+  }
+  for (int r = r0 + rsub; r < r1; r += rpb) {
+    const size_t off = (size_t)r * C + col;
+    const float4 xv = *reinterpret_cast<const float4*>(a.x + off);
+    const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
+    if (!BACKWARD) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s0[e] += xa[e];
+        s1[e] = fmaf(xa[e], xa[e], s1[e]);
+      }
+    } else {
+      const float4 gv = *reinterpret_cast<const float4*>(a.dy + off);
+      float ga[4] = {gv.x, gv.y, gv.z, gv.w};
+      if (a.relu) {
+        const float4 yv = *reinterpret_cast<const float4*>(a.y + off);
+        const float ya[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ga[e] = ya[e] > 0.f ? ga[e] : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s0[e] += ga[e];
+        s1[e] = fmaf(ga[e], (xa[e] - mu[e]) * is[e], s1[e]);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    sh[threadIdx.x * 8 + e] = s0[e];
+    sh[threadIdx.x * 8 + 4 + e] = s1[e];
+  }
+  __syncthreads();
+  if (threadIdx.x < tpr) {
+    float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < rpb; ++j) {
+      const float* p = sh + (j * tpr + threadIdx.x) * 8;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        t0[e] += p[e];
+        t1[e] += p[4 + e];
+      }
+    }
+    float* dst = a.partial + (size_t)blockIdx.x * 2 * C;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      dst[col + e] = t0[e];
+      dst[C + col + e] = t1[e];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    last = (atomicAdd(a.counter, 1u) == gridDim.x - 1);
+    if (last) __threadfence();
+  }
+  __syncthreads();
+  if (!last) return;
+  // final reduction over the CTAs' partials: BN_THREADS / C threads per channel, each adds a
+  // strided subset in a fixed order, then the subsets are added in a fixed order (reproducible)
+  double* shd = reinterpret_cast<double*>(sh);  // 2 * BN_THREADS doubles = 4 KiB
+  for (int cbase = 0; cbase < C; cbase += BN_THREADS) {
+    const int cw = min(C - cbase, BN_THREADS);   // channels in this pass
+    const int nsub = BN_THREADS / cw;
+    const int c = cbase + threadIdx.x % cw, sub = threadIdx.x / cw;
+    double t0 = 0.0, t1 = 0.0;
+    if (sub < nsub)
+      for (unsigned b = sub; b < gridDim.x; b += nsub) {
+        t0 += (double)__ldcg(a.partial + (size_t)b * 2 * C + c);
+        t1 += (double)__ldcg(a.partial + (size_t)b * 2 * C + C + c);
+      }
+    __syncthreads();
+    shd[threadIdx.x * 2] = t0;
+    shd[threadIdx.x * 2 + 1] = t1;
+    __syncthreads();
+    if (threadIdx.x < cw) {
+      t0 = 0.0; t1 = 0.0;
+      for (int j = 0; j < nsub; ++j) {
+        t0 += shd[(j * cw + threadIdx.x) * 2];
+        t1 += shd[(j * cw + threadIdx.x) * 2 + 1];
+      }
+      if (!BACKWARD) {
+        const double mean = t0 / a.P;
+        double var = t1 / a.P - mean * mean;
+        if (var < 0.0) var = 0.0;
+        a.mean[c] = (float)mean;
+        a.invstd[c] = (float)(1.0 / sqrt(var + (double)a.eps));
+        if (a.running_mean != nullptr) {
+          const double unbiased = a.P > 1 ? var * a.P / (a.P - 1) : var;
+          a.running_mean[c] = (1.f - a.momentum) * a.running_mean[c] + a.momentum * (float)mean;
+          a.running_var[c] = (1.f - a.momentum) * a.running_var[c] + a.momentum * (float)unbiased;
+        }
+      } else {
+        a.dbeta[c] = (float)t0;
+        a.dgamma[c] = (float)t1;
+      }
+    }
+  }
+  if (threadIdx.x == 0) *a.counter = 0;
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_fwd_apply_kernel(BnArgs a) {
+  const size_t n4 = (size_t)a.P * a.C / 4;
+  const int c4 = a.C >> 2;
+  for (size_t i = (size_t)blockIdx.x * BN_THREADS + threadIdx.x; i < n4; i += (size_t)gridDim.x * BN_THREADS) {
+    const int col = (int)(i % c4) * 4;
+    const float4 xv = reinterpret_cast<const float4*>(a.x)[i];
+    const float4 m = *reinterpret_cast<const float4*>(a.mean + col);
+    const float4 s = *reinterpret_cast<const float4*>(a.invstd + col);
+    const float4 g = *reinterpret_cast<const float4*>(a.gamma + col);
+    const float4 b = *reinterpret_cast<const float4*>(a.beta + col);
+    float4 y;
+    y.x = fmaf((xv.x - m.x) * s.x, g.x, b.x);
+    y.y = fmaf((xv.y - m.y) * s.y, g.y, b.y);
+    y.z = fmaf((xv.z - m.z) * s.z, g.z, b.z);
+    y.w = fmaf((xv.w - m.w) * s.w, g.w, b.w);
+    if (a.residual != nullptr) {
+      const float4 r = reinterpret_cast<const float4*>(a.residual)[i];
+      y.x += r.x; y.y += r.y; y.z += r.z; y.w += r.w;
+    }
+    if (a.relu) {
+      y.x = fmaxf(y.x, 0.f); y.y = fmaxf(y.y, 0.f); y.z = fmaxf(y.z, 0.f); y.w = fmaxf(y.w, 0.f);
+    }
+    reinterpret_cast<float4*>(a.out)[i] = y;
+  }
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnArgs a) {
+  const size_t n4 = (size_t)a.P * a.C / 4;
+  const int c4 = a.C >> 2;
+  const float inv_p = 1.f / (float)a.P;
+  for (size_t i = (size_t)blockIdx.x * BN_THREADS + threadIdx.x; i < n4; i += (size_t)gridDim.x * BN_THREADS) {
+    const int col = (int)(i % c4) * 4;
+    const float4 xv = reinterpret_cast<const float4*>(a.x)[i];
+    float4 gv = reinterpret_cast<const float4*>(a.dy)[i];
+    if (a.relu) {
+      const float4 yv = reinterpret_cast<const float4*>(a.y)[i];
+      gv.x = yv.x > 0.f ? gv.x : 0.f; gv.y = yv.y > 0.f ? gv.y : 0.f;
+      gv.z = yv.z > 0.f ? gv.z : 0.f; gv.w = yv.w > 0.f ? gv.w : 0.f;
+    }
+    if (a.out2 != nullptr) reinterpret_cast<float4*>(a.out2)[i] = gv;
+    const float4 m = *reinterpret_cast<const float4*>(a.mean + col);
+    const float4 s = *reinterpret_cast<const float4*>(a.invstd + col);
+    const float4 g = *reinterpret_cast<const float4*>(a.gamma + col);
+    const float4 db = *reinterpret_cast<const float4*>(a.dbeta + col);
+    const float4 dg = *reinterpret_cast<const float4*>(a.dgamma + col);
+    float4 dx;
+    dx.x = g.x * s.x * (gv.x - db.x * inv_p - (xv.x - m.x) * s.x * dg.x * inv_p);
+    dx.y = g.y * s.y * (gv.y - db.y * inv_p - (xv.y - m.y) * s.y * dg.y * inv_p);
+    dx.z = g.z * s.z * (gv.z - db.z * inv_p - (xv.z - m.z) * s.z * dg.z * inv_p);
+    dx.w = g.w * s.w * (gv.w - db.w * inv_p - (xv.w - m.w) * s.w * dg.w * inv_p);
+    reinterpret_cast<float4*>(a.out)[i] = dx;
+  }
+}
+
+static int grid_for(long long n4) {
+  long long b = (n4 + BN_THREADS - 1) / BN_THREADS;
+  if (b > 148 * 8) b = 148 * 8;
+  return (int)(b < 1 ? 1 : b);
+}
+
+extern "C" int bn_reduce_grid(int P, int C) {
+  const int rpb = BN_THREADS / (C / 4);
+  int g = (P + rpb * 8 - 1) / (rpb * 8);  // at least 8 passes of rows per CTA
+  if (g > 148 * 4) g = 148 * 4;
+  return g < 1 ? 1 : g;
+}
+
+extern "C" int bn_forward(const BnArgs* args, cudaStream_t st) {
+  BnArgs a = *args;
+  if (a.C % 4 != 0 || BN_THREADS % (a.C / 4) != 0 || a.C / 4 > BN_THREADS) return -1;
+  bn_reduce_kernel<false><<<bn_reduce_grid(a.P, a.C), BN_THREADS, 0, st>>>(a);
+  bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4), BN_THREADS, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int bn_backward(const BnArgs* args, cudaStream_t st) {
+  BnArgs a = *args;
+  if (a.C % 4 != 0 || BN_THREADS % (a.C / 4) != 0 || a.C / 4 > BN_THREADS) return -1;
+  bn_reduce_kernel<true><<<bn_reduce_grid(a.P, a.C), BN_THREADS, 0, st>>>(a);
+  bn_bwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4), BN_THREADS, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int bn_args_size() { return (int)sizeof(BnArgs); }

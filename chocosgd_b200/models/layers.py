@@ -24,6 +24,13 @@ Embedding = nn.Embedding
 LSTM = native_nn.LSTM
 
 
+def bn_act(bn, x, residual=None, relu=True):
+    """relu(bn(x) + residual): one fused kernel pair on the native path."""
+    from ..ops.bn import bn_act as _f
+
+    return _f(bn, x, residual, relu)
+
+
 def conv3x3(in_planes, out_planes, stride=1):
     return Conv2d(in_planes, out_planes, kernel_size=3, stride=stride, padding=1, bias=False)
 

@@ -26,9 +26,8 @@ class BasicBlock(nn.Module):
 
     def forward(self, x):
         residual = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.bn2(self.conv2(out))
-        return self.relu(out + residual)
+        out = L.bn_act(self.bn1, self.conv1(x))
+        return L.bn_act(self.bn2, self.conv2(out), residual=residual)
 
 
 class Bottleneck(nn.Module):
@@ -48,10 +47,9 @@ class Bottleneck(nn.Module):
 
     def forward(self, x):
         residual = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.relu(self.bn2(self.conv2(out)))
-        out = self.bn3(self.conv3(out))
-        return self.relu(out + residual)
+        out = L.bn_act(self.bn1, self.conv1(x))
+        out = L.bn_act(self.bn2, self.conv2(out))
+        return L.bn_act(self.bn3, self.conv3(out), residual=residual)
 
 
 class _ResNetBase(nn.Module):
@@ -89,7 +87,7 @@ class ResNetCifar(_ResNetBase):
         L.he_init(self)
 
     def forward(self, x):
-        x = self.relu(self.bn1(self.conv1(x)))
+        x = L.bn_act(self.bn1, self.conv1(x))
         x = self.layer3(self.layer2(self.layer1(x)))
         x = self.avgpool(x)
         return self.fc(x.reshape(x.size(0), -1))
@@ -123,7 +121,7 @@ class ResNetImagenet(_ResNetBase):
         L.he_init(self)
 
     def forward(self, x):
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.maxpool(L.bn_act(self.bn1, self.conv1(x)))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = self.avgpool(x)
         return self.fc(x.reshape(x.size(0), -1))

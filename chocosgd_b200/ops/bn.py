@@ -1,0 +1,125 @@
+"""Fused training-mode BatchNorm (+ residual add) (+ ReLU) on NHWC fp32 tensors
+(``csrc/bn_nhwc.cu``).  ``bn_act(bn_module, x, residual=None, relu=True)`` is what the model
+blocks call; it uses the fused kernels for channels_last CUDA fp32 tensors in training mode
+when the native path is enabled and the plain PyTorch composition otherwise."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+
+class BnArgsC(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in (
+        "x", "dy", "y", "residual", "gamma", "beta", "out", "out2", "mean", "invstd", "running_mean", "running_var",
+        "dgamma", "dbeta", "partial", "counter")] + [
+        ("P", ctypes.c_int), ("C", ctypes.c_int), ("relu", ctypes.c_int), ("eps", ctypes.c_float),
+        ("momentum", ctypes.c_float)]
+
+
+_scratch = {}
+
+
+def _lib_bn():
+    lib = _lib.load()
+    if not getattr(lib, "_bn_declared", False):
+        for name in ("bn_forward", "bn_backward"):
+            fn = getattr(lib, name)
+            fn.argtypes = [ctypes.POINTER(BnArgsC), ctypes.c_void_p]
+            fn.restype = ctypes.c_int
+        lib.bn_reduce_grid.argtypes = [ctypes.c_int, ctypes.c_int]
+        lib.bn_reduce_grid.restype = ctypes.c_int
+        lib.bn_args_size.restype = ctypes.c_int
+        assert lib.bn_args_size() == ctypes.sizeof(BnArgsC)
+        lib._bn_declared = True
+    return lib
+
+
+def _get_scratch(device, P, C, lib):
+    """Per-device scratch for the partial sums (one stream at a time uses it: kernels of one
+    training step are ordered on a single stream)."""
+    need = lib.bn_reduce_grid(P, C) * 2 * C
+    key = device.index
+    buf = _scratch.get(key)
+    if buf is None or buf[0].numel() < need:
+        buf = (torch.empty(max(need, 1 << 16), dtype=torch.float32, device=device),
+               torch.zeros(1, dtype=torch.int32, device=device))
+        _scratch[key] = buf
+    return buf
+
+
+def supported(x, C) -> bool:
+    return (x.is_cuda and x.dtype == torch.float32 and x.dim() == 4 and C % 4 == 0 and (C // 4) <= 256
+            and 256 % (C // 4) == 0 and x.is_contiguous(memory_format=torch.channels_last))
+
+
+class _BnActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, residual, running_mean, running_var, relu, momentum, eps):
+        lib = _lib_bn()
+        N, C, H, W = x.shape
+        P = N * H * W
+        y = torch.empty_like(x)  # channels_last preserved
+        mean = torch.empty(C, dtype=torch.float32, device=x.device)
+        invstd = torch.empty_like(mean)
+        partial, counter = _get_scratch(x.device, P, C, lib)
+        a = BnArgsC()
+        a.x, a.gamma, a.beta, a.out = x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr()
+        a.residual = residual.data_ptr() if residual is not None else 0
+        a.mean, a.invstd = mean.data_ptr(), invstd.data_ptr()
+        a.running_mean = running_mean.data_ptr() if running_mean is not None else 0
+        a.running_var = running_var.data_ptr() if running_var is not None else 0
+        a.partial, a.counter = partial.data_ptr(), counter.data_ptr()
+        a.P, a.C, a.relu, a.eps, a.momentum = P, C, int(relu), float(eps), float(momentum)
+        rc = lib.bn_forward(ctypes.byref(a), _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"bn_forward failed ({rc})")
+        ctx.save_for_backward(x, y, gamma, mean, invstd)
+        ctx.relu, ctx.has_res = bool(relu), residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib_bn()
+        x, y, gamma, mean, invstd = ctx.saved_tensors
+        N, C, H, W = x.shape
+        P = N * H * W
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = torch.empty_like(x)
+        dres = torch.empty_like(x) if ctx.has_res else None
+        dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty_like(dgamma)
+        partial, counter = _get_scratch(x.device, P, C, lib)
+        a = BnArgsC()
+        a.x, a.dy, a.y, a.gamma = x.data_ptr(), dy.data_ptr(), y.data_ptr(), gamma.data_ptr()
+        a.out = dx.data_ptr()
+        a.out2 = dres.data_ptr() if dres is not None else 0
+        a.mean, a.invstd, a.dgamma, a.dbeta = mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr()
+        a.partial, a.counter = partial.data_ptr(), counter.data_ptr()
+        a.P, a.C, a.relu = P, C, int(ctx.relu)
+        rc = lib.bn_backward(ctypes.byref(a), _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"bn_backward failed ({rc})")
+        return dx, dgamma, dbeta, dres, None, None, None, None, None
+
+
+def bn_act(bn, x, residual=None, relu=True):
+    """``relu(bn(x) + residual)`` with one fused kernel pair when possible."""
+    from . import nn as native_nn
+
+    if (native_nn.native_enabled("bn") and bn.training and bn.track_running_stats is not None
+            and supported(x, bn.num_features) and bn.affine
+            and (residual is None or (residual.shape == x.shape and residual.is_contiguous(memory_format=torch.channels_last)))):
+        if bn.track_running_stats and bn.num_batches_tracked is not None:
+            bn.num_batches_tracked.add_(1)
+        mom = bn.momentum if bn.momentum is not None else 0.1
+        rm = bn.running_mean if bn.track_running_stats else None
+        rv = bn.running_var if bn.track_running_stats else None
+        return _BnActFn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps)
+    out = bn(x)
+    if residual is not None:
+        out = out + residual
+    return F.relu(out, inplace=True) if relu else out

@@ -11,12 +11,23 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-_NATIVE = {"linear": False, "conv": False, "lstm": False}
+_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False}
 
 
-def set_native(enabled: bool = True, which=("linear", "conv", "lstm")):
+def set_native(enabled: bool = True, which=("linear", "conv", "lstm", "bn")):
     for k in which:
         _NATIVE[k] = bool(enabled)
+
+
+def available_kinds():
+    """Kinds of layers whose native kernels are built into this tree."""
+    import importlib.util
+
+    kinds = ["bn", "linear"]
+    for kind, mod in (("conv", "conv"), ("lstm", "lstm")):
+        if importlib.util.find_spec(f"{__package__}.{mod}") is not None:
+            kinds.append(kind)
+    return tuple(kinds)
 
 
 def native_enabled(kind: str) -> bool:
