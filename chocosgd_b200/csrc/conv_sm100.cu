@@ -1,0 +1,233 @@
+// 3x3 / stride 1 / pad 1 convolution as an implicit GEMM on tcgen05 tensor cores, NHWC fp32 (TF32).
+//
+//   y[n,h,w,:] = sum_{r,s} x[n, h+r-1, w+s-1, :] . W[:, r, s, :]^T        M = N H W, N = C_out, K = 9 C_in
+//
+// The im2col matrix is never built.  A CTA owns 128 consecutive output pixels (TW x TH x TN
+// box of the image tensor); for each of the 9 filter taps and each block of KC <= 32 input
+// channels ONE 4-d TMA load fetches the shifted activation tile straight from the NHWC tensor
+// (coordinates may run outside the image: TMA fills zeros, which is exactly the padding) and
+// one 2-d TMA load fetches the matching [C_out, KC] slice of the KRSC weight tensor.  Both
+// land K-major with a 64- or 128-byte swizzle, a single thread issues tcgen05.mma
+// (M = 128, N = C_out, K = 8 per instruction), the accumulator stays in TMEM across all
+// 9 C_in / KC blocks, and the epilogue writes 128 NHWC output rows.
+//
+// The input gradient of such a convolution is the same operation applied to dy with the
+// filter flipped and its channel roles exchanged (conv_flip_weights), so one kernel serves
+// forward and dgrad.  Bounded mbarrier waits as in the GEMM kernel; no cluster multicast.
+#include "tc_common.cuh"
+
+#define CONV_THREADS 192
+#define CONV_STAGES 6
+
+struct ConvArgs {
+  float* y;        // [N*H*W, C_out]
+  int* error;
+  int H, W, Cin;
+  int TH, TN;      // tile: W x TH x TN = 128 pixels
+  int tiles_h;     // H / TH
+  int relu;
+};
+
+template <int COUT, int KC>
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv3x3_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ConvArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int ROW = KC * 4;                  // bytes per K-major row: 64 or 128
+  constexpr int A_BYTES = 128 * ROW;
+  constexpr int B_BYTES = COUT * ROW;
+  constexpr uint32_t LAYOUT = ROW == 128 ? 2u : 4u;   // 128-byte / 64-byte swizzle
+  constexpr uint32_t SBO = 8 * ROW;                   // 8 rows
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + CONV_STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sB + CONV_STAGES * B_BYTES);
+  uint64_t* empty = full + CONV_STAGES;
+  uint64_t* acc_ready = empty + CONV_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;
+  const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
+  const int cblocks = g.Cin / KC;
+  const int n_kb = 9 * cblocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < CONV_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_ready, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  constexpr uint32_t TMEM_COLS = COUT < 32 ? 32 : COUT;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4 && lane == 0) {
+    for (int i = 0; i < n_kb; ++i) {
+      const int s = i % CONV_STAGES;
+      if (i >= CONV_STAGES && !mbar_wait(empty + s, ((i / CONV_STAGES) - 1) & 1)) { *abort_flag = 1; break; }
+      if (*abort_flag) break;
+      const int tap = i / cblocks, c0 = (i % cblocks) * KC;
+      const int r = tap / 3, t = tap % 3;
+      mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+      // the channel coordinate is a multiple of 16 elements: 16-byte aligned as TMA requires
+      tma_load_4d(sA + s * A_BYTES, &map_x, full + s, c0, t - 1, h0 + r - 1, n0);
+      tma_load_2d(sB + s * B_BYTES, &map_w, full + s, tap * g.Cin + c0, 0);
+    }
+  } else if (warp == 5 && lane == 0) {
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(COUT >> 3) << 17) | ((128u >> 4) << 24);
+    bool ok = true;
+    for (int i = 0; i < n_kb && ok; ++i) {
+      const int s = i % CONV_STAGES;
+      if (!mbar_wait(full + s, (i / CONV_STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+      tc_fence_after();
+      const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+      for (int k = 0; k < KC / 8; ++k)
+        umma_tf32(tmem_base, make_desc(a_addr + k * 32, 16, SBO, LAYOUT), make_desc(b_addr + k * 32, 16, SBO, LAYOUT),
+                  idesc, (i > 0 || k > 0) ? 1u : 0u);
+      tc_commit(empty + s);
+    }
+    if (ok) tc_commit(acc_ready);
+  } else if (warp < 4) {
+    bool ok = mbar_wait(acc_ready, 0);
+    if (!ok) *abort_flag = 1;
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      // the tile's 128 pixels are consecutive rows of the [N*H*W, C_out] output
+      const size_t pix = ((size_t)n0 * g.H + h0) * g.W + warp * 32 + lane;
+      float* out = g.y + pix * COUT;
+#pragma unroll 1
+      for (int c = 0; c < COUT; c += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c, v);
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                 __uint_as_float(v[j + 3]));
+          if (g.relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
+          *reinterpret_cast<float4*>(out + c + j) = o;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(g.error, 1);
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// W'[ci, r, s, co] = W[co, 2 - r, 2 - s, ci]   (both KRSC): the filter of the input-gradient convolution
+__global__ void conv_flip_weights_kernel(const float* __restrict__ w, float* __restrict__ out, int cout, int cin) {
+  const int total = cout * 9 * cin;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int co = i % cout, tap = (i / cout) % 9, ci = i / (9 * cout);
+    out[i] = w[(co * 9 + (8 - tap)) * cin + ci];
+  }
+}
+
+extern "C" int conv_flip_weights(const void* w, void* out, int cout, int cin, cudaStream_t st) {
+  const int total = cout * 9 * cin;
+  conv_flip_weights_kernel<<<(total + 255) / 256, 256, 0, st>>>(reinterpret_cast<const float*>(w),
+                                                                 reinterpret_cast<float*>(out), cout, cin);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------- host side ----------------------------------------------
+static int* g_conv_error[64];
+
+static int* conv_error_word() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (g_conv_error[dev] == nullptr) {
+    if (cudaMalloc(&g_conv_error[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(g_conv_error[dev], 0, sizeof(int));
+  }
+  return g_conv_error[dev];
+}
+
+extern "C" int conv3x3_last_error() {
+  int* w = conv_error_word();
+  int v = -1;
+  if (w != nullptr) cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+
+template <int COUT, int KC>
+static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, const ConvArgs& g, int tiles, cudaStream_t st) {
+  constexpr int smem = CONV_STAGES * (128 * KC * 4 + COUT * KC * 4) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(conv3x3_tf32_kernel<COUT, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  conv3x3_tf32_kernel<COUT, KC><<<tiles, CONV_THREADS, smem, st>>>(mx, mw, g);
+  return (int)cudaGetLastError();
+}
+
+// 1 when conv3x3_tf32 handles this shape
+extern "C" int conv3x3_supported(int N, int H, int W, int Cin, int Cout) {
+  if (!(W == 8 || W == 16 || W == 32)) return 0;
+  if (!(Cin == 16 || Cin == 32 || Cin == 64 || Cin == 128)) return 0;
+  if (!(Cout == 16 || Cout == 32 || Cout == 64 || Cout == 128)) return 0;
+  int th = 128 / W;
+  if (th > H) th = H;
+  const int tn = 128 / (W * th);
+  if (W * th * tn != 128) return 0;
+  if (H % th != 0 || N % tn != 0) return 0;
+  if (tn > 1 && th != H) return 0;
+  return 1;
+}
+
+// x [N,H,W,Cin], w [Cout,3,3,Cin], y [N,H,W,Cout], all fp32 NHWC / KRSC
+extern "C" int conv3x3_tf32(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout, int relu,
+                            cudaStream_t st) {
+  if (!conv3x3_supported(N, H, W, Cin, Cout)) return -1;
+  int th = 128 / W;
+  if (th > H) th = H;
+  const int tn = 128 / (W * th);
+  const int kc = Cin >= 32 ? 32 : 16;
+  const CUtensorMapSwizzle sw = kc == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUtensorMap mx, mw;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    cuuint64_t str[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
+    cuuint32_t box[4] = {(cuuint32_t)kc, (cuuint32_t)W, (cuuint32_t)th, (cuuint32_t)tn};
+    int rc = tc_make_map(&mx, x, 4, dims, str, box, sw);
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)9 * Cin, (cuuint64_t)Cout};
+    cuuint64_t str[1] = {(cuuint64_t)9 * Cin * 4};
+    cuuint32_t box[2] = {(cuuint32_t)kc, (cuuint32_t)Cout};
+    int rc = tc_make_map(&mw, w, 2, dims, str, box, sw);
+    if (rc) return rc;
+  }
+  ConvArgs g;
+  g.y = reinterpret_cast<float*>(y);
+  g.error = conv_error_word();
+  if (g.error == nullptr) return -13;
+  g.H = H; g.W = W; g.Cin = Cin; g.TH = th; g.TN = tn; g.tiles_h = H / th; g.relu = relu;
+  const int tiles = (N / tn) * (H / th);
+#define CONV_CASE(CO)                                                              \
+  if (Cout == CO) return kc == 32 ? launch_conv<CO, 32>(mx, mw, g, tiles, st) : launch_conv<CO, 16>(mx, mw, g, tiles, st);
+  CONV_CASE(16) CONV_CASE(32) CONV_CASE(64) CONV_CASE(128)
+#undef CONV_CASE
+  return -1;
+}

@@ -1,0 +1,85 @@
+"""Native convolution path: 3x3 / stride 1 / pad 1 NHWC fp32 convolutions run the tcgen05
+implicit-GEMM kernel (``csrc/conv_sm100.cu``) for the forward pass and for the input gradient
+(same kernel on dy with the flipped filter).  The weight gradient and all other convolution
+shapes (strided, 1x1, first layer with 3 input channels) use the library convolution."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _declare():
+    lib = _lib.load()
+    if not getattr(lib, "_conv_declared", False):
+        vp, i = ctypes.c_void_p, ctypes.c_int
+        lib.conv3x3_tf32.argtypes = [vp, vp, vp, i, i, i, i, i, i, vp]
+        lib.conv3x3_tf32.restype = i
+        lib.conv3x3_supported.argtypes = [i, i, i, i, i]
+        lib.conv3x3_supported.restype = i
+        lib.conv_flip_weights.argtypes = [vp, vp, i, i, vp]
+        lib.conv_flip_weights.restype = i
+        lib.conv3x3_last_error.restype = i
+        lib._conv_declared = True
+    return lib
+
+
+def conv_supported(m, x) -> bool:
+    if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 4 and m.weight.dtype == torch.float32):
+        return False
+    if m.kernel_size != (3, 3) or m.stride != (1, 1) or m.padding != (1, 1) or m.dilation != (1, 1):
+        return False
+    if m.groups != 1 or m.bias is not None or m.padding_mode != "zeros":
+        return False
+    if not (x.is_contiguous(memory_format=torch.channels_last) and m.weight.is_contiguous(memory_format=torch.channels_last)):
+        return False
+    n, c, h, w = x.shape
+    return bool(_declare().conv3x3_supported(n, h, w, c, m.out_channels)) and bool(
+        _declare().conv3x3_supported(n, h, w, m.out_channels, c))
+
+
+def conv3x3(x, w_krsc_ptr_tensor, cout, relu=False):
+    """x: [N, Cin, H, W] channels_last; weight tensor whose memory is [Cout, 3, 3, Cin]."""
+    lib = _declare()
+    n, cin, h, w = x.shape
+    y = torch.empty((n, cout, h, w), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+    rc = lib.conv3x3_tf32(_lib.ptr(x), _lib.ptr(w_krsc_ptr_tensor), _lib.ptr(y), n, h, w, cin, cout, int(relu),
+                          _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"conv3x3_tf32 failed ({rc})")
+    return y
+
+
+def last_error() -> int:
+    return _declare().conv3x3_last_error()
+
+
+class _Conv3x3Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return conv3x3(x, weight, weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        lib = _declare()
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        cout, cin = weight.shape[0], weight.shape[1]
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            flipped = torch.empty(cin * 9 * cout, dtype=torch.float32, device=x.device)
+            rc = lib.conv_flip_weights(_lib.ptr(weight), _lib.ptr(flipped), cout, cin, _lib.stream_ptr())
+            if rc != 0:
+                raise RuntimeError(f"conv_flip_weights failed ({rc})")
+            dx = conv3x3(dy, flipped, cin)
+        if ctx.needs_input_grad[1]:
+            dw = torch.ops.aten.convolution_backward(
+                dy, x, weight, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1, (False, True, False))[1]
+        return dx, dw
+
+
+def conv2d_native(m, x):
+    return _Conv3x3Fn.apply(x, m.weight)
