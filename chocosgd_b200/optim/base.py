@@ -79,6 +79,45 @@ class DistributedOptimizer(Optimizer):
         )
         self.decentralized_aggregator = DecentralizedAggregation(self.rank, self.neighbors_info, group)
         self._epoch_override = None
+        self.group = group
+        self._exchange = None
+        self._gather = None
+
+    # ---- transports ----------------------------------------------------------------------
+    def _mailbox_ok(self) -> bool:
+        import torch.distributed as dist
+
+        return (self.device.type == "cuda" and self.n_nodes > 1 and dist.is_available() and dist.is_initialized()
+                and getattr(self.conf, "gossip_impl", "auto") != "nccl")
+
+    def neighbor_exchange(self):
+        """Transport of neighbour payloads: peer-mapped mailboxes written from inside kernels
+        on NVLink, ``torch.distributed`` send/recv otherwise (CPU / Gloo, ``--gossip_impl nccl``)."""
+        if self._exchange is None:
+            if self._mailbox_ok() and len(self.neighbors_info) - 1 <= 16:
+                from ..parallel.exchange import MailboxExchange
+
+                self._exchange = MailboxExchange(self.graph, self.seg.total, self.device, self.group,
+                                                 getattr(self.conf, "wait_budget_ms", 2000.0))
+            else:
+                self._exchange = self.decentralized_aggregator
+        return self._exchange
+
+    def gather_payloads(self, payload):
+        """Payloads of all ranks in rank order (all-gather; by mailbox push on NVLink)."""
+        if self._gather is None:
+            if self._mailbox_ok() and self.n_nodes - 1 <= 16:
+                from ..parallel.exchange import MailboxExchange
+                from ..parallel.topology import Graph
+
+                full = Graph("complete", self.n_nodes, self.rank)
+                self._gather = MailboxExchange(full, self.seg.total, self.device, self.group,
+                                               getattr(self.conf, "wait_budget_ms", 2000.0))
+            else:
+                self._gather = False
+        if self._gather is False:
+            return self.world_aggregator._agg(payload, communication_scheme="all_gather")
+        return self._gather.all_gather(payload)
 
     # ---- hyper-parameters ------------------------------------------------------------
     @property

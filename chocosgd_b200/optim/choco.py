@@ -96,7 +96,7 @@ class ChocoSGD(DistributedOptimizer):
             a.x.add_(self.s - self.x_hat, alpha=self.consensus_stepsize)
         with timer("sync.start_sync", epoch=ep):
             payload = self.codec.compress(a.x - self.x_hat, self.gossip_step, self.rank)
-            self._pending = (self.decentralized_aggregator.start(payload), self.gossip_step)
+            self._pending = (self.neighbor_exchange().start(payload), self.gossip_step)
             self._pending_bits = self.codec.n_bits()
             self.gossip_step += 1
             if not self.overlap:

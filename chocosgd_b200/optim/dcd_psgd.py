@@ -50,7 +50,7 @@ class DCD_PSGD(DistributedOptimizer):
         with timer("grad.compress", epoch=ep):
             payload = self.codec.compress(half - a.x, step, self.rank)
         with timer("grad.sync", epoch=ep):
-            received = self.decentralized_aggregator._agg(payload, op="get_raw_sync_data")
+            received = self.neighbor_exchange()._agg(payload, op="get_raw_sync_data")
         with timer("grad.unflatten_to_update", epoch=ep):
             self._apply(received, step)
             a.x.copy_(self.neighbor_hat_params[self.rank])

@@ -42,7 +42,7 @@ class DeepSqueeze(DistributedOptimizer):
         with timer("grad.update_memory", epoch=ep):
             self.memory.sub_(self.codec.decompress(payload, step, self.rank))
         with timer("grad.sync", epoch=ep):
-            received = self.decentralized_aggregator._agg(payload, op="get_raw_sync_data")
+            received = self.neighbor_exchange()._agg(payload, op="get_raw_sync_data")
         with timer("grad.decompress", epoch=ep):
             for rank, w in self.neighbors_info.items():
                 coeff = self.consensus_stepsize * (w - (1.0 if rank == self.rank else 0.0))

@@ -104,7 +104,7 @@ class DGC(DistributedOptimizer):
                 payload = codec.compress(d, step, self.rank)
         with timer("grad.sync", epoch=ep):
             if self.is_compress_op:
-                gathered = self.world_aggregator._agg(payload, communication_scheme="all_gather")
+                gathered = self.gather_payloads(payload)
             else:
                 dense = codec.decompress(payload, step, self.rank)
                 gathered = self.world_aggregator._agg(dense, op="sum", communication_scheme="all_reduce")

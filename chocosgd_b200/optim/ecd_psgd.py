@@ -45,7 +45,7 @@ class ECD_PSGD(DistributedOptimizer):
         with timer("grad.compress", epoch=ep):
             payload = self.codec.compress(z, step, self.rank)
         with timer("grad.sync", epoch=ep):
-            received = self.decentralized_aggregator._agg(payload, op="get_raw_sync_data")
+            received = self.neighbor_exchange()._agg(payload, op="get_raw_sync_data")
         with timer("grad.unflatten_to_update", epoch=ep):
             for rank in self.neighbors_info:
                 hat = self.neighbor_hat_params[rank]

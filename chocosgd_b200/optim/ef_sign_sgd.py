@@ -41,7 +41,7 @@ class EF_SignSGD(DistributedOptimizer):
             own = self.codec.decompress(payload)
             self.memory.copy_(p - own)
         with timer("sync.sync", epoch=ep):
-            gathered = self.world_aggregator._agg(payload, communication_scheme="all_gather")
+            gathered = self.gather_payloads(payload)
         with timer("sync.decompress", epoch=ep):
             avg = torch.zeros_like(a.x)
             for msg in gathered:

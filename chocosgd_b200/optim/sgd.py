@@ -66,8 +66,12 @@ class SGD(DistributedOptimizer):
                 a.x.add_(self.local_direction(), alpha=-self.lr)
             with timer("sync.sync", epoch=ep):
                 if self.n_nodes > 1:
-                    mixed = self.decentralized_aggregator._agg(a.x, op="weighted")
-                    with timer("sync.update_model", epoch=ep):
-                        a.x.copy_(mixed)
+                    ex = self.neighbor_exchange()
+                    if hasattr(ex, "mix_"):
+                        ex.mix_(a.x)  # push + fused wait / weighted sum, no library call
+                    else:
+                        mixed = ex._agg(a.x, op="weighted")
+                        with timer("sync.update_model", epoch=ep):
+                            a.x.copy_(mixed)
         self.n_bits = 32 * self.seg.n_elements
         return self.n_bits

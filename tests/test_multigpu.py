@@ -113,3 +113,77 @@ def test_fused_choco_over_nvlink_matches_simulator(world):
                 np.testing.assert_allclose(x, sim.x[r].numpy(), rtol=2e-5, atol=2e-6, err_msg=f"{comm_op} x rank {r}")
                 np.testing.assert_allclose(xh, sim.x_hat[r].numpy(), rtol=2e-5, atol=2e-6, err_msg=f"{comm_op} x_hat")
                 np.testing.assert_allclose(s, sim.s[r].numpy(), rtol=2e-5, atol=2e-6, err_msg=f"{comm_op} s")
+
+
+OTHER = [("sgd", None, "ring"), ("dcd_psgd", "compress_top_k", "ring"), ("ecd_psgd", "quantize_qsgd", "ring"),
+         ("deep_squeeze", "sign", "ring"), ("dgc", "compress_top_k", "complete"), ("ef_sign_sgd", None, "complete"),
+         ("parallel_choco_v", "sign", "ring")]
+
+
+def conf_other(optimizer, comm_op, topo, n, impl):
+    from chocosgd_b200.config import get_args
+
+    argv = ["--optimizer", optimizer, "--graph_topology", topo, "--n_mpi_process", str(n), "--lr", "0.05",
+            "--momentum_factor", "0.9", "--use_nesterov", "True", "--weight_decay", "0.01",
+            "--consensus_stepsize", "0.4", "--gossip_impl", impl, "--wait_budget_ms", "5000"]
+    if comm_op:
+        argv += ["--comm_op", comm_op]
+    if comm_op and "compress" in comm_op:
+        argv += ["--compress_ratio", "0.9"]
+    if comm_op == "quantize_qsgd":
+        argv += ["--quantize_level", "4"]
+    return get_args(argv)
+
+
+def _worker_other(rank, world, port, steps, out):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from chocosgd_b200.optim import define_optimizer
+        from chocosgd_b200.parallel.exchange import sq_distance
+        from chocosgd_b200.parallel.topology import Graph
+
+        res = {}
+        for optimizer, comm_op, topo in OTHER:
+            xs = {}
+            for impl in ("fused", "nccl"):  # mailbox transport vs torch.distributed on the same GPUs
+                conf = conf_other(optimizer, comm_op, topo, world, impl)
+                if optimizer == "parallel_choco_v" and impl == "fused":
+                    continue
+                graph = Graph(topo, world, rank)
+                model = make_model().cuda()
+                opt = define_optimizer(conf, model, graph)
+                for t in range(steps):
+                    opt.arena.g.copy_(grad_flat(rank, t, opt.seg))
+                    opt.step(epoch=0.5)
+                opt.finalize()
+                torch.cuda.synchronize()
+                xs[impl] = opt.arena.x.clone()
+                dist.barrier()
+            if "fused" in xs:
+                d = float(sq_distance(xs["fused"], xs["nccl"]))
+                res[optimizer] = (d, float((xs["nccl"].double() ** 2).sum()))
+        out[rank] = res
+    finally:
+        dist.destroy_process_group()
+
+
+def test_mailbox_transport_equals_library_transport():
+    """Every non-fused algorithm gives the same parameters whether its payloads travel through the
+    peer-mapped mailboxes (in-kernel NVLink stores) or through torch.distributed."""
+    world = 2
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    port = free_port()
+    procs = [ctx.Process(target=_worker_other, args=(r, world, port, 5, out)) for r in range(world)]
+    [p.start() for p in procs]
+    [p.join(600) for p in procs]
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    for r in range(world):
+        for name, (d, ref) in out[r].items():
+            assert d <= 1e-10 * ref + 1e-12, (name, d, ref)
