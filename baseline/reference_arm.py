@@ -141,6 +141,15 @@ def build(rank, world, comm_op, batch_size, device, consensus_stepsize=0.5):
     return conf, model, optimizer, metrics, timer, criterion
 
 
+def finish(state):
+    """Join the reference's helper thread so no exchange is in flight at teardown."""
+    optimizer = state[2]
+    thread = getattr(optimizer, "helper_thread", None)
+    if thread is not None:
+        thread.join()
+    torch.cuda.synchronize()
+
+
 def train_iteration(conf, model, optimizer, metrics, timer, criterion, inp_host, tgt_host, step):
     """One iteration of the reference's CV loop."""
     model.train()

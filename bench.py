@@ -233,6 +233,7 @@ def run_reference(args, rank, world, local):
     sampler = ClockSampler(rank == 0, local)
     ms = timed(it, args.steps, world)
     clocks = sampler.stop()
+    ref.finish(state)
     return ms, ms, clocks, 0, out["loss"], BATCH * 3 * 32 * 32 * 4 + BATCH * 8, {}
 
 
@@ -277,8 +278,12 @@ def main():
         }
         print(json.dumps(line))
     if dist.is_initialized():
-        dist.barrier()
-        dist.destroy_process_group()
+        try:
+            torch.cuda.synchronize()
+            dist.barrier()
+            dist.destroy_process_group()
+        except Exception as e:  # a failing teardown must not turn a measured run into an error
+            print(f"[bench] teardown: {e!r}", file=sys.stderr)
 
 
 if __name__ == "__main__":

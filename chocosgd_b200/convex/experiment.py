@@ -49,8 +49,8 @@ def epsilon_final_params(n=400000, d=2000, n_cores=9, num_epoch=10, seeds=(1, 2,
     combos = [
         dict(method="plain", quantization="full"),
         dict(method="choco", quantization="top", coordinates_to_keep=k, consensus_lr=0.04),
-        dict(method="choco", quantization="random-unbiased", coordinates_to_keep=k, consensus_lr=0.01),
-        dict(method="choco", quantization="qsgd-unbiased", num_levels=levels, consensus_lr=0.34),
+        dict(method="choco", quantization="random-biased", coordinates_to_keep=k, consensus_lr=0.01),
+        dict(method="choco", quantization="qsgd-biased", num_levels=levels, consensus_lr=0.34),
         dict(method="dcd-psgd", quantization="random-unbiased", coordinates_to_keep=k),
         dict(method="dcd-psgd", quantization="qsgd-unbiased", num_levels=levels),
         dict(method="ecd-psgd", quantization="random-unbiased", coordinates_to_keep=k),
