@@ -131,6 +131,12 @@ class ChocoSGD(DistributedOptimizer):
         self.local_index += 1
         return self._step_torch(timer, ep)
 
+    def reset_consensus_state(self):
+        """Zero x_hat and s (all survivors do this together after the graph changed)."""
+        self.finalize()
+        self.x_hat.zero_()
+        self.s.zero_()
+
     def finalize(self):
         if self.impl == "fused":
             self.engine.flush(self)
