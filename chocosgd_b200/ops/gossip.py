@@ -41,11 +41,12 @@ HYP_LR, HYP_MOMENTUM, HYP_GAMMA, HYP_NESTEROV, HYP_GSCALE, HYP_N = 0, 1, 2, 3, 4
 
 
 def pick_chunk_elems(total: int) -> int:
-    if total <= (1 << 22):
-        return 1024
-    if total <= (1 << 26):
-        return 4096
-    return 8192
+    """Elements per CTA: as large as possible (the per-CTA prologue / publish epilogue is a fixed
+    cost) while keeping about two waves of CTAs on 148 SMs x 8 resident CTAs."""
+    c = 1024
+    while c < 32768 and total // (2 * c) >= 2400:
+        c *= 2
+    return c
 
 
 class SegTables:
