@@ -1,0 +1,89 @@
+"""TrainStep on a GPU: CUDA-graph replay, eager fused and the torch-path optimizer agree."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(arch, comm_op, impl, extra=()):
+    from chocosgd_b200.config import get_args
+    from chocosgd_b200.models import define_model
+    from chocosgd_b200.optim import define_optimizer
+    from chocosgd_b200.parallel.topology import Graph
+
+    argv = ["--arch", arch, "--optimizer", "parallel_choco_v", "--comm_op", comm_op, "--graph_topology", "ring",
+            "--lr", "0.05", "--momentum_factor", "0.9", "--use_nesterov", "True", "--weight_decay", "1e-4",
+            "--consensus_stepsize", "0.3", "--gossip_impl", impl, "--drop_rate", "0.0"] + list(extra)
+    if "compress" in comm_op:
+        argv += ["--compress_ratio", "0.9"]
+    if comm_op == "quantize_qsgd":
+        argv += ["--quantize_level", "4"]
+    conf = get_args(argv)
+    graph = Graph("ring", 1, 0)
+    torch.manual_seed(0)
+    dl = {"n_tokens": 500} if arch == "rnn_lm" else None
+    model = define_model(conf, graph, data_loader=dl, device=torch.device("cuda"), consistent=False, verbose=False)
+    return conf, model, define_optimizer(conf, model, graph)
+
+
+def _run_cv(impl, use_graph, comm_op, steps=6):
+    from chocosgd_b200.train.engine import TrainStep
+    from chocosgd_b200.train.metrics import Metrics
+
+    conf, model, opt = _build("resnet20", comm_op, impl)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(16, 3, 32, 32, generator=g).pin_memory()
+    y = torch.randint(0, 10, (16,), generator=g).pin_memory()
+    step = TrainStep(model, torch.nn.CrossEntropyLoss(), opt, x, y, metrics=Metrics(model), use_cuda_graph=use_graph,
+                     warmup_iters=1)
+    model.train()
+    losses = []
+    n_calls = steps - 1 if use_graph else steps  # the first graph call runs warm-up (1) + captured (1) steps
+    for _ in range(n_calls):
+        losses.append(float(step(x, y)))
+    opt.finalize()
+    if opt.engine is not None:
+        opt.engine.check()
+    return losses, opt.arena.x.clone(), opt.local_index
+
+
+@pytest.mark.parametrize("comm_op", ["sign", "compress_top_k"])
+def test_graph_replay_equals_eager_fused(comm_op):
+    l_e, x_e, n_e = _run_cv("fused", False, comm_op)
+    l_g, x_g, n_g = _run_cv("fused", True, comm_op)
+    assert n_e == n_g == 6
+    assert abs(l_e[-1] - l_g[-1]) < 2e-2 * abs(l_e[-1]) + 1e-3
+    assert (x_e - x_g).abs().max() < 5e-3
+    assert l_e[-1] < l_e[0]
+
+
+def test_fused_kernels_equal_torch_path_in_training():
+    l_f, x_f, _ = _run_cv("fused", False, "sign")
+    l_t, x_t, _ = _run_cv("nccl", False, "sign")
+    assert abs(l_f[-1] - l_t[-1]) < 2e-2 * abs(l_t[-1]) + 1e-3
+    assert (x_f - x_t).abs().max() < 5e-3
+
+
+def test_lstm_step_with_clipping_in_a_graph():
+    from chocosgd_b200.train.engine import TrainStep
+    from chocosgd_b200.train.metrics import Metrics
+
+    outs = {}
+    for use_graph in (False, True):
+        conf, model, opt = _build("rnn_lm", "quantize_qsgd", "fused",
+                                  ["--rnn_n_hidden", "64", "--rnn_n_layers", "2", "--rnn_clip", "0.4"])
+        g = torch.Generator().manual_seed(2)
+        x = torch.randint(0, 500, (8, 4), generator=g).pin_memory()
+        y = torch.randint(0, 500, (8, 4), generator=g).pin_memory()
+        hidden = tuple(h.cuda() for h in model.init_hidden(4))
+        step = TrainStep(model, torch.nn.CrossEntropyLoss(), opt, x, y, metrics=Metrics(model, "language_modeling"),
+                         use_cuda_graph=use_graph, clip_grad_norm=0.4, hidden=hidden, warmup_iters=1)
+        model.train()
+        n_calls = 5 if use_graph else 6
+        losses = [float(step(x, y)) for _ in range(n_calls)]
+        opt.finalize()
+        opt.engine.check()
+        outs[use_graph] = (losses, opt.arena.x.clone(), float(step.perf[0]))
+    assert outs[False][0][-1] < outs[False][0][0]
+    assert abs(outs[True][0][-1] - outs[False][0][-1]) < 3e-2 * outs[False][0][-1]
+    assert outs[True][2] > 1.0  # perplexity
