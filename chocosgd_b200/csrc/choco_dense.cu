@@ -30,6 +30,41 @@ __device__ __forceinline__ float qsgd_value(const uint32_t* planes, int nbits, i
   return ((planes[nbits] >> bit) & 1u) ? -mag : mag;
 }
 
+// Decode 4 consecutive positions of one group and accumulate  acc[e] += unit * level * sign.
+// Up to 8 plane words (nbits <= 7) stay in registers (fully unrolled, predicated loads).
+__device__ __forceinline__ void qsgd_accumulate4(const uint32_t* __restrict__ src, int nbits, int bit0, int n_valid,
+                                                 float unit, float* acc, float* acc2, float w2) {
+  if (nbits <= 7) {
+    uint32_t pw[8];
+#pragma unroll
+    for (int b = 0; b < 8; ++b) pw[b] = (b <= nbits) ? __ldcg(src + b) : 0u;
+    uint32_t sgn = 0;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) sgn = (b == nbits) ? pw[b] : sgn;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (e < n_valid) {
+        uint32_t lv = 0;
+#pragma unroll
+        for (int b = 0; b < 7; ++b) lv |= (b < nbits) ? (((pw[b] >> (bit0 + e)) & 1u) << b) : 0u;
+        float q = unit * (float)lv;
+        q = ((sgn >> (bit0 + e)) & 1u) ? -q : q;
+        acc[e] += q;
+        if (acc2 != nullptr) acc2[e] += w2 * q;
+      }
+    }
+  } else {
+    uint32_t planes[33];
+    for (int b = 0; b <= nbits; ++b) planes[b] = __ldcg(src + b);
+    for (int e = 0; e < 4; ++e)
+      if (e < n_valid) {
+        const float q = qsgd_value(planes, nbits, bit0 + e, unit);
+        acc[e] += q;
+        if (acc2 != nullptr) acc2[e] += w2 * q;
+      }
+  }
+}
+
 // codec: 0 = qsgd (fused decode + L2 norm), 1 = top-k (first radix histogram), 2 = random-k
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_dense_prep_kernel(const ChocoParams* __restrict__ params,
                                                                        int mode, int codec) {
@@ -96,23 +131,12 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_dense_prep_kernel(const C
     const float4 sv = *reinterpret_cast<const float4*>(p.s + pos);
     float xh_a[4] = {xh.x, xh.y, xh.z, xh.w}, s_a[4] = {sv.x, sv.y, sv.z, sv.w};
     if (do_decode) {
-      uint32_t planes[33];
-      const uint32_t* src = p.outbox + par_prev * PW + body + group * pl;
-      for (int b = 0; b < pl; ++b) planes[b] = __ldcg(src + b);
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (base + e < valid) {
-          const float q = qsgd_value(planes, nbits, bit0 + e, unit_own);
-          xh_a[e] += q;
-          s_a[e] += p.w_self * q;
-        }
-      for (int k = 0; k < n_peers; ++k) {
-        const uint32_t* ps = p.my_inbox[k] + par_prev * PW + body + group * pl;
-        for (int b = 0; b < pl; ++b) planes[b] = __ldcg(ps + b);
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (base + e < valid) s_a[e] += qsgd_value(planes, nbits, bit0 + e, unit_peer[k]);
-      }
+      const int nv = valid - base < 4 ? valid - base : 4;
+      // own payload: x_hat += q, s += w_ii q ; neighbours: s += w_ij q_j (weight folded into unit)
+      qsgd_accumulate4(p.outbox + par_prev * PW + body + group * pl, nbits, bit0, nv, unit_own, xh_a, s_a, p.w_self);
+      for (int k = 0; k < n_peers; ++k)
+        qsgd_accumulate4(p.my_inbox[k] + par_prev * PW + body + group * pl, nbits, bit0, nv, unit_peer[k], s_a, nullptr,
+                         0.f);
       *reinterpret_cast<float4*>(p.x_hat + pos) = make_float4(xh_a[0], xh_a[1], xh_a[2], xh_a[3]);
       *reinterpret_cast<float4*>(p.s + pos) = make_float4(s_a[0], s_a[1], s_a[2], s_a[3]);
     }
@@ -207,29 +231,44 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_kernel(const Ch
   const float s_f = (float)p.qsgd_s;
   const uint32_t ubase = uniform_base(p.seed, t);
 
-  // one warp per group of 32 positions (lane = position inside the group)
-  for (int base = (threadIdx.x >> 5) * 32; base < span; base += CHOCO_THREADS) {
-    const int pos = start + base + lane;
-    const bool ok = base + lane < valid;
-    const float d = ok ? p.scratch_d[pos] : 0.f;
-    uint32_t lv = 0;
-    if (ok && norm > 0.f) {
-      const float lvl = (s_f * fabsf(d)) / norm;
-      const float fl = floorf(lvl);
-      const float u = counter_uniform(ubase, (uint32_t)pos);
-      lv = (uint32_t)fl + ((u < (lvl - fl)) ? 1u : 0u);
+  // one warp per group of 32 positions (lane = position inside the group); four groups are
+  // loaded before any of them is processed so that four loads per lane are in flight
+  const int warp = threadIdx.x >> 5;
+  for (int base0 = warp * 32; base0 < span; base0 += CHOCO_THREADS * 4) {
+    float dv[4];
+    bool okv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int base = base0 + u * CHOCO_THREADS;
+      okv[u] = base < span && base + lane < valid;
+      dv[u] = okv[u] ? p.scratch_d[start + base + lane] : 0.f;
     }
-    uint32_t mine = 0;
-    for (int b = 0; b < nbits; ++b) {
-      const uint32_t w = __ballot_sync(0xffffffffu, (lv >> b) & 1u);
-      if (lane == b) mine = w;
-    }
-    const uint32_t sgn = __ballot_sync(0xffffffffu, ok && d < 0.f);
-    if (lane == nbits) mine = sgn;
-    if (lane < pl) {
-      const int off = par_cur * PW + body + ((start + base) >> 5) * pl + lane;
-      p.outbox[off] = mine;
-      for (int k = 0; k < p.n_peers; ++k) p.peer_inbox[k][off] = mine;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int base = base0 + u * CHOCO_THREADS;
+      if (base >= span) break;  // uniform over the warp
+      const int pos = start + base + lane;
+      const bool ok = okv[u];
+      const float d = dv[u];
+      uint32_t lv = 0;
+      if (ok && norm > 0.f) {
+        const float lvl = (s_f * fabsf(d)) / norm;
+        const float fl = floorf(lvl);
+        const float u01 = counter_uniform(ubase, (uint32_t)pos);
+        lv = (uint32_t)fl + ((u01 < (lvl - fl)) ? 1u : 0u);
+      }
+      uint32_t mine = 0;
+      for (int b = 0; b < nbits; ++b) {
+        const uint32_t w = __ballot_sync(0xffffffffu, (lv >> b) & 1u);
+        if (lane == b) mine = w;
+      }
+      const uint32_t sgn = __ballot_sync(0xffffffffu, ok && d < 0.f);
+      if (lane == nbits) mine = sgn;
+      if (lane < pl) {
+        const int off = par_cur * PW + body + ((start + base) >> 5) * pl + lane;
+        p.outbox[off] = mine;
+        for (int k = 0; k < p.n_peers; ++k) p.peer_inbox[k][off] = mine;
+      }
     }
   }
   __syncthreads();
@@ -286,24 +325,12 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_decode_kernel(const 
       const float4 xh = *reinterpret_cast<const float4*>(p.x_hat + pos);
       const float4 sv = *reinterpret_cast<const float4*>(p.s + pos);
       float xh_a[4] = {xh.x, xh.y, xh.z, xh.w}, s_a[4] = {sv.x, sv.y, sv.z, sv.w};
-      uint32_t planes[33];
-      const uint32_t* src = p.outbox + par_prev * PW + body + group * pl;
-      for (int b = 0; b < pl; ++b) planes[b] = __ldcg(src + b);
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (base + e < valid) {
-          const float q = qsgd_value(planes, nbits, bit0 + e, unit_own);
-          xh_a[e] += q;
-          s_a[e] += p.w_self * q;
-        }
+      const int nv = valid - base < 4 ? valid - base : 4;
+      qsgd_accumulate4(p.outbox + par_prev * PW + body + group * pl, nbits, bit0, nv, unit_own, xh_a, s_a, p.w_self);
       for (int k = 0; k < n_peers; ++k) {
         const float unit =
             p.w_peer[k] * ((sc * __uint_as_float(__ldcg(p.my_inbox[k] + par_prev * PW + seg))) / (float)p.qsgd_s);
-        const uint32_t* ps = p.my_inbox[k] + par_prev * PW + body + group * pl;
-        for (int b = 0; b < pl; ++b) planes[b] = __ldcg(ps + b);
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (base + e < valid) s_a[e] += qsgd_value(planes, nbits, bit0 + e, unit);
+        qsgd_accumulate4(p.my_inbox[k] + par_prev * PW + body + group * pl, nbits, bit0, nv, unit, s_a, nullptr, 0.f);
       }
       *reinterpret_cast<float4*>(p.x_hat + pos) = make_float4(xh_a[0], xh_a[1], xh_a[2], xh_a[3]);
       *reinterpret_cast<float4*>(p.s + pos) = make_float4(s_a[0], s_a[1], s_a[2], s_a[3]);
