@@ -56,29 +56,43 @@ __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnArgs a) {
     mu[0] = m.x; mu[1] = m.y; mu[2] = m.z; mu[3] = m.w;
     is[0] = v.x; is[1] = v.y; is[2] = v.z; is[3] = v.w;
   }
-  for (int r = r0 + rsub; r < r1; r += rpb) {
-    const size_t off = (size_t)r * C + col;
-    const float4 xv = *reinterpret_cast<const float4*>(a.x + off);
-    const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
-    if (!BACKWARD) {
+  // four rows per trip: all their loads are issued before the first accumulate
+  for (int r = r0 + rsub; r < r1; r += 4 * rpb) {
+    float4 xv[4], gv[4], yv[4];
+    bool in[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        s0[e] += xa[e];
-        s1[e] = fmaf(xa[e], xa[e], s1[e]);
+    for (int u = 0; u < 4; ++u) {
+      const int rr = r + u * rpb;
+      in[u] = rr < r1;
+      const size_t off = (size_t)(in[u] ? rr : r) * C + col;
+      xv[u] = *reinterpret_cast<const float4*>(a.x + off);
+      if (BACKWARD) {
+        gv[u] = *reinterpret_cast<const float4*>(a.dy + off);
+        if (a.relu) yv[u] = *reinterpret_cast<const float4*>(a.y + off);
       }
-    } else {
-      const float4 gv = *reinterpret_cast<const float4*>(a.dy + off);
-      float ga[4] = {gv.x, gv.y, gv.z, gv.w};
-      if (a.relu) {
-        const float4 yv = *reinterpret_cast<const float4*>(a.y + off);
-        const float ya[4] = {yv.x, yv.y, yv.z, yv.w};
+    }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) ga[e] = ya[e] > 0.f ? ga[e] : 0.f;
-      }
+    for (int u = 0; u < 4; ++u) {
+      if (!in[u]) continue;
+      const float xa[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+      if (!BACKWARD) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        s0[e] += ga[e];
-        s1[e] = fmaf(ga[e], (xa[e] - mu[e]) * is[e], s1[e]);
+        for (int e = 0; e < 4; ++e) {
+          s0[e] += xa[e];
+          s1[e] = fmaf(xa[e], xa[e], s1[e]);
+        }
+      } else {
+        float ga[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
+        if (a.relu) {
+          const float ya[4] = {yv[u].x, yv[u].y, yv[u].z, yv[u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) ga[e] = ya[e] > 0.f ? ga[e] : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s0[e] += ga[e];
+          s1[e] = fmaf(ga[e], (xa[e] - mu[e]) * is[e], s1[e]);
+        }
       }
     }
   }
@@ -218,7 +232,7 @@ static int grid_for(long long n4) {
 
 extern "C" int bn_reduce_grid(int P, int C) {
   const int rpb = BN_THREADS / (C / 4);
-  int g = (P + rpb * 8 - 1) / (rpb * 8);  // at least 8 passes of rows per CTA
+  int g = (P + rpb * 4 - 1) / (rpb * 4);  // one 4-row trip per thread when the tensor is small
   if (g > 148 * 4) g = 148 * 4;
   return g < 1 ? 1 : g;
 }

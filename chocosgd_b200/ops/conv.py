@@ -1,7 +1,8 @@
 """Native convolution path: 3x3 / stride 1 / pad 1 NHWC fp32 convolutions run the tcgen05
 implicit-GEMM kernel (``csrc/conv_sm100.cu``) for the forward pass and for the input gradient
-(same kernel on dy with the flipped filter).  The weight gradient and all other convolution
-shapes (strided, 1x1, first layer with 3 input channels) use the library convolution."""
+(same kernel on dy with the flipped filter), and ``csrc/conv_wgrad_sm100.cu`` for the weight
+gradient when C_in == C_out in {16, 32, 64}.  All other convolution shapes (strided, 1x1, first
+layer with 3 input channels) use the library convolution."""
 from __future__ import annotations
 
 import ctypes
@@ -22,6 +23,11 @@ def _declare():
         lib.conv_flip_weights.argtypes = [vp, vp, i, i, vp]
         lib.conv_flip_weights.restype = i
         lib.conv3x3_last_error.restype = i
+        lib.conv3x3_wgrad_tf32.argtypes = [vp, vp, vp, i, i, i, i, vp]
+        lib.conv3x3_wgrad_tf32.restype = i
+        lib.conv3x3_wgrad_supported.argtypes = [i, i, i, i, i]
+        lib.conv3x3_wgrad_supported.restype = i
+        lib.conv3x3_wgrad_last_error.restype = i
         lib._conv_declared = True
     return lib
 
@@ -53,7 +59,19 @@ def conv3x3(x, w_krsc_ptr_tensor, cout, relu=False):
 
 
 def last_error() -> int:
-    return _declare().conv3x3_last_error()
+    lib = _declare()
+    return lib.conv3x3_last_error() | lib.conv3x3_wgrad_last_error()
+
+
+def conv3x3_wgrad(x, dy, weight):
+    """dW (same memory order as ``weight``: [C_out, 3, 3, C_in]) by the tcgen05 kernel."""
+    lib = _declare()
+    n, c, h, w = x.shape
+    dw = torch.zeros_like(weight)
+    rc = lib.conv3x3_wgrad_tf32(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), n, h, w, c, _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"conv3x3_wgrad_tf32 failed ({rc})")
+    return dw
 
 
 class _Conv3x3Fn(torch.autograd.Function):
@@ -75,7 +93,12 @@ class _Conv3x3Fn(torch.autograd.Function):
             if rc != 0:
                 raise RuntimeError(f"conv_flip_weights failed ({rc})")
             dx = conv3x3(dy, flipped, cin)
-        if ctx.needs_input_grad[1]:
+        n, _, h, w = x.shape
+        from . import nn as native_nn
+
+        if ctx.needs_input_grad[1] and native_nn.native_enabled("wgrad") and lib.conv3x3_wgrad_supported(n, h, w, cin, cout):
+            dw = conv3x3_wgrad(x, dy, weight)
+        elif ctx.needs_input_grad[1]:
             dw = torch.ops.aten.convolution_backward(
                 dy, x, weight, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1, (False, True, False))[1]
         return dx, dw

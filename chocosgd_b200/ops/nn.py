@@ -11,7 +11,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False}
+_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False, "wgrad": False}
 
 
 def set_native(enabled: bool = True, which=("linear", "conv", "lstm", "bn")):
@@ -23,7 +23,7 @@ def available_kinds():
     """Kinds of layers whose native kernels are built into this tree."""
     import importlib.util
 
-    kinds = ["bn", "linear"]
+    kinds = ["bn", "linear", "wgrad"]
     for kind, mod in (("conv", "conv"), ("lstm", "lstm")):
         if importlib.util.find_spec(f"{__package__}.{mod}") is not None:
             kinds.append(kind)

@@ -9,8 +9,9 @@ SHAPES = [(4, 16, 32, 32, 16), (2, 32, 16, 16, 32), (4, 64, 8, 8, 64), (8, 32, 3
           (128, 16, 32, 32, 16)]
 
 
+@pytest.mark.parametrize("wgrad", [False, True])
 @pytest.mark.parametrize("n,cin,h,w,cout", SHAPES)
-def test_conv3x3_forward_and_dgrad(n, cin, h, w, cout):
+def test_conv3x3_forward_and_dgrad(n, cin, h, w, cout, wgrad):
     from chocosgd_b200.ops import nn as nnn
     from chocosgd_b200.ops.conv import conv_supported, last_error
 
@@ -22,7 +23,7 @@ def test_conv3x3_forward_and_dgrad(n, cin, h, w, cout):
     ref = F.conv2d(x, conv.weight, padding=1)
     g = torch.randn_like(ref)
     gx_ref, gw_ref = torch.autograd.grad(ref, (x, conv.weight), g)
-    nnn.set_native(True, which=("conv",))
+    nnn.set_native(True, which=("conv", "wgrad") if wgrad else ("conv",))
     try:
         out = conv(x)
         gx, gw = torch.autograd.grad(out, (x, conv.weight), g)
