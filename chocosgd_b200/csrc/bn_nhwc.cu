@@ -13,6 +13,7 @@
 // Layout: x is [P, C] with C contiguous, C a multiple of 4, C/4 a power of two <= 256.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define BN_THREADS 256
 
@@ -102,21 +103,23 @@ __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnArgs a) {
     sh[threadIdx.x * 8 + 4 + e] = s1[e];
   }
   __syncthreads();
-  if (threadIdx.x < tpr) {
-    float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int j = 0; j < rpb; ++j) {
-      const float* p = sh + (j * tpr + threadIdx.x) * 8;
+  // fixed-shape tree over the rows held by this CTA (rpb is a power of two): reproducible
+  for (int stride = rpb >> 1; stride > 0; stride >>= 1) {
+    if (rsub < stride) {
+      float* mine = sh + threadIdx.x * 8;
+      const float* other = sh + (threadIdx.x + stride * tpr) * 8;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        t0[e] += p[e];
-        t1[e] += p[4 + e];
-      }
+      for (int e = 0; e < 8; ++e) mine[e] += other[e];
     }
+    __syncthreads();
+  }
+  if (threadIdx.x < tpr) {
     float* dst = a.partial + (size_t)blockIdx.x * 2 * C;
+    const float* p = sh + threadIdx.x * 8;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      dst[col + e] = t0[e];
-      dst[C + col + e] = t1[e];
+      dst[col + e] = p[e];
+      dst[C + col + e] = p[4 + e];
     }
   }
   __syncthreads();
@@ -233,7 +236,12 @@ static int grid_for(long long n4) {
 extern "C" int bn_reduce_grid(int P, int C) {
   const int rpb = BN_THREADS / (C / 4);
   int g = (P + rpb * 4 - 1) / (rpb * 4);  // one 4-row trip per thread when the tensor is small
-  if (g > 148 * 4) g = 148 * 4;
+  static int cap = 0;                      // CTAs: enough to fill the machine, few enough that the
+  if (cap == 0) {                          // last CTA's pass over the partials stays short
+    const char* e = getenv("CHOCO_BN_GRID_CAP");
+    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : 296;
+  }
+  if (g > cap) g = cap;
   return g < 1 ? 1 : g;
 }
 

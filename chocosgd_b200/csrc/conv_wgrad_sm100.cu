@@ -6,10 +6,9 @@
 // dY tiles ([pixels, C_out], channel contiguous) and, per filter tap, the shifted X tile fetched by a 4-d
 // TMA box (zero fill = padding) are used exactly as they lie in memory; no transpose, no im2col.
 // The only shared-memory layout the tensor core accepts for MN-major 32-bit operands is the 128-byte
-// swizzle with 32-byte units, which TMA produces (SWIZZLE_128B_ATOM_32B).  Rows must be 32 floats wide:
-// with 16 channels two adjacent pixels are viewed as one 32-float row (a pure reinterpretation of the
-// NHWC bytes); the products of "pixel 0 of the pair" with "pixel 1 of the pair" land in off-diagonal
-// 16x16 blocks of the accumulator that the epilogue ignores.
+// swizzle with 32-byte units, which TMA produces (SWIZZLE_128B_ATOM_32B) for rows of exactly 32 floats:
+// the kernel therefore covers C = 32 and C = 64 (two 32-channel blocks); 16-channel layers use the
+// library weight gradient.
 //
 // One CTA reduces a contiguous range of 128-pixel tiles: the dY tile is loaded once per tile and
 // multiplied with the 9 shifted X tiles into 9 accumulators of 32 columns in TMEM (M = 128 with the
@@ -19,7 +18,6 @@
 
 #define WG_THREADS 192
 #define WG_BSTAGES 6
-#define WG_TILE_BYTES 16384   // 128 rows x 128 B (or 64 pair-rows x 128 B = 8 KiB when C = 16)
 
 struct WgradArgs {
   float* dw;       // [C, 9, C]
@@ -34,8 +32,8 @@ __global__ void __launch_bounds__(WG_THREADS, 1)
 conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x, WgradArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr bool PAIR = (C == 16);
-  constexpr int KROWS = PAIR ? 64 : 128;            // reduction rows per tile (pixel pairs or pixels)
+  static_assert(C == 32 || C == 64, "rows of 32 floats are required");
+  constexpr int KROWS = 128;                        // reduction rows (pixels) per tile
   constexpr int TILE = KROWS * 128;                 // bytes of one 32-float-wide operand block
   constexpr int A_BLOCKS = C == 64 ? 2 : 1;         // 32-float blocks of dY channels
   constexpr int A_BYTES = A_BLOCKS * TILE;
@@ -86,12 +84,12 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
         if (i >= 2 && !mbar_wait(a_empty + ab, ((i >> 1) - 1) & 1)) { *abort_flag = 1; break; }
         mbar_expect_tx(a_full + ab, A_BYTES);
         for (int j = 0; j < A_BLOCKS; ++j)
-          tma_load_2d(sA + ab * A_BYTES + j * TILE, &map_dy, a_full + ab, 32 * j, PAIR ? p0 / 2 : p0);
+          tma_load_2d(sA + ab * A_BYTES + j * TILE, &map_dy, a_full + ab, 32 * j, p0);
         for (int tap = 0; tap < 9; ++tap, ++bcount) {
           const int s = bcount % WG_BSTAGES;
           if (bcount >= WG_BSTAGES && !mbar_wait(b_empty + s, ((bcount / WG_BSTAGES) - 1) & 1)) { *abort_flag = 1; break; }
           mbar_expect_tx(b_full + s, TILE);
-          tma_load_4d(sB + s * TILE, &map_x, b_full + s, PAIR ? 0 : ci0, tap % 3 - 1, h0 + tap / 3 - 1, n0);
+          tma_load_4d(sB + s * TILE, &map_x, b_full + s, ci0, tap % 3 - 1, h0 + tap / 3 - 1, n0);
         }
       }
     } else if (warp == 5 && lane == 0) {
@@ -130,25 +128,16 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
       constexpr int REAL_ROWS = C == 64 ? 64 : 32;
       if (ok && warp * 32 < REAL_ROWS) {
         tc_fence_after();
-        const int m = warp * 32 + lane;                     // accumulator row
-        const int co = PAIR ? (m & 15) : m;
-        const int jrow = PAIR ? (m >> 4) : 0;               // which pixel of the pair this row belongs to
+        const int co = warp * 32 + lane;                    // accumulator row = output channel
 #pragma unroll 1
         for (int tap = 0; tap < 9; ++tap) {
 #pragma unroll 1
           for (int c = 0; c < 32; c += 16) {
             uint32_t v[16];
             tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(tap * 32 + c), v);
-            if (PAIR) {
-              if ((c >> 4) != jrow) continue;                // keep the diagonal 16 x 16 block only
-              float* dst = g.dw + ((size_t)co * 9 + tap) * C;
+            float* dst = g.dw + ((size_t)co * 9 + tap) * C + ci0 + c;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
-            } else {
-              float* dst = g.dw + ((size_t)co * 9 + tap) * C + ci0 + c;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
-            }
+            for (int j = 0; j < 16; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
           }
         }
       }
@@ -185,7 +174,7 @@ extern "C" int conv3x3_wgrad_last_error() {
 }
 
 extern "C" int conv3x3_wgrad_supported(int N, int H, int W, int Cin, int Cout) {
-  if (Cin != Cout || !(Cin == 16 || Cin == 32 || Cin == 64)) return 0;
+  if (Cin != Cout || !(Cin == 32 || Cin == 64)) return 0;
   if (!(W == 8 || W == 16 || W == 32)) return 0;
   int th = 128 / W;
   if (th > H) th = H;
@@ -197,7 +186,7 @@ extern "C" int conv3x3_wgrad_supported(int N, int H, int W, int Cin, int Cout) {
 
 template <int C>
 static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const WgradArgs& g, dim3 grid, cudaStream_t st) {
-  constexpr int tile = (C == 16 ? 64 : 128) * 128;
+  constexpr int tile = 128 * 128;
   constexpr int smem = 2 * (C == 64 ? 2 : 1) * tile + WG_BSTAGES * tile + 1024 + 256;
   static bool configured = false;
   if (!configured) {
@@ -216,19 +205,18 @@ extern "C" int conv3x3_wgrad_tf32(const void* x, const void* dy, void* dw, int N
   if (th > H) th = H;
   const int tn = 128 / (W * th);
   const long long P = (long long)N * H * W;
-  const bool pair = C == 16;
   CUtensorMap mdy, mx;
   {
-    cuuint64_t dims[2] = {(cuuint64_t)(pair ? 32 : C), (cuuint64_t)(pair ? P / 2 : P)};
-    cuuint64_t str[1] = {(cuuint64_t)(pair ? 32 : C) * 4};
-    cuuint32_t box[2] = {32, (cuuint32_t)(pair ? 64 : 128)};
+    cuuint64_t dims[2] = {(cuuint64_t)C, (cuuint64_t)P};
+    cuuint64_t str[1] = {(cuuint64_t)C * 4};
+    cuuint32_t box[2] = {32, 128};
     int rc = tc_make_map(&mdy, dy, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (rc) return rc;
   }
   {
     cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
     cuuint64_t str[3] = {(cuuint64_t)C * 4, (cuuint64_t)W * C * 4, (cuuint64_t)H * W * C * 4};
-    cuuint32_t box[4] = {(cuuint32_t)(pair ? 16 : 32), (cuuint32_t)W, (cuuint32_t)th, (cuuint32_t)tn};
+    cuuint32_t box[4] = {32, (cuuint32_t)W, (cuuint32_t)th, (cuuint32_t)tn};
     int rc = tc_make_map(&mx, x, 4, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (rc) return rc;
   }
@@ -240,7 +228,6 @@ extern "C" int conv3x3_wgrad_tf32(const void* x, const void* dy, void* dw, int N
   g.n_tiles = (N / tn) * (H / th);
   g.tiles_per_cta = (g.n_tiles + 147) / 148;
   dim3 grid((g.n_tiles + g.tiles_per_cta - 1) / g.tiles_per_cta, C == 64 ? 2 : 1);
-  if (C == 16) return launch_wgrad<16>(mdy, mx, g, grid, st);
   if (C == 32) return launch_wgrad<32>(mdy, mx, g, grid, st);
   return launch_wgrad<64>(mdy, mx, g, grid, st);
 }
