@@ -42,7 +42,7 @@ def parse():
     p.add_argument("--comm_op", default="compress_top_k",
                    choices=("compress_top_k", "sign", "quantize_qsgd", "compress_random_k"))
     p.add_argument("--no_graph", action="store_true")
-    p.add_argument("--native_layers", default="auto", choices=("auto", "on", "off", "bn"))
+    p.add_argument("--native_layers", default="auto", choices=("auto", "on", "off", "bn", "conv"))
     return p.parse_args()
 
 
@@ -168,6 +168,8 @@ def run_ours(args, rank, world, local):
     torch.backends.cudnn.benchmark = True
     if args.native_layers == "bn":
         native_nn.set_native(True, which=("bn", "linear"))
+    elif args.native_layers == "conv":
+        native_nn.set_native(True, which=("bn", "linear", "conv"))
     elif args.native_layers != "off":
         native_nn.set_native(True, which=native_nn.available_kinds())
     model = define_model(conf, graph, device=device, verbose=False)

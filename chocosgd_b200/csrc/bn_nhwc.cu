@@ -138,11 +138,27 @@ __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnArgs a) {
     const int nsub = BN_THREADS / cw;
     const int c = cbase + threadIdx.x % cw, sub = threadIdx.x / cw;
     double t0 = 0.0, t1 = 0.0;
-    if (sub < nsub)
-      for (unsigned b = sub; b < gridDim.x; b += nsub) {
+    if (sub < nsub) {
+      // four independent loads per trip (the adds stay in a fixed order)
+      unsigned b = sub;
+      for (; b + 3 * nsub < gridDim.x; b += 4 * nsub) {
+        float u0[4], u1[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          u0[q] = __ldcg(a.partial + (size_t)(b + q * nsub) * 2 * C + c);
+          u1[q] = __ldcg(a.partial + (size_t)(b + q * nsub) * 2 * C + C + c);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          t0 += (double)u0[q];
+          t1 += (double)u1[q];
+        }
+      }
+      for (; b < gridDim.x; b += nsub) {
         t0 += (double)__ldcg(a.partial + (size_t)b * 2 * C + c);
         t1 += (double)__ldcg(a.partial + (size_t)b * 2 * C + C + c);
       }
+    }
     __syncthreads();
     shd[threadIdx.x * 2] = t0;
     shd[threadIdx.x * 2 + 1] = t1;
@@ -239,7 +255,7 @@ extern "C" int bn_reduce_grid(int P, int C) {
   static int cap = 0;                      // CTAs: enough to fill the machine, few enough that the
   if (cap == 0) {                          // last CTA's pass over the partials stays short
     const char* e = getenv("CHOCO_BN_GRID_CAP");
-    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : 296;
+    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : 148;
   }
   if (g > cap) g = cap;
   return g < 1 ? 1 : g;

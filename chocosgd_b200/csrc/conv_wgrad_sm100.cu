@@ -12,15 +12,15 @@
 //
 // One CTA reduces a contiguous range of 128-pixel tiles: the dY tile is loaded once per tile and
 // multiplied with the 9 shifted X tiles into 9 accumulators of 32 columns in TMEM (M = 128 with the
-// 32- or 64-row operand replicated, N = 32).  The epilogue adds the partial result into dW with fp32
-// atomics (dW is zeroed by the caller; CTAs split the pixel range).
+// 32- or 64-row operand replicated, N = 32).  Each CTA stores its partial dW into its own slice of a
+// scratch buffer; a second small kernel adds the slices in a fixed order (reproducible, no atomics).
 #include "tc_common.cuh"
 
 #define WG_THREADS 192
 #define WG_BSTAGES 6
 
 struct WgradArgs {
-  float* dw;       // [C, 9, C]
+  float* dw;       // partial results: [gridDim.x][C, 9, C]
   int* error;
   int H, W, C;
   int TH, TN, tiles_h, n_tiles;
@@ -135,9 +135,11 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
           for (int c = 0; c < 32; c += 16) {
             uint32_t v[16];
             tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(tap * 32 + c), v);
-            float* dst = g.dw + ((size_t)co * 9 + tap) * C + ci0 + c;
+            float* dst = g.dw + (size_t)blockIdx.x * (C * 9 * C) + ((size_t)co * 9 + tap) * C + ci0 + c;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) atomicAdd(dst + j, __uint_as_float(v[j]));
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
           }
         }
       }
@@ -198,8 +200,27 @@ static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const Wgr
   return (int)cudaGetLastError();
 }
 
-// dw [C, 3, 3, C] must be zero on entry.  x, dy: [N, H, W, C] fp32 NHWC.
-extern "C" int conv3x3_wgrad_tf32(const void* x, const void* dy, void* dw, int N, int H, int W, int C, cudaStream_t st) {
+// dw[i] = sum over slices of partial[slice][i], slices added in index order
+__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, int n_parts, int n, float* __restrict__ dw) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0.f;
+  for (int s = 0; s < n_parts; ++s) acc += partial[(size_t)s * n + i];
+  dw[i] = acc;
+}
+
+extern "C" int conv3x3_wgrad_parts(int N, int H, int W) {
+  int th = 128 / W;
+  if (th > H) th = H;
+  const int tn = 128 / (W * th);
+  const int n_tiles = (N / tn) * (H / th);
+  const int per = (n_tiles + 147) / 148;
+  return (n_tiles + per - 1) / per;
+}
+
+// x, dy: [N, H, W, C] fp32 NHWC; dw: [C, 3, 3, C]; scratch: conv3x3_wgrad_parts() * 9 C C floats.
+extern "C" int conv3x3_wgrad_tf32(const void* x, const void* dy, void* dw, void* scratch, int N, int H, int W, int C,
+                                  cudaStream_t st) {
   if (!conv3x3_wgrad_supported(N, H, W, C, C)) return -1;
   int th = 128 / W;
   if (th > H) th = H;
@@ -221,13 +242,17 @@ extern "C" int conv3x3_wgrad_tf32(const void* x, const void* dy, void* dw, int N
     if (rc) return rc;
   }
   WgradArgs g;
-  g.dw = reinterpret_cast<float*>(dw);
+  g.dw = reinterpret_cast<float*>(scratch);
   g.error = wg_error_word();
   if (g.error == nullptr) return -13;
   g.H = H; g.W = W; g.C = C; g.TH = th; g.TN = tn; g.tiles_h = H / th;
   g.n_tiles = (N / tn) * (H / th);
   g.tiles_per_cta = (g.n_tiles + 147) / 148;
   dim3 grid((g.n_tiles + g.tiles_per_cta - 1) / g.tiles_per_cta, C == 64 ? 2 : 1);
-  if (C == 32) return launch_wgrad<32>(mdy, mx, g, grid, st);
-  return launch_wgrad<64>(mdy, mx, g, grid, st);
+  const int rc = C == 32 ? launch_wgrad<32>(mdy, mx, g, grid, st) : launch_wgrad<64>(mdy, mx, g, grid, st);
+  if (rc) return rc;
+  const int n = C * 9 * C;
+  wgrad_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(reinterpret_cast<const float*>(scratch), (int)grid.x, n,
+                                                       reinterpret_cast<float*>(dw));
+  return (int)cudaGetLastError();
 }

@@ -23,7 +23,9 @@ def _declare():
         lib.conv_flip_weights.argtypes = [vp, vp, i, i, vp]
         lib.conv_flip_weights.restype = i
         lib.conv3x3_last_error.restype = i
-        lib.conv3x3_wgrad_tf32.argtypes = [vp, vp, vp, i, i, i, i, vp]
+        lib.conv3x3_wgrad_tf32.argtypes = [vp, vp, vp, vp, i, i, i, i, vp]
+        lib.conv3x3_wgrad_parts.argtypes = [i, i, i]
+        lib.conv3x3_wgrad_parts.restype = i
         lib.conv3x3_wgrad_tf32.restype = i
         lib.conv3x3_wgrad_supported.argtypes = [i, i, i, i, i]
         lib.conv3x3_wgrad_supported.restype = i
@@ -67,8 +69,10 @@ def conv3x3_wgrad(x, dy, weight):
     """dW (same memory order as ``weight``: [C_out, 3, 3, C_in]) by the tcgen05 kernel."""
     lib = _declare()
     n, c, h, w = x.shape
-    dw = torch.zeros_like(weight)
-    rc = lib.conv3x3_wgrad_tf32(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), n, h, w, c, _lib.stream_ptr())
+    dw = torch.empty_like(weight)
+    scratch = torch.empty(lib.conv3x3_wgrad_parts(n, h, w) * 9 * c * c, dtype=torch.float32, device=x.device)
+    rc = lib.conv3x3_wgrad_tf32(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, h, w, c,
+                                _lib.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"conv3x3_wgrad_tf32 failed ({rc})")
     return dw
