@@ -317,8 +317,19 @@ class LogisticDecentralizedSGD:
         WmI = W - torch.eye(n, dtype=dt, device=dev)
         lam = p.regularizer or 0.0
 
+        A32 = y32 = None
+        if dev.type == "cuda" and d % 4 == 0:
+            try:  # hand-written full-data loss kernel (fp32 features, fp64 accumulation)
+                from ..ops.logreg import logreg_loss
+
+                A32, y32 = At.float().contiguous(), yt.float().contiguous()
+            except Exception:
+                A32 = None
+
         def loss_of(xe):
             xm = xe.mean(dim=1)
+            if A32 is not None:
+                return logreg_loss(A32, y32, xm.contiguous(), lam)
             out = torch.nn.functional.softplus(-yt * (At @ xm)).sum() / num_samples
             return float(out + lam * (xm * xm).sum() / 2)
 

@@ -205,7 +205,8 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, int n_par
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float acc = 0.f;
-  for (int s = 0; s < n_parts; ++s) acc += partial[(size_t)s * n + i];
+#pragma unroll 8
+  for (int s = 0; s < n_parts; ++s) acc += __ldcg(partial + (size_t)s * n + i);
   dw[i] = acc;
 }
 

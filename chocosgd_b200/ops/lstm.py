@@ -1,0 +1,102 @@
+"""Native LSTM layer stack: gate GEMMs + fused cell kernels (``csrc/lstm_cell.cu``).
+
+Per layer the input projection of all time steps is ONE GEMM (the tcgen05 kernel when the
+dimensions are multiples of 4, the library GEMM otherwise, e.g. hidden size 650); each time step is
+one recurrent GEMM plus one fused pointwise kernel.  Backward runs the cell kernel in reverse and
+forms dW_ih, dW_hh and dX with three GEMMs over the whole sequence.  Same parameters, gate order and
+results as ``torch.nn.LSTM`` (``dl_code/pcode/models/rnn_lm.py:29,53-61``); dropout between layers as there."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .gemm import gemm
+
+
+def _declare():
+    lib = _lib.load()
+    if not getattr(lib, "_lstm_declared", False):
+        vp, i = ctypes.c_void_p, ctypes.c_int
+        lib.lstm_cell_fwd.argtypes = [vp, vp, vp, vp, i, i, vp]
+        lib.lstm_cell_bwd.argtypes = [vp, vp, vp, vp, vp, i, i, vp]
+        lib.lstm_cell_fwd.restype = lib.lstm_cell_bwd.restype = i
+        lib._lstm_declared = True
+    return lib
+
+
+def _mm_nt(a, b):
+    """a [M, K] @ b[N, K]^T."""
+    if a.shape[1] % 4 == 0 and b.shape[0] % 4 == 0 and a.is_contiguous() and b.is_contiguous():
+        return gemm(a, b)
+    return a @ b.t()
+
+
+class _LSTMLayerFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, h0, c0, w_ih, w_hh, b_ih, b_hh):
+        lib = _declare()
+        T, B, _ = x.shape
+        H = w_hh.shape[1]
+        gates = _mm_nt(x.reshape(T * B, -1).contiguous(), w_ih).add_(b_ih + b_hh).view(T, B, 4 * H)
+        hs = torch.empty(T + 1, B, H, dtype=x.dtype, device=x.device)
+        cs = torch.empty(T + 1, B, H, dtype=x.dtype, device=x.device)
+        hs[0].copy_(h0)
+        cs[0].copy_(c0)
+        sp = _lib.stream_ptr()
+        for t in range(T):
+            gates[t].addmm_(hs[t], w_hh.t())
+            _lib.check(lib.lstm_cell_fwd(_lib.ptr(gates[t]), _lib.ptr(cs[t]), _lib.ptr(cs[t + 1]), _lib.ptr(hs[t + 1]),
+                                         B, H, sp), "lstm_cell_fwd")
+        ctx.save_for_backward(x, w_ih, w_hh, gates, hs, cs)
+        return hs[1:], hs[T].clone(), cs[T].clone()
+
+    @staticmethod
+    def backward(ctx, d_out, d_hn, d_cn):
+        lib = _declare()
+        x, w_ih, w_hh, gates, hs, cs = ctx.saved_tensors
+        T, B, _ = x.shape
+        H = w_hh.shape[1]
+        dgates = gates.clone()  # activations in, d(pre-activations) out
+        dh = d_hn.clone() if d_hn is not None else torch.zeros(B, H, dtype=x.dtype, device=x.device)
+        dc = d_cn.clone() if d_cn is not None else torch.zeros(B, H, dtype=x.dtype, device=x.device)
+        d_out = d_out.contiguous() if d_out is not None else None
+        sp = _lib.stream_ptr()
+        for t in range(T - 1, -1, -1):
+            if d_out is not None:
+                dh = dh + d_out[t]
+            _lib.check(lib.lstm_cell_bwd(_lib.ptr(dgates[t]), _lib.ptr(cs[t]), _lib.ptr(cs[t + 1]), _lib.ptr(dh),
+                                         _lib.ptr(dc), B, H, sp), "lstm_cell_bwd")
+            dh = dgates[t] @ w_hh
+        dg2 = dgates.view(T * B, 4 * H)
+        dx = (dg2 @ w_ih).view_as(x)
+        dw_ih = dg2.t() @ x.reshape(T * B, -1)
+        dw_hh = dg2.t() @ hs[:-1].reshape(T * B, H)
+        db = dg2.sum(dim=0)
+        return dx, dh, dc, dw_ih, dw_hh, db, db.clone()
+
+
+def lstm_supported(m, x) -> bool:
+    return (x.dim() == 3 and not m.bidirectional and not m.batch_first and m.bias and m.proj_size == 0
+            and x.dtype == torch.float32 and x.is_cuda)
+
+
+def lstm_native(m, x, hx=None):
+    T, B, _ = x.shape
+    L, H = m.num_layers, m.hidden_size
+    if hx is None:
+        z = x.new_zeros(L, B, H)
+        hx = (z, z.clone())
+    h0, c0 = hx
+    out, hn, cn = x, [], []
+    for l in range(L):
+        w_ih, w_hh = getattr(m, f"weight_ih_l{l}"), getattr(m, f"weight_hh_l{l}")
+        b_ih, b_hh = getattr(m, f"bias_ih_l{l}"), getattr(m, f"bias_hh_l{l}")
+        out, h, c = _LSTMLayerFn.apply(out.contiguous(), h0[l], c0[l], w_ih, w_hh, b_ih, b_hh)
+        hn.append(h)
+        cn.append(c)
+        if m.dropout > 0 and m.training and l < L - 1:
+            out = F.dropout(out, p=m.dropout, training=True)
+    return out, (torch.stack(hn), torch.stack(cn))
