@@ -255,7 +255,7 @@ extern "C" int bn_reduce_grid(int P, int C) {
   static int cap = 0;                      // CTAs: enough to fill the machine, few enough that the
   if (cap == 0) {                          // last CTA's pass over the partials stays short
     const char* e = getenv("CHOCO_BN_GRID_CAP");
-    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : 148;
+    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : 74;
   }
   if (g > cap) g = cap;
   return g < 1 ? 1 : g;

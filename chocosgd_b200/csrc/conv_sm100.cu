@@ -140,6 +140,28 @@ __global__ void conv_flip_weights_kernel(const float* __restrict__ w, float* __r
   }
 }
 
+// all registered layers in one launch: table[l] = {w, out, cout, cin}; gridDim.y = layer
+struct FlipEntry {
+  const float* w;
+  float* out;
+  int cout, cin;
+};
+
+__global__ void conv_flip_weights_multi_kernel(const FlipEntry* __restrict__ table) {
+  const FlipEntry e = table[blockIdx.y];
+  const int total = e.cout * 9 * e.cin;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int co = i % e.cout, tap = (i / e.cout) % 9, ci = i / (9 * e.cout);
+    e.out[i] = e.w[(co * 9 + (8 - tap)) * e.cin + ci];
+  }
+}
+
+extern "C" int conv_flip_weights_multi(const void* table, int n_layers, int max_elems, cudaStream_t st) {
+  dim3 grid((max_elems + 255) / 256 > 64 ? 64 : (max_elems + 255) / 256, n_layers);
+  conv_flip_weights_multi_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const FlipEntry*>(table));
+  return (int)cudaGetLastError();
+}
+
 extern "C" int conv_flip_weights(const void* w, void* out, int cout, int cin, cudaStream_t st) {
   const int total = cout * 9 * cin;
   conv_flip_weights_kernel<<<(total + 255) / 256, 256, 0, st>>>(reinterpret_cast<const float*>(w),

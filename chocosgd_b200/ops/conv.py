@@ -30,6 +30,8 @@ def _declare():
         lib.conv3x3_wgrad_supported.argtypes = [i, i, i, i, i]
         lib.conv3x3_wgrad_supported.restype = i
         lib.conv3x3_wgrad_last_error.restype = i
+        lib.conv_flip_weights_multi.argtypes = [vp, i, i, vp]
+        lib.conv_flip_weights_multi.restype = i
         lib._conv_declared = True
     return lib
 
@@ -78,6 +80,55 @@ def conv3x3_wgrad(x, dy, weight):
     return dw
 
 
+class FlippedWeights:
+    """Flipped filters of all native convolutions of a model, refreshed by ONE kernel per step.
+
+    ``refresh()`` is called at the start of a training step (the weights do not change between the
+    forward and the backward of a step); ``get(weight)`` returns the buffer for the input-gradient
+    convolution, or None when the cache is not valid (the layer then flips its own filter)."""
+
+    def __init__(self, model):
+        import numpy as np
+
+        self.entries = {}
+        rows = []
+        for m in model.modules():
+            if (isinstance(m, torch.nn.Conv2d) and m.kernel_size == (3, 3) and m.stride == (1, 1) and m.weight.is_cuda
+                    and m.weight.dtype == torch.float32 and m.bias is None and m.groups == 1
+                    and m.weight.is_contiguous(memory_format=torch.channels_last)
+                    and m.in_channels % 16 == 0 and m.out_channels % 16 == 0):
+                buf = torch.empty(m.weight.numel(), dtype=torch.float32, device=m.weight.device)
+                self.entries[m.weight.data_ptr()] = buf
+                rows.append((m.weight.data_ptr(), buf.data_ptr(), m.out_channels, m.in_channels))
+        self.n = len(rows)
+        self.valid = False
+        if self.n:
+            dt = np.dtype([("w", np.uint64), ("out", np.uint64), ("cout", np.int32), ("cin", np.int32)])
+            host = np.array(rows, dtype=dt)
+            dev = next(iter(self.entries.values())).device
+            self.table = torch.from_numpy(host.view(np.uint8).copy()).to(dev)
+            self.max_elems = max(r[2] * r[3] * 9 for r in rows)
+
+    def refresh(self):
+        if not self.n:
+            return
+        rc = _declare().conv_flip_weights_multi(_lib.ptr(self.table), self.n, self.max_elems, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"conv_flip_weights_multi failed ({rc})")
+        self.valid = True
+
+    def get(self, weight):
+        return self.entries.get(weight.data_ptr()) if self.valid else None
+
+
+_ACTIVE_FLIPS = None
+
+
+def set_active_flips(f):
+    global _ACTIVE_FLIPS
+    _ACTIVE_FLIPS = f
+
+
 class _Conv3x3Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight):
@@ -92,10 +143,12 @@ class _Conv3x3Fn(torch.autograd.Function):
         cout, cin = weight.shape[0], weight.shape[1]
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            flipped = torch.empty(cin * 9 * cout, dtype=torch.float32, device=x.device)
-            rc = lib.conv_flip_weights(_lib.ptr(weight), _lib.ptr(flipped), cout, cin, _lib.stream_ptr())
-            if rc != 0:
-                raise RuntimeError(f"conv_flip_weights failed ({rc})")
+            flipped = _ACTIVE_FLIPS.get(weight) if _ACTIVE_FLIPS is not None else None
+            if flipped is None:
+                flipped = torch.empty(cin * 9 * cout, dtype=torch.float32, device=x.device)
+                rc = lib.conv_flip_weights(_lib.ptr(weight), _lib.ptr(flipped), cout, cin, _lib.stream_ptr())
+                if rc != 0:
+                    raise RuntimeError(f"conv_flip_weights failed ({rc})")
             dx = conv3x3(dy, flipped, cin)
         n, _, h, w = x.shape
         from . import nn as native_nn

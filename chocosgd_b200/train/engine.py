@@ -65,10 +65,23 @@ class TrainStep:
         self._warm = 0
         self._warmup_iters = warmup_iters
         self.kernel_launches_per_step = None
+        self.flips = None
+        if self.is_cuda:
+            from ..ops import nn as native_nn
+
+            if native_nn.native_enabled("conv"):
+                from ..ops.conv import FlippedWeights
+
+                self.flips = FlippedWeights(model)
 
     # ---- the step body (captured or eager) ------------------------------------------------------
     def _forward_backward(self):
         params = self.opt.arena.params
+        if self.flips is not None:
+            from ..ops.conv import set_active_flips
+
+            self.flips.refresh()  # one kernel: flipped filters of every native convolution
+            set_active_flips(self.flips)
         if self.fused:
             for p in params:
                 p.grad = None  # autograd then hands over its own gradient tensors (no accumulate kernels)
@@ -82,6 +95,8 @@ class TrainStep:
                 out = self.model(self.static_input)
                 loss = self.criterion(out, self.static_target)
         loss.backward()
+        if self.flips is not None:
+            self.flips.valid = False
         with torch.no_grad():
             if self.hidden is not None:
                 for dst, src in zip(self.hidden, new_h):
