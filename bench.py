@@ -130,8 +130,14 @@ def max_over_ranks(ms, world):
     return ms
 
 
-def timed(fn, steps, world):
-    """K calls of fn(i) bracketed by barrier + synchronize, CUDA events, max over ranks."""
+def timed(fn, steps, world, quiesce=None):
+    """K calls of fn(i) bracketed by barrier + synchronize, CUDA events, max over ranks.
+
+    ``quiesce`` runs before each barrier: an arm that communicates from a helper thread must
+    have no point-to-point call in flight while this thread issues a collective on the same
+    NCCL communicator (the two would be enqueued in different orders on different ranks)."""
+    if quiesce is not None:
+        quiesce()
     barrier_sync(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -140,6 +146,8 @@ def timed(fn, steps, world):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
+    if quiesce is not None:
+        quiesce()
     barrier_sync(world)
     return max_over_ranks(ms, world)
 
@@ -166,12 +174,7 @@ def run_ours(args, rank, world, local):
     graph = Graph("ring", world, rank)
     torch.manual_seed(6)
     torch.backends.cudnn.benchmark = True
-    if args.native_layers == "bn":
-        native_nn.set_native(True, which=("bn", "linear"))
-    elif args.native_layers == "conv":
-        native_nn.set_native(True, which=("bn", "linear", "conv"))
-    elif args.native_layers != "off":
-        native_nn.set_native(True, which=native_nn.available_kinds())
+    native_nn.configure_native("auto" if args.native_layers == "on" else args.native_layers)
     model = define_model(conf, graph, device=device, verbose=False)
     optimizer = define_optimizer(conf, model, graph)
     metrics = Metrics(model)
@@ -233,7 +236,7 @@ def run_reference(args, rank, world, local):
         it(i)
     torch.cuda.synchronize()
     sampler = ClockSampler(rank == 0, local)
-    ms = timed(it, args.steps, world)
+    ms = timed(it, args.steps, world, quiesce=lambda: ref.finish(state))
     clocks = sampler.stop()
     ref.finish(state)
     return ms, ms, clocks, 0, out["loss"], BATCH * 3 * 32 * 32 * 4 + BATCH * 8, {}

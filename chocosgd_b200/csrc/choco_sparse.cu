@@ -75,11 +75,23 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_hist_kernel(const Ch
   const int nb = pass == 2 ? 2048 : 512;
   for (int i = threadIdx.x; i < nb; i += CHOCO_THREADS) sh_hist[i] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < valid; i += CHOCO_THREADS) {
-    const uint32_t key = key_of(p.scratch_d[start + i]);
-    if ((key >> 20) == b1) {
-      if (pass == 2) atomicAdd(&sh_hist[(key >> 9) & 2047u], 1u);
-      else if (((key >> 9) & 2047u) == b2) atomicAdd(&sh_hist[key & 511u], 1u);
+  // 2 x 16-byte loads in flight per thread; the padding behind `valid` holds zeros and is skipped
+  const float* dptr = p.scratch_d + start;
+  const int span = (valid + 3) & ~3;
+  for (int base = threadIdx.x * 4; base < span; base += CHOCO_THREADS * 8) {
+    const int base2 = base + CHOCO_THREADS * 4;
+    const float4 va = *reinterpret_cast<const float4*>(dptr + base);
+    float4 vb = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (base2 < span) vb = *reinterpret_cast<const float4*>(dptr + base2);
+    const float d8[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int i = (e < 4 ? base : base2 - 4) + e;
+      const uint32_t key = key_of(d8[e]);
+      if (i < valid && (key >> 20) == b1) {
+        if (pass == 2) atomicAdd(&sh_hist[(key >> 9) & 2047u], 1u);
+        else if (((key >> 9) & 2047u) == b2) atomicAdd(&sh_hist[key & 511u], 1u);
+      }
     }
   }
   __syncthreads();
@@ -112,10 +124,23 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_count_kernel(const C
   find_bucket(gh + 4096, 512, k2, sh, b3, k3);
   const uint32_t thr = (b1 << 20) | (b2 << 9) | b3;
   uint32_t gt = 0, eq = 0;
-  for (int i = threadIdx.x; i < valid; i += CHOCO_THREADS) {
-    const uint32_t key = key_of(p.scratch_d[start + i]);
-    gt += key > thr;
-    eq += key == thr;
+  const float* dptr = p.scratch_d + start;
+  const int span = (valid + 3) & ~3;
+  for (int base = threadIdx.x * 4; base < span; base += CHOCO_THREADS * 8) {
+    const int base2 = base + CHOCO_THREADS * 4;
+    const float4 va = *reinterpret_cast<const float4*>(dptr + base);
+    float4 vb = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (base2 < span) vb = *reinterpret_cast<const float4*>(dptr + base2);
+    const float d8[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int i = (e < 4 ? base : base2 - 4) + e;
+      const uint32_t key = key_of(d8[e]);
+      if (i < valid) {
+        gt += key > thr;
+        eq += key == thr;
+      }
+    }
   }
   // exact integer block sums through the float reducer would lose bits: use shuffles on ints
   for (int o = 16; o > 0; o >>= 1) {
@@ -184,9 +209,14 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const Ch
 
   // totals of the preceding chunks of this segment
   uint32_t gt_b = 0, eq_b = 0;
-  for (int c = c0 + threadIdx.x; c < chunk; c += CHOCO_THREADS) {
-    gt_b += __ldcg(p.chunk_cnt + c * 2);
-    eq_b += __ldcg(p.chunk_cnt + c * 2 + 1);
+  {
+    const uint2* cc = reinterpret_cast<const uint2*>(p.chunk_cnt);
+#pragma unroll 4
+    for (int c = c0 + threadIdx.x; c < chunk; c += CHOCO_THREADS) {
+      const uint2 v = __ldcg(cc + c);
+      gt_b += v.x;
+      eq_b += v.y;
+    }
   }
   for (int o = 16; o > 0; o >>= 1) {
     gt_b += __shfl_xor_sync(0xffffffffu, gt_b, o);
@@ -212,20 +242,37 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const Ch
   uint32_t* out_idx = p.outbox + par_cur * PW;
   uint32_t* out_val = out_idx + sum_k;
 
-  const int n_tiles = (valid + CHOCO_THREADS - 1) / CHOCO_THREADS;
+  // tiles of 2048 elements, 8 consecutive elements per thread (two 16-byte loads): one block scan
+  // of the packed (gt, eq) counts per tile keeps the output ordered by index
+  constexpr int EPT = 8, TILE = CHOCO_THREADS * EPT;
+  const float* dptr = p.scratch_d + start;
+  const int span = (valid + 3) & ~3;
+  const int n_tiles = (valid + TILE - 1) / TILE;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 na = zero4, nb = zero4;  // next tile, loaded one iteration ahead
+  {
+    const int i0 = threadIdx.x * EPT;
+    if (i0 < span) na = *reinterpret_cast<const float4*>(dptr + i0);
+    if (i0 + 4 < span) nb = *reinterpret_cast<const float4*>(dptr + i0 + 4);
+  }
   for (int tile = 0; tile < n_tiles; ++tile) {
-    const int i = tile * CHOCO_THREADS + threadIdx.x;
-    float d = 0.f;
-    uint32_t is_gt = 0, is_eq = 0;
-    if (i < valid) {
-      d = p.scratch_d[start + i];
-      const uint32_t key = key_of(d);
-      is_gt = key > thr;
-      is_eq = key == thr;
+    const int i0 = tile * TILE + threadIdx.x * EPT;
+    const float4 va = na, vb = nb;
+    na = zero4; nb = zero4;
+    if (i0 + TILE < span) na = *reinterpret_cast<const float4*>(dptr + i0 + TILE);
+    if (i0 + TILE + 4 < span) nb = *reinterpret_cast<const float4*>(dptr + i0 + TILE + 4);
+    const float d8[EPT] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+    uint32_t gt_mask = 0, eq_mask = 0;
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      const uint32_t key = key_of(d8[e]);
+      if (i0 + e < valid) {
+        gt_mask |= (uint32_t)(key > thr) << e;
+        eq_mask |= (uint32_t)(key == thr) << e;
+      }
     }
-    // exclusive block scan of (gt, eq) packed as 16 + 16 bits (a tile holds 256 elements)
-    uint32_t v = is_gt | (is_eq << 16);
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint32_t v = __popc(gt_mask) | (__popc(eq_mask) << 16);
     uint32_t inc = v;
     for (int o = 1; o < 32; o <<= 1) {
       const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
@@ -236,23 +283,30 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const Ch
     __syncthreads();
     uint32_t warp_off = 0, tile_tot = 0;
     for (int w = 0; w < CHOCO_THREADS / 32; ++w) {
-      const uint32_t s = sh[w];
-      if (w < wid) warp_off += s;
-      tile_tot += s;
+      const uint32_t sw = sh[w];
+      if (w < wid) warp_off += sw;
+      tile_tot += sw;
     }
-    const uint32_t exc = warp_off + inc - v;
-    const uint32_t g_before = G + (exc & 0xFFFFu), e_before = E + (exc >> 16);
-    const bool take = is_gt || (is_eq && e_before < need_eq);
-    if (take) {
-      const uint32_t slot = koff + g_before + (e_before < need_eq ? e_before : need_eq);
-      const uint32_t idx = (uint32_t)(start + i - seg_start);
-      const uint32_t vb = __float_as_uint(d);
-      out_idx[slot] = idx;
-      out_val[slot] = vb;
-      for (int k = 0; k < p.n_peers; ++k) {
-        uint32_t* pi = p.peer_inbox[k] + par_cur * PW;
-        pi[slot] = idx;
-        pi[sum_k + slot] = vb;
+    if (gt_mask | eq_mask) {
+      const uint32_t exc = warp_off + inc - v;
+      uint32_t g_run = G + (exc & 0xFFFFu), e_run = E + (exc >> 16);
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) {
+        const bool is_gt = (gt_mask >> e) & 1u, is_eq = (eq_mask >> e) & 1u;
+        if (is_gt || (is_eq && e_run < need_eq)) {
+          const uint32_t slot = koff + g_run + (e_run < need_eq ? e_run : need_eq);
+          const uint32_t idx = (uint32_t)(start + i0 + e - seg_start);
+          const uint32_t vbits = __float_as_uint(d8[e]);
+          out_idx[slot] = idx;
+          out_val[slot] = vbits;
+          for (int k = 0; k < p.n_peers; ++k) {
+            uint32_t* pi = p.peer_inbox[k] + par_cur * PW;
+            pi[slot] = idx;
+            pi[sum_k + slot] = vbits;
+          }
+        }
+        g_run += is_gt;
+        e_run += is_eq;
       }
     }
     G += tile_tot & 0xFFFFu;

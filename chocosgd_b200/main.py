@@ -61,6 +61,10 @@ def main(conf):
         verbosity_level=1 if conf.track_time and not conf.train_fast else 0,
         log_fn=run.logger.log_metric, on_cuda=graph.on_cuda,
     )
+    if graph.on_cuda:
+        from .ops import nn as native_nn
+
+        native_nn.configure_native(getattr(conf, "native_layers", "auto"))
     data_loader = define_dataset(conf, graph, run, device=device)
     model = define_model(conf, graph, data_loader=data_loader, device=device)
     optimizer = define_optimizer(conf, model, graph)

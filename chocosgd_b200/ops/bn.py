@@ -113,13 +113,50 @@ def bn_act(bn, x, residual=None, relu=True):
     if (native_nn.native_enabled("bn") and bn.training and bn.track_running_stats is not None
             and supported(x, bn.num_features) and bn.affine
             and (residual is None or (residual.shape == x.shape and residual.is_contiguous(memory_format=torch.channels_last)))):
-        if bn.track_running_stats and bn.num_batches_tracked is not None:
+        if bn.track_running_stats and bn.num_batches_tracked is not None and not getattr(bn, "_fused_counter", False):
             bn.num_batches_tracked.add_(1)
         mom = bn.momentum if bn.momentum is not None else 0.1
         rm = bn.running_mean if bn.track_running_stats else None
         rv = bn.running_var if bn.track_running_stats else None
         return _BnActFn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps)
     out = bn(x)
+    if getattr(bn, "_fused_counter", False) and bn.training and bn.track_running_stats:
+        bn.num_batches_tracked.sub_(1)  # the library path counted this batch; BnCounters.tick() counts it again
     if residual is not None:
         out = out + residual
     return F.relu(out, inplace=True) if relu else out
+
+
+class BnCounters:
+    """The ``num_batches_tracked`` buffers of every batch-norm layer of a model as views of ONE
+    int64 tensor, advanced by a single add per training step (the stock module launches one
+    increment kernel per layer per step).  ``state_dict`` / ``load_state_dict`` keep working on
+    the per-layer views."""
+
+    def __init__(self, model):
+        self.model = model
+        self.flat = None
+        self._fuse()
+
+    def _fuse(self):
+        self.mods = [m for m in self.model.modules()
+                     if isinstance(m, torch.nn.modules.batchnorm._BatchNorm) and m.track_running_stats
+                     and m.num_batches_tracked is not None]
+        if not self.mods:
+            self.flat = None
+            return
+        self.flat = torch.stack([m.num_batches_tracked.detach() for m in self.mods])
+        for i, m in enumerate(self.mods):
+            m._buffers["num_batches_tracked"] = self.flat[i]
+            m._fused_counter = True
+
+    def tick(self):
+        if self.flat is None:
+            return
+        if self.mods[0].num_batches_tracked.data_ptr() != self.flat.data_ptr():
+            self._fuse()  # the module was moved / reloaded: its buffers are no longer our views
+        self.flat.add_(1)
+
+    def release(self):
+        for m in self.mods:
+            m._fused_counter = False

@@ -142,6 +142,17 @@ class _Conv3x3Fn(torch.autograd.Function):
         dy = dy.contiguous(memory_format=torch.channels_last)
         cout, cin = weight.shape[0], weight.shape[1]
         dx = dw = None
+        n, _, h, w = x.shape
+        from . import nn as native_nn
+
+        # the weight gradient is forked first so that it does not wait for this layer's dgrad
+        if ctx.needs_input_grad[1]:
+            if native_nn.native_enabled("wgrad") and lib.conv3x3_wgrad_supported(n, h, w, cin, cout):
+                fn = lambda: conv3x3_wgrad(x, dy, weight)
+            else:
+                fn = lambda: torch.ops.aten.convolution_backward(
+                    dy, x, weight, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1, (False, True, False))[1]
+            dw = _WGRAD_STREAM.run(fn, (x, dy), x.device) if _WGRAD_STREAM.enabled else fn()
         if ctx.needs_input_grad[0]:
             flipped = _ACTIVE_FLIPS.get(weight) if _ACTIVE_FLIPS is not None else None
             if flipped is None:
@@ -150,15 +161,67 @@ class _Conv3x3Fn(torch.autograd.Function):
                 if rc != 0:
                     raise RuntimeError(f"conv_flip_weights failed ({rc})")
             dx = conv3x3(dy, flipped, cin)
-        n, _, h, w = x.shape
-        from . import nn as native_nn
-
-        if ctx.needs_input_grad[1] and native_nn.native_enabled("wgrad") and lib.conv3x3_wgrad_supported(n, h, w, cin, cout):
-            dw = conv3x3_wgrad(x, dy, weight)
-        elif ctx.needs_input_grad[1]:
-            dw = torch.ops.aten.convolution_backward(
-                dy, x, weight, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1, (False, True, False))[1]
         return dx, dw
+
+
+class _WgradStream:
+    """Weight gradients on a second stream.
+
+    The critical path of the backward pass is dgrad -> BN backward -> dgrad ...; the weight
+    gradient of a layer is needed only by the update at the end.  Each wgrad kernel is forked onto
+    a side stream (which first waits for everything enqueued so far on the launching stream), and
+    joined either when more than ``depth`` of them are pending or by a callback at the end of the
+    backward pass.  The operands stay referenced until the join, so the allocator cannot hand
+    their memory to later kernels of the launching stream.  Works the same under CUDA-graph
+    capture (the fork / join become graph dependencies)."""
+
+    depth = 4
+
+    def __init__(self):
+        self.enabled = True
+        self._streams = {}
+        self._pending = []
+        self._callback_queued = False
+
+    def _side(self, device):
+        st = self._streams.get(device)
+        if st is None:
+            st = self._streams[device] = torch.cuda.Stream(device=device)
+        return st
+
+    def run(self, fn, keep, device):
+        main = torch.cuda.current_stream(device)
+        side = self._side(device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            out = fn()
+            ev = torch.cuda.Event()
+            ev.record(side)
+        self._pending.append((ev, main, keep, out))
+        if not self._callback_queued:
+            torch.autograd.Variable._execution_engine.queue_callback(self.join)
+            self._callback_queued = True
+        while len(self._pending) > self.depth:
+            self._join_one()
+        return out
+
+    def _join_one(self):
+        ev, main, _keep, _out = self._pending.pop(0)
+        main.wait_event(ev)
+
+    def join(self):
+        """Make the launching stream wait for every pending weight gradient."""
+        while self._pending:
+            self._join_one()
+        self._callback_queued = False
+
+
+_WGRAD_STREAM = _WgradStream()
+
+
+def set_wgrad_side_stream(on: bool):
+    _WGRAD_STREAM.join()
+    _WGRAD_STREAM.enabled = bool(on)
 
 
 def conv2d_native(m, x):

@@ -96,6 +96,14 @@ class SegTables:
         c.chunk_elems, c.total = self.chunk_elems, self.seg.total
 
 
+ALLREDUCE = "allreduce"
+
+
+class ArPlanC(ctypes.Structure):
+    _fields_ = [("n_world", ctypes.c_int), ("my_rank", ctypes.c_int), ("shard_words", ctypes.c_int),
+                ("slot_of", ctypes.c_int * (_lib.MAX_PEERS + 1))]
+
+
 class RankBuffers:
     """Flat state of one logical rank (all fp32, length ``seg.total``)."""
 
@@ -138,7 +146,7 @@ class ChocoEngine:
         wait_budget_ms: float = 2000.0,
         chunk_elems: Optional[int] = None,
     ):
-        if comm_op is not None and comm_op not in CODEC_ID:
+        if comm_op is not None and comm_op != ALLREDUCE and comm_op not in CODEC_ID:
             raise NotImplementedError(f"fused gossip kernels do not cover comm_op={comm_op!r}")
         self.lib = _lib.load()
         self.device = torch.device(device)
@@ -150,7 +158,15 @@ class ChocoEngine:
         self.tables = SegTables(seg, weight_decay, ks, self.device, chunk_elems)
         self.s_levels = qsgd_levels_from(quantize_level, qsgd_levels) if comm_op == "quantize_qsgd" else 1
         self.nbits = qsgd_nbits(self.s_levels) if comm_op == "quantize_qsgd" else 0
-        self.payload_words, self.body_off = payload_layout(comm_op, seg, self.tables.sum_k, self.nbits)
+        if comm_op == ALLREDUCE:
+            # two-shot all-reduce: one shard of scattered gradients + one shard of averages per slot
+            self.n_world = len(neighborhoods[self.ranks[0]])
+            assert all(sorted(neighborhoods[r]) == list(range(self.n_world)) for r in self.ranks), \
+                "the fused all-reduce needs the complete graph over ranks 0..n-1"
+            self.shard_words = -(-self.tables.n_chunks // self.n_world) * self.tables.chunk_elems
+            self.payload_words, self.body_off = 2 * self.shard_words, 0
+        else:
+            self.payload_words, self.body_off = payload_layout(comm_op, seg, self.tables.sum_k, self.nbits)
         self.mailbox = mailbox(self.payload_words) if callable(mailbox) else mailbox
         peers_max = max(len([j for j in neighborhoods[r] if j != r]) for r in self.ranks)
         if peers_max > _lib.MAX_PEERS:
@@ -180,7 +196,7 @@ class ChocoEngine:
                 "partial": z(nc, torch.float32),
                 "status": z(4, torch.int32),
                 "outbox": z(2 * self.payload_words, torch.int32),
-                "scratch_d": z(seg.total, torch.float32) if self.codec != 3 else None,
+                "scratch_d": z(seg.total, torch.float32) if self.codec in (0, 1, 2) else None,
                 "hist": z(T * self.lib.choco_hist_words(), torch.int32) if self.codec == 1 else None,
                 "chunk_cnt": z(2 * nc, torch.int32) if self.codec == 1 else None,
                 "sel": z(4 * T, torch.int32) if self.codec == 1 else None,
@@ -212,6 +228,8 @@ class ChocoEngine:
             blocks.append(c)
         self._structs = blocks
         self._grad_tables = {}
+        if comm_op == ALLREDUCE:
+            self._init_allreduce()
         raw = np.frombuffer(b"".join(bytes(c) for c in blocks), dtype=np.uint8).copy()
         self.params = torch.from_numpy(raw).to(dev)
         self._pp = ctypes.c_void_p(self.params.data_ptr())
@@ -319,6 +337,34 @@ class ChocoEngine:
         else:
             self._launch_sparse_decode(sp)
 
+    def _init_allreduce(self):
+        L = self.lib
+        L.allreduce_sgd_step.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        plans = []
+        for r in self.ranks:
+            pl = ArPlanC()
+            pl.n_world, pl.my_rank, pl.shard_words = self.n_world, int(r), self.shard_words
+            peers = self.mailbox.view(r).peers
+            for j in range(_lib.MAX_PEERS + 1):
+                pl.slot_of[j] = peers.index(j) if j in peers else -1
+            plans.append(pl)
+        assert L.ar_plan_size() == ctypes.sizeof(ArPlanC), "ArPlan layout mismatch"
+        raw = np.frombuffer(b"".join(bytes(c) for c in plans), dtype=np.uint8).copy()
+        self._plans = torch.from_numpy(raw).to(self.device)
+        with torch.cuda.device(self.device):
+            cap = L.allreduce_sgd_max_grid(self.n_local)
+        if cap < 1:
+            raise RuntimeError("the fused all-reduce kernel cannot be made co-resident on this device")
+        self.ar_grid = max(1, min(self.tables.n_chunks, cap))
+
+    def launch_allreduce_sgd(self, stream=None):
+        """Gradient averaging over all ranks + momentum-SGD update, one kernel."""
+        self._n_launch = 0
+        self._chk(self.lib.allreduce_sgd_step(self._pp, ctypes.c_void_p(self._plans.data_ptr()), self.ar_grid,
+                                              self.n_local, _lib.stream_ptr(stream)), "allreduce_sgd_step")
+        self._steps += 1
+        self.launches_per_step = 1
+
     def launch_sgd_only(self, apply=True, stream=None):
         self._chk(
             self.lib.fused_sgd_step(self._pp, self.tables.n_chunks, self.n_local, 1 if apply else 0,
@@ -386,7 +432,12 @@ class LoopbackWorld:
     def step(self, grads: torch.Tensor, lr, momentum, gamma, nesterov):
         self.g.copy_(grads.to(self.device))
         self.engine.set_hyper(lr, momentum, gamma, nesterov)
-        self.engine.launch_step()
+        if self.engine.comm_op == ALLREDUCE:
+            self.engine.launch_allreduce_sgd()
+        else:
+            self.engine.launch_step()
 
     def flush(self):
+        if self.engine.comm_op == ALLREDUCE:
+            return self.engine.check()
         self.engine.flush()

@@ -30,6 +30,20 @@ def available_kinds():
     return tuple(kinds)
 
 
+def configure_native(mode: str = "auto"):
+    """Apply a ``--native_layers`` choice: auto = every kind built into the tree, bn = batch-norm
+    + linear, conv = bn + convolution forward / input gradient, off = library ops only."""
+    set_native(False, which=tuple(_NATIVE))
+    if mode in ("off", None) or not torch.cuda.is_available():
+        return
+    if mode == "bn":
+        set_native(True, which=("bn", "linear"))
+    elif mode == "conv":
+        set_native(True, which=("bn", "linear", "conv"))
+    else:
+        set_native(True, which=available_kinds())
+
+
 def native_enabled(kind: str) -> bool:
     return _NATIVE[kind]
 

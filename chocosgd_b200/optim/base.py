@@ -208,7 +208,10 @@ class DistributedOptimizer(Optimizer):
         self.wd_vec = self.arena.per_element([g["weight_decay"] for g in self.param_groups])
         st = sd.get("state", {})
         if st:
-            self.momentum_buf = torch.zeros_like(self.arena.x)
+            if self.momentum_buf is None:
+                self.momentum_buf = torch.zeros_like(self.arena.x)
+            else:
+                self.momentum_buf.zero_()  # in place: the fused kernels hold its address
             for i, sl in enumerate(self.seg.slices()):
                 ent = st.get(i, st.get(str(i)))
                 if ent is not None and "momentum_buffer" in ent:

@@ -17,25 +17,37 @@ class SGD(DistributedOptimizer):
     def __init__(self, model, conf, graph, group=None, is_centralized=None):
         super().__init__(model, conf, graph, group)
         self.is_centralized = (conf.graph_topology == "complete") if is_centralized is None else is_centralized
-        # single node on a GPU: the whole update is one fused kernel (capturable in a CUDA graph)
+        # On a GPU the update runs in the fused kernels (capturable in a CUDA graph):
+        #   one node                  fused momentum-SGD
+        #   complete graph, n > 1     gradient all-reduce + SGD in ONE kernel over the peer mailboxes
+        #   other graphs, n > 1       fused SGD, then push + fused weighted neighbour sum (eager)
         self.engine = None
+        self.fused_allreduce = False
         want = getattr(conf, "gossip_impl", "auto")
-        if self.n_nodes == 1 and self.device.type == "cuda" and want != "nccl":
-            from ..ops.gossip import ChocoEngine, RankBuffers
-            from ..parallel.symm import LoopbackMailbox
+        multi = self.n_nodes > 1 and self._mailbox_ok() and self.n_nodes - 1 <= 16
+        if self.device.type == "cuda" and want != "nccl" and (self.n_nodes == 1 or multi):
+            from ..ops.gossip import ALLREDUCE, ChocoEngine, RankBuffers
+            from ..parallel.symm import DistributedMailbox, LoopbackMailbox
 
             self.momentum_buf = torch.zeros_like(self.arena.x)
             z = torch.zeros(32, device=self.device)
             bufs = {self.rank: RankBuffers(self.arena.x, self.arena.g, self.momentum_buf, z, z)}
+            self.fused_allreduce = self.n_nodes > 1 and self.is_centralized
+            if self.fused_allreduce:
+                nbh = {self.rank: {r: 1.0 / self.n_nodes for r in range(self.n_nodes)}}
+                mailbox = lambda pw: DistributedMailbox(graph, pw, self.device, group)
+            else:
+                nbh = {self.rank: {self.rank: 1.0}}
+                mailbox = lambda pw: LoopbackMailbox({self.rank: []}, pw, self.device)
             self.engine = ChocoEngine(
-                [self.rank], bufs, {self.rank: {self.rank: 1.0}}, self.seg,
-                [g["weight_decay"] for g in self.param_groups], None,
-                lambda pw: LoopbackMailbox({self.rank: []}, pw, self.device), self.device,
+                [self.rank], bufs, nbh, self.seg, [g["weight_decay"] for g in self.param_groups],
+                ALLREDUCE if self.fused_allreduce else None, mailbox, self.device,
+                wait_budget_ms=getattr(conf, "wait_budget_ms", 2000.0),
             )
 
     @property
     def capturable(self) -> bool:
-        return self.engine is not None
+        return self.engine is not None and (self.n_nodes == 1 or self.fused_allreduce)
 
     def prepare_step(self):
         self.local_index += 1
@@ -44,7 +56,16 @@ class SGD(DistributedOptimizer):
         return self.n_bits
 
     def launch(self, stream=None):
-        self.engine.launch_sgd_only(True, stream)
+        if self.fused_allreduce:
+            self.engine.launch_allreduce_sgd(stream)
+        else:
+            self.engine.launch_sgd_only(True, stream)
+
+    def load_algo_state(self, st):
+        if self.engine is not None:
+            # the restored momentum buffer counts as initialised; the all-reduce counter stays
+            # in step with the (fresh) mailbox flags
+            self.engine.per_rank[self.rank]["step"][1] = 1 if self.local_index > 0 else 0
 
     def step(self, closure=None, **kargs):
         timer, a = self.timer_of(kargs), self.arena
@@ -53,6 +74,9 @@ class SGD(DistributedOptimizer):
             with timer("sync.apply_grad", epoch=ep):
                 bits = self.prepare_step()
                 self.launch()
+            if self.n_nodes > 1 and not self.fused_allreduce:
+                with timer("sync.sync", epoch=ep):
+                    self.neighbor_exchange().mix_(a.x)
             return bits
         self.local_index += 1
         if self.is_centralized:

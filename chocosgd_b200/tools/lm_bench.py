@@ -19,6 +19,7 @@ def main(argv=None):
     p.add_argument("--steps", type=int, default=50)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--no_graph", action="store_true")
+    p.add_argument("--native", default="off", help="comma list of native layer kinds (lstm, linear) or off")
     a = p.parse_args(argv)
     from ..config import get_args
     from ..models import define_model
@@ -42,6 +43,10 @@ def main(argv=None):
                      "--rnn_clip", "0.4", "--batch_size", str(B), "--gossip_impl", "fused"])
     graph = Graph("ring", world, rank)
     torch.manual_seed(6)
+    if a.native != "off":
+        from ..ops import nn as native_nn
+
+        native_nn.set_native(True, which=tuple(a.native.split(",")))
     model = define_model(conf, graph, data_loader={"n_tokens": V}, device=dev, verbose=False)
     opt = define_optimizer(conf, model, graph)
     g = torch.Generator().manual_seed(rank)
@@ -71,7 +76,7 @@ def main(argv=None):
     opt.engine.check()
     if rank == 0:
         print(json.dumps({"bench": "lstm_lm", "n_gpus": world, "tokens_per_s": B * T * world * a.steps / (ms * 1e-3),
-                          "ms_per_step": ms / a.steps, "loss": float(loss), "graph": step.use_graph,
+                          "ms_per_step": ms / a.steps, "loss": float(loss), "graph": step.use_graph, "native": a.native,
                           "kernels_per_step": opt.engine.launches_per_step, "comm_op": "quantize_qsgd 4 bit",
                           "params": sum(p.numel() for p in model.parameters())}))
     if world > 1:

@@ -66,8 +66,14 @@ class TrainStep:
         self._warmup_iters = warmup_iters
         self.kernel_launches_per_step = None
         self.flips = None
+        self.bn_counters = None
         if self.is_cuda:
             from ..ops import nn as native_nn
+
+            if native_nn.native_enabled("bn"):
+                from ..ops.bn import BnCounters
+
+                self.bn_counters = BnCounters(model)
 
             if native_nn.native_enabled("conv"):
                 from ..ops.conv import FlippedWeights
@@ -82,6 +88,8 @@ class TrainStep:
 
             self.flips.refresh()  # one kernel: flipped filters of every native convolution
             set_active_flips(self.flips)
+        if self.bn_counters is not None and self.model.training:
+            self.bn_counters.tick()  # one add for all batch-norm step counters
         if self.fused:
             for p in params:
                 p.grad = None  # autograd then hands over its own gradient tensors (no accumulate kernels)
@@ -125,7 +133,9 @@ class TrainStep:
 
     def _capture_with_table(self, table):
         eng = self.opt.engine
-        s = torch.cuda.Stream()
+        # the step runs on a high-priority stream: kernels forked to side streams (weight
+        # gradients) then fill the SMs that the critical path leaves idle instead of delaying it
+        s = torch.cuda.Stream(priority=-1)
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             for _ in range(self._warmup_iters):
@@ -141,7 +151,7 @@ class TrainStep:
             p.grad = None
         self.graph = torch.cuda.CUDAGraph()
         self.opt.prepare_step()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, stream=s):
             self._forward_backward()
             if self.clip is not None:
                 grad_clip_(eng, self.clip)

@@ -146,6 +146,53 @@ def test_wait_times_out_without_hanging():
     assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0  # context still alive
 
 
+@pytest.mark.parametrize("n,chunk", [(2, None), (4, 1024), (8, 1024), (3, 1024)])
+def test_fused_allreduce_sgd_matches_centralized_simulator(n, chunk):
+    """Two-shot all-reduce + momentum-SGD in one (cooperative, all ranks in one launch) kernel
+    against the averaged-gradient simulator; replicas must stay bit-identical."""
+    from chocosgd_b200.ops.gossip import LoopbackWorld
+
+    seg = Segments.from_sizes(SIZES)
+    wd = [0.0 if i % 3 == 0 else 1e-2 for i in range(seg.n_segments)]
+    w = mixing_matrix("complete", n)
+    x0 = _x0(seg)
+    sim = Simulator("choco", w, x0, seg, None, lr=0.05, consensus_stepsize=0.0, weight_decay=wd, momentum=0.9,
+                    nesterov=True)
+    world = LoopbackWorld(w, seg, x0, "allreduce", wd, device="cuda", chunk_elems=chunk)
+    for t in range(5):
+        g = _grad(seg, n, t)
+        sim.step_centralized(lambda i, tt, x: g[i])
+        world.step(g, 0.05, 0.9, 0.0, True)
+    world.flush()
+    torch.cuda.synchronize()
+    assert world.engine.step_index() == 5
+    torch.testing.assert_close(world.x.cpu(), sim.x, rtol=2e-5, atol=2e-6)
+    for i in range(1, n):
+        assert torch.equal(world.x[i], world.x[0])
+    assert world.g.abs().sum() == 0
+
+
+def test_fused_allreduce_times_out_without_hanging():
+    """A peer that never takes part: both bounded waits expire and the host raises."""
+    from chocosgd_b200.ops.gossip import ChocoEngine, RankBuffers
+    from chocosgd_b200.parallel.symm import LoopbackMailbox
+    from chocosgd_b200.utils.error_handler import GossipTimeout
+
+    seg = Segments.from_sizes([100, 40])
+    dev = torch.device("cuda")
+    mk = lambda: torch.zeros(seg.total, device=dev)
+    bufs = {0: RankBuffers(mk(), mk(), mk(), mk(), mk())}
+    eng = ChocoEngine([0], bufs, {0: {0: 0.5, 1: 0.5}}, seg, [0.0, 0.0], "allreduce",
+                      lambda pw: LoopbackMailbox({0: [1], 1: [0]}, pw, dev), dev, wait_budget_ms=20.0)
+    eng.set_hyper(0.1, 0.0, 0.0, False)
+    eng.launch_allreduce_sgd()
+    torch.cuda.synchronize()
+    with pytest.raises(GossipTimeout) as ei:
+        eng.check()
+    assert ei.value.peer == 1
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0  # context still alive
+
+
 def test_fused_sgd_and_clip():
     from chocosgd_b200.ops.gossip import ChocoEngine, RankBuffers
     from chocosgd_b200.parallel.symm import LoopbackMailbox

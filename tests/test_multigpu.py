@@ -115,7 +115,7 @@ def test_fused_choco_over_nvlink_matches_simulator(world):
                 np.testing.assert_allclose(s, sim.s[r].numpy(), rtol=2e-5, atol=2e-6, err_msg=f"{comm_op} s")
 
 
-OTHER = [("sgd", None, "ring"), ("dcd_psgd", "compress_top_k", "ring"), ("ecd_psgd", "quantize_qsgd", "ring"),
+OTHER = [("sgd", None, "ring"), ("sgd", None, "complete"), ("dcd_psgd", "compress_top_k", "ring"), ("ecd_psgd", "quantize_qsgd", "ring"),
          ("deep_squeeze", "sign", "ring"), ("dgc", "compress_top_k", "complete"), ("ef_sign_sgd", None, "complete"),
          ("parallel_choco_v", "sign", "ring")]
 
@@ -165,16 +165,19 @@ def _worker_other(rank, world, port, steps, out):
                 dist.barrier()
             if "fused" in xs:
                 d = float(sq_distance(xs["fused"], xs["nccl"]))
-                res[optimizer] = (d, float((xs["nccl"].double() ** 2).sum()))
+                res[f"{optimizer}-{topo}"] = (d, float((xs["nccl"].double() ** 2).sum()))
         out[rank] = res
     finally:
         dist.destroy_process_group()
 
 
-def test_mailbox_transport_equals_library_transport():
-    """Every non-fused algorithm gives the same parameters whether its payloads travel through the
-    peer-mapped mailboxes (in-kernel NVLink stores) or through torch.distributed."""
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_mailbox_transport_equals_library_transport(world):
+    """Every other algorithm gives the same parameters whether its payloads travel through the
+    peer-mapped mailboxes (in-kernel NVLink stores; for centralized SGD the one-kernel all-reduce +
+    update) or through torch.distributed."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
 
     ctx = mp.get_context("spawn")

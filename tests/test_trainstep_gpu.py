@@ -96,3 +96,36 @@ def test_lstm_step_with_clipping_in_a_graph():
     assert outs[False][0][-1] < outs[False][0][0]
     assert abs(outs[True][0][-1] - outs[False][0][-1]) < 3e-2 * outs[False][0][-1]
     assert outs[True][2] > 1.0  # perplexity
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_native_layers_in_a_step_count_batches_and_join_the_side_stream(use_graph):
+    """All native layer kinds inside TrainStep: every batch-norm counter advances once per step
+    (one fused add), the weight gradients computed on the side stream reach the update (training
+    makes progress and matches the library-op run after one step)."""
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.train.engine import TrainStep
+
+    def run(native):
+        nnn.configure_native("auto" if native else "off")
+        try:
+            conf, model, opt = _build("resnet20", "sign", "fused")
+            g = torch.Generator().manual_seed(1)
+            x = torch.randn(32, 3, 32, 32, generator=g).pin_memory()
+            y = torch.randint(0, 10, (32,), generator=g).pin_memory()
+            step = TrainStep(model, torch.nn.CrossEntropyLoss(), opt, x, y, use_cuda_graph=use_graph, warmup_iters=1)
+            model.train()
+            losses = [float(step(x, y)) for _ in range(5)]
+            opt.finalize()
+            opt.engine.check()
+            counters = [int(m.num_batches_tracked) for m in model.modules() if isinstance(m, torch.nn.BatchNorm2d)]
+            return losses, counters, opt.local_index
+        finally:
+            nnn.configure_native("off")
+
+    l_n, c_n, n_n = run(True)
+    l_r, c_r, n_r = run(False)
+    assert n_n == n_r and c_n == c_r and set(c_n) == {n_n}
+    assert abs(l_n[0] - l_r[0]) < 2e-2 * abs(l_r[0])
+    assert l_n[-1] < l_n[0]
+    assert abs(l_n[-1] - l_r[-1]) < 0.15 * abs(l_r[-1]) + 1e-2
