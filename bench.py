@@ -42,7 +42,7 @@ def parse():
     p.add_argument("--comm_op", default="compress_top_k",
                    choices=("compress_top_k", "sign", "quantize_qsgd", "compress_random_k"))
     p.add_argument("--no_graph", action="store_true")
-    p.add_argument("--native_layers", default="auto", choices=("auto", "on", "off", "bn", "conv"))
+    p.add_argument("--native_layers", default="auto", choices=("auto", "all", "on", "off", "bn", "conv"))
     return p.parse_args()
 
 

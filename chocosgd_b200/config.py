@@ -257,9 +257,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--use_cuda_graph", default=True, type=str2bool)
     p.add_argument("--channels_last", default=True, type=str2bool,
                    help="keep 4-d activations and convolution weights in NHWC / KRSC memory order on CUDA")
-    p.add_argument("--native_layers", default="auto", choices=("auto", "off", "bn", "conv"),
-                   help="layers routed to the hand-written sm_100a kernels on CUDA: auto = all kinds built "
-                   "into the tree (batch-norm, linear, 3x3 convolution fwd/dgrad/wgrad, LSTM cell), "
+    p.add_argument("--native_layers", default="auto", choices=("auto", "all", "off", "bn", "conv"),
+                   help="layers routed to the hand-written sm_100a kernels on CUDA: auto = batch-norm + 3x3 "
+                   "convolution fwd/dgrad/wgrad, all = auto + linear + LSTM cell, "
                    "bn = batch-norm + linear only, conv = bn + convolution fwd/dgrad, off = library ops")
     p.add_argument("--overlap_gossip", default=True, type=str2bool)
     p.add_argument("--qsgd_levels", default=None, type=int,

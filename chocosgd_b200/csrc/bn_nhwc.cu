@@ -4,9 +4,11 @@
 //   backward:  g = dy * [y > 0] ;  dbeta = sum g ;  dgamma = sum g * xhat ;
 //              dx = gamma invstd (g - dbeta / P - xhat dgamma / P) ;  dresidual = g
 //
-// Each direction is two kernels: a per-channel reduction over all P = N*H*W pixels (per-CTA
-// partials, the last CTA to arrive adds them in a fixed order in double precision and, in the
-// forward, updates the running statistics) and one elementwise pass.  That replaces the
+// Each direction is two kernels: a per-channel reduction over all P = N*H*W pixels into per-CTA
+// partials, and one elementwise pass.  When the partials are few (G * 2C <= 8192 floats) every
+// CTA of the elementwise kernel adds them itself, in a fixed order in double precision, before it
+// starts (CTA 0 also stores the statistics and updates the running ones): the reduction kernel
+// then has no serial tail.  Otherwise the last CTA of the reduction kernel adds the partials.  That replaces the
 // library batch-norm kernel plus separate add / ReLU / ReLU-backward / add-backward kernels
 // (dl_code/pcode/models/resnet.py:37-56: conv -> bn -> relu, conv -> bn -> += residual -> relu).
 //
@@ -36,6 +38,8 @@ struct BnArgs {
   unsigned* counter;     // arrival counter (self-resetting)
   int P, C, relu;
   float eps, momentum;
+  int n_partials;        // G: CTAs of the reduction kernel (set by the launcher)
+  int fused_finalize;    // 1: the elementwise kernel adds the partials (set by the launcher)
 };
 
 // per-channel sums of (a, b) over this CTA's rows -> partial; last CTA finalises
@@ -122,6 +126,7 @@ __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnArgs a) {
       dst[C + col + e] = p[4 + e];
     }
   }
+  if (a.fused_finalize) return;
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -189,14 +194,90 @@ __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnArgs a) {
   if (threadIdx.x == 0) *a.counter = 0;
 }
 
+#define BN_MAX_C 1024
+#define BN_FUSED_LIMIT 8192   // floats of partials a CTA of the elementwise kernel may add itself
+
+// Statistics of the elementwise kernels in shared memory: st0 / st1 = mean / invstd (forward) or
+// dbeta / dgamma (backward).  fused_finalize: derived here from the partials [G][2C] with a fixed
+// summation order (sub-sums of strided subsets, then the subsets in order), so that every CTA
+// obtains bit-identical values; CTA 0 publishes them.  Otherwise they are read from global memory.
+template <bool BACKWARD>
+__device__ void bn_stats_to_smem(const BnArgs& a, float* st0, float* st1, double* tot, double* shd) {
+  const int C = a.C;
+  if (!a.fused_finalize) {
+    for (int c = threadIdx.x; c < C; c += BN_THREADS) {
+      st0[c] = BACKWARD ? a.dbeta[c] : a.mean[c];
+      st1[c] = BACKWARD ? a.dgamma[c] : a.invstd[c];
+    }
+    __syncthreads();
+    return;
+  }
+  const int C2 = 2 * C, G = a.n_partials;
+  const int cw = C2 < BN_THREADS ? C2 : BN_THREADS, nsub = BN_THREADS / cw;
+  for (int cbase = 0; cbase < C2; cbase += BN_THREADS) {
+    const int col = cbase + threadIdx.x % cw, sub = threadIdx.x / cw;
+    double t = 0.0;
+    if (sub < nsub) {
+      int b = sub;
+      for (; b + 3 * nsub < G; b += 4 * nsub) {
+        float u[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) u[q] = __ldcg(a.partial + (size_t)(b + q * nsub) * C2 + col);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) t += (double)u[q];
+      }
+      for (; b < G; b += nsub) t += (double)__ldcg(a.partial + (size_t)b * C2 + col);
+    }
+    shd[threadIdx.x] = t;
+    __syncthreads();
+    if (threadIdx.x < cw) {
+      double acc = 0.0;
+      for (int j = 0; j < nsub; ++j) acc += shd[j * cw + threadIdx.x];
+      tot[col] = acc;
+    }
+    __syncthreads();
+  }
+  for (int c = threadIdx.x; c < C; c += BN_THREADS) {
+    const double t0 = tot[c], t1 = tot[C + c];
+    if (!BACKWARD) {
+      const double mean = t0 / a.P;
+      double var = t1 / a.P - mean * mean;
+      if (var < 0.0) var = 0.0;
+      const float mf = (float)mean, isf = (float)(1.0 / sqrt(var + (double)a.eps));
+      st0[c] = mf;
+      st1[c] = isf;
+      if (blockIdx.x == 0) {
+        a.mean[c] = mf;
+        a.invstd[c] = isf;
+        if (a.running_mean != nullptr) {
+          const double unbiased = a.P > 1 ? var * a.P / (a.P - 1) : var;
+          a.running_mean[c] = (1.f - a.momentum) * a.running_mean[c] + a.momentum * mf;
+          a.running_var[c] = (1.f - a.momentum) * a.running_var[c] + a.momentum * (float)unbiased;
+        }
+      }
+    } else {
+      st0[c] = (float)t0;
+      st1[c] = (float)t1;
+      if (blockIdx.x == 0) {
+        a.dbeta[c] = (float)t0;
+        a.dgamma[c] = (float)t1;
+      }
+    }
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(BN_THREADS) bn_fwd_apply_kernel(BnArgs a) {
+  __shared__ float st0[BN_MAX_C], st1[BN_MAX_C];
+  __shared__ double tot[2 * BN_MAX_C], shd[BN_THREADS];
+  bn_stats_to_smem<false>(a, st0, st1, tot, shd);
   const size_t n4 = (size_t)a.P * a.C / 4;
   const int c4 = a.C >> 2;
   for (size_t i = (size_t)blockIdx.x * BN_THREADS + threadIdx.x; i < n4; i += (size_t)gridDim.x * BN_THREADS) {
     const int col = (int)(i % c4) * 4;
     const float4 xv = reinterpret_cast<const float4*>(a.x)[i];
-    const float4 m = *reinterpret_cast<const float4*>(a.mean + col);
-    const float4 s = *reinterpret_cast<const float4*>(a.invstd + col);
+    const float4 m = *reinterpret_cast<const float4*>(st0 + col);
+    const float4 s = *reinterpret_cast<const float4*>(st1 + col);
     const float4 g = *reinterpret_cast<const float4*>(a.gamma + col);
     const float4 b = *reinterpret_cast<const float4*>(a.beta + col);
     float4 y;
@@ -216,6 +297,9 @@ __global__ void __launch_bounds__(BN_THREADS) bn_fwd_apply_kernel(BnArgs a) {
 }
 
 __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnArgs a) {
+  __shared__ float st0[BN_MAX_C], st1[BN_MAX_C];
+  __shared__ double tot[2 * BN_MAX_C], shd[BN_THREADS];
+  bn_stats_to_smem<true>(a, st0, st1, tot, shd);
   const size_t n4 = (size_t)a.P * a.C / 4;
   const int c4 = a.C >> 2;
   const float inv_p = 1.f / (float)a.P;
@@ -232,8 +316,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnArgs a) {
     const float4 m = *reinterpret_cast<const float4*>(a.mean + col);
     const float4 s = *reinterpret_cast<const float4*>(a.invstd + col);
     const float4 g = *reinterpret_cast<const float4*>(a.gamma + col);
-    const float4 db = *reinterpret_cast<const float4*>(a.dbeta + col);
-    const float4 dg = *reinterpret_cast<const float4*>(a.dgamma + col);
+    const float4 db = *reinterpret_cast<const float4*>(st0 + col);
+    const float4 dg = *reinterpret_cast<const float4*>(st1 + col);
     float4 dx;
     dx.x = g.x * s.x * (gv.x - db.x * inv_p - (xv.x - m.x) * s.x * dg.x * inv_p);
     dx.y = g.y * s.y * (gv.y - db.y * inv_p - (xv.y - m.y) * s.y * dg.y * inv_p);
@@ -249,30 +333,49 @@ static int grid_for(long long n4) {
   return (int)(b < 1 ? 1 : b);
 }
 
+// CTAs of the reduction kernel: four 4-row trips per thread, at most one CTA per SM.  Few enough
+// partials -> the elementwise kernel adds them (fused finalize); otherwise the last CTA of the
+// reduction kernel does, and the grid is capped lower to keep that serial pass short.
 extern "C" int bn_reduce_grid(int P, int C) {
   const int rpb = BN_THREADS / (C / 4);
-  int g = (P + rpb * 4 - 1) / (rpb * 4);  // one 4-row trip per thread when the tensor is small
-  static int cap = 0;                      // CTAs: enough to fill the machine, few enough that the
-  if (cap == 0) {                          // last CTA's pass over the partials stays short
+  const int trips = (P + rpb * 4 - 1) / (rpb * 4);
+  static int cap = 0, cap_last = 0;
+  if (cap == 0) {
     const char* e = getenv("CHOCO_BN_GRID_CAP");
-    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : 74;
+    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : 148;
+    cap_last = cap < 74 ? cap : 74;
   }
+  int g = (trips + 3) / 4;
   if (g > cap) g = cap;
-  return g < 1 ? 1 : g;
+  if (g < 1) g = 1;
+  if ((long long)g * 2 * C > BN_FUSED_LIMIT && g > cap_last) g = cap_last;
+  return g;
+}
+
+static int bn_prepare(BnArgs& a) {
+  if (a.C % 4 != 0 || BN_THREADS % (a.C / 4) != 0 || a.C / 4 > BN_THREADS || a.C > BN_MAX_C) return -1;
+  a.n_partials = bn_reduce_grid(a.P, a.C);
+  static int allow = -1;
+  if (allow < 0) {
+    const char* e = getenv("CHOCO_BN_FUSED_FINALIZE");
+    allow = e == nullptr || atoi(e) != 0;
+  }
+  a.fused_finalize = allow && (long long)a.n_partials * 2 * a.C <= BN_FUSED_LIMIT;
+  return 0;
 }
 
 extern "C" int bn_forward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
-  if (a.C % 4 != 0 || BN_THREADS % (a.C / 4) != 0 || a.C / 4 > BN_THREADS) return -1;
-  bn_reduce_kernel<false><<<bn_reduce_grid(a.P, a.C), BN_THREADS, 0, st>>>(a);
+  if (bn_prepare(a) != 0) return -1;
+  bn_reduce_kernel<false><<<a.n_partials, BN_THREADS, 0, st>>>(a);
   bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4), BN_THREADS, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
 
 extern "C" int bn_backward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
-  if (a.C % 4 != 0 || BN_THREADS % (a.C / 4) != 0 || a.C / 4 > BN_THREADS) return -1;
-  bn_reduce_kernel<true><<<bn_reduce_grid(a.P, a.C), BN_THREADS, 0, st>>>(a);
+  if (bn_prepare(a) != 0) return -1;
+  bn_reduce_kernel<true><<<a.n_partials, BN_THREADS, 0, st>>>(a);
   bn_bwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4), BN_THREADS, 0, st>>>(a);
   return (int)cudaGetLastError();
 }

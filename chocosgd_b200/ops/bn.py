@@ -17,7 +17,7 @@ class BnArgsC(ctypes.Structure):
         "x", "dy", "y", "residual", "gamma", "beta", "out", "out2", "mean", "invstd", "running_mean", "running_var",
         "dgamma", "dbeta", "partial", "counter")] + [
         ("P", ctypes.c_int), ("C", ctypes.c_int), ("relu", ctypes.c_int), ("eps", ctypes.c_float),
-        ("momentum", ctypes.c_float)]
+        ("momentum", ctypes.c_float), ("n_partials", ctypes.c_int), ("fused_finalize", ctypes.c_int)]
 
 
 _scratch = {}
@@ -119,12 +119,18 @@ def bn_act(bn, x, residual=None, relu=True):
         rm = bn.running_mean if bn.track_running_stats else None
         rv = bn.running_var if bn.track_running_stats else None
         return _BnActFn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps)
-    out = bn(x)
-    if getattr(bn, "_fused_counter", False) and bn.training and bn.track_running_stats:
-        bn.num_batches_tracked.sub_(1)  # the library path counted this batch; BnCounters.tick() counts it again
+    out = stock_forward(bn, x)
     if residual is not None:
         out = out + residual
     return F.relu(out, inplace=True) if relu else out
+
+
+def stock_forward(bn, x):
+    """The library batch-norm of a module (also for our subclass, whose ``forward`` routes here)."""
+    out = torch.nn.modules.batchnorm._BatchNorm.forward(bn, x)
+    if getattr(bn, "_fused_counter", False) and bn.training and bn.track_running_stats:
+        bn.num_batches_tracked.sub_(1)  # the library op counted this batch; BnCounters.tick() counts it too
+    return out
 
 
 class BnCounters:
@@ -139,9 +145,10 @@ class BnCounters:
         self._fuse()
 
     def _fuse(self):
+        from .nn import BatchNorm2d  # only our subclass: its forward compensates on the library path
+
         self.mods = [m for m in self.model.modules()
-                     if isinstance(m, torch.nn.modules.batchnorm._BatchNorm) and m.track_running_stats
-                     and m.num_batches_tracked is not None]
+                     if isinstance(m, BatchNorm2d) and m.track_running_stats and m.num_batches_tracked is not None]
         if not self.mods:
             self.flat = None
             return

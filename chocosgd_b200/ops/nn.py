@@ -30,9 +30,17 @@ def available_kinds():
     return tuple(kinds)
 
 
+#: kinds switched on by ``auto``: the ones measured faster than the library op inside a training
+#: step.  ``linear`` (tcgen05 GEMM at about half of the library's TF32 throughput on large
+#: shapes) and ``lstm`` (per-timestep cell kernels against the library's persistent kernel) are
+#: opt-in through ``set_native`` / ``--native_layers all``.
+AUTO_KINDS = ("bn", "conv", "wgrad")
+
+
 def configure_native(mode: str = "auto"):
-    """Apply a ``--native_layers`` choice: auto = every kind built into the tree, bn = batch-norm
-    + linear, conv = bn + convolution forward / input gradient, off = library ops only."""
+    """Apply a ``--native_layers`` choice: auto = batch-norm + 3x3 convolution forward / input /
+    weight gradient, all = every kind built into the tree, bn = batch-norm + linear, conv = bn +
+    convolution forward / input gradient, off = library ops only."""
     set_native(False, which=tuple(_NATIVE))
     if mode in ("off", None) or not torch.cuda.is_available():
         return
@@ -40,8 +48,10 @@ def configure_native(mode: str = "auto"):
         set_native(True, which=("bn", "linear"))
     elif mode == "conv":
         set_native(True, which=("bn", "linear", "conv"))
-    else:
+    elif mode == "all":
         set_native(True, which=available_kinds())
+    else:
+        set_native(True, which=tuple(k for k in AUTO_KINDS if k in available_kinds()))
 
 
 def native_enabled(kind: str) -> bool:
@@ -69,7 +79,12 @@ class Conv2d(nn.Conv2d):
 
 
 class BatchNorm2d(nn.BatchNorm2d):
-    pass
+    def forward(self, x):
+        from .bn import bn_act, stock_forward
+
+        if _NATIVE["bn"] and x.is_cuda:
+            return bn_act(self, x, None, relu=False)
+        return stock_forward(self, x)
 
 
 class LSTM(nn.LSTM):
