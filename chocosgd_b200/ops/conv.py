@@ -152,7 +152,10 @@ class _Conv3x3Fn(torch.autograd.Function):
             else:
                 fn = lambda: torch.ops.aten.convolution_backward(
                     dy, x, weight, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1, (False, True, False))[1]
-            dw = _WGRAD_STREAM.run(fn, (x, dy), x.device) if _WGRAD_STREAM.enabled else fn()
+            # Side stream only when autograd will take the result over as the new .grad without
+            # touching it (no accumulate / copy kernel on the launching stream before the join).
+            fork = _WGRAD_STREAM.enabled and weight.grad is None and not torch.is_grad_enabled()
+            dw = _WGRAD_STREAM.run(fn, (x, dy), x.device) if fork else fn()
         if ctx.needs_input_grad[0]:
             flipped = _ACTIVE_FLIPS.get(weight) if _ACTIVE_FLIPS is not None else None
             if flipped is None:
@@ -172,7 +175,9 @@ class _WgradStream:
     a side stream (which first waits for everything enqueued so far on the launching stream), and
     joined either when more than ``depth`` of them are pending or by a callback at the end of the
     backward pass.  The operands stay referenced until the join, so the allocator cannot hand
-    their memory to later kernels of the launching stream.  Works the same under CUDA-graph
+    their memory to later kernels of the launching stream.  Nothing on the launching stream may
+    read the result before the join: the fork is used only when the parameter has no ``.grad``
+    yet, so that autograd adopts the new tensor without launching a kernel on it.  Works the same under CUDA-graph
     capture (the fork / join become graph dependencies)."""
 
     depth = 4
@@ -197,7 +202,9 @@ class _WgradStream:
             out = fn()
             ev = torch.cuda.Event()
             ev.record(side)
-        self._pending.append((ev, main, keep, out))
+        # the result itself is NOT kept: a second reference would make autograd copy it (on the
+        # launching stream, before the join) instead of adopting it as the parameter's .grad
+        self._pending.append((ev, main, keep))
         if not self._callback_queued:
             torch.autograd.Variable._execution_engine.queue_callback(self.join)
             self._callback_queued = True
@@ -206,7 +213,7 @@ class _WgradStream:
         return out
 
     def _join_one(self):
-        ev, main, _keep, _out = self._pending.pop(0)
+        ev, main, _keep = self._pending.pop(0)
         main.wait_event(ev)
 
     def join(self):

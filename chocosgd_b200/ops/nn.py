@@ -11,7 +11,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False, "wgrad": False}
+_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False, "wgrad": False, "ce": False}
 
 
 def set_native(enabled: bool = True, which=("linear", "conv", "lstm", "bn")):
@@ -23,7 +23,7 @@ def available_kinds():
     """Kinds of layers whose native kernels are built into this tree."""
     import importlib.util
 
-    kinds = ["bn", "linear", "wgrad"]
+    kinds = ["bn", "linear", "wgrad", "ce"]
     for kind, mod in (("conv", "conv"), ("lstm", "lstm")):
         if importlib.util.find_spec(f"{__package__}.{mod}") is not None:
             kinds.append(kind)
@@ -34,7 +34,7 @@ def available_kinds():
 #: step.  ``linear`` (tcgen05 GEMM at about half of the library's TF32 throughput on large
 #: shapes) and ``lstm`` (per-timestep cell kernels against the library's persistent kernel) are
 #: opt-in through ``set_native`` / ``--native_layers all``.
-AUTO_KINDS = ("bn", "conv", "wgrad")
+AUTO_KINDS = ("bn", "conv", "wgrad", "ce")
 
 
 def configure_native(mode: str = "auto"):
@@ -45,9 +45,9 @@ def configure_native(mode: str = "auto"):
     if mode in ("off", None) or not torch.cuda.is_available():
         return
     if mode == "bn":
-        set_native(True, which=("bn", "linear"))
+        set_native(True, which=("bn", "linear", "ce"))
     elif mode == "conv":
-        set_native(True, which=("bn", "linear", "conv"))
+        set_native(True, which=("bn", "linear", "conv", "ce"))
     elif mode == "all":
         set_native(True, which=available_kinds())
     else:

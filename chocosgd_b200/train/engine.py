@@ -22,6 +22,7 @@ from typing import Optional
 
 import torch
 
+from ..ops.ce import criterion_is_plain_ce, cross_entropy as fused_cross_entropy, supported as ce_supported
 from ..ops.sgd import grad_clip_
 
 
@@ -67,8 +68,11 @@ class TrainStep:
         self.kernel_launches_per_step = None
         self.flips = None
         self.bn_counters = None
+        self._fused_ce = False
         if self.is_cuda:
             from ..ops import nn as native_nn
+
+            self._fused_ce = native_nn.native_enabled("ce") and criterion_is_plain_ce(criterion)
 
             if native_nn.native_enabled("bn"):
                 from ..ops.bn import BnCounters
@@ -94,14 +98,19 @@ class TrainStep:
             for p in params:
                 p.grad = None  # autograd then hands over its own gradient tensors (no accumulate kernels)
         ctx = torch.autocast("cuda", dtype=self.amp_dtype) if self.amp_dtype is not None else _null()
+        stats = None
         with ctx:
             if self.hidden is not None:
                 h = tuple(t.detach() for t in self.hidden)
                 out, new_h = self.model(self.static_input, h)
-                loss = self.criterion(out.reshape(-1, out.size(-1)), self.static_target.reshape(-1))
+                logits, tgt = out.reshape(-1, out.size(-1)), self.static_target.reshape(-1)
             else:
                 out = self.model(self.static_input)
-                loss = self.criterion(out, self.static_target)
+                logits, tgt = out, self.static_target
+            if self._fused_ce and logits.dim() == 2 and ce_supported(logits, tgt):
+                loss, stats = fused_cross_entropy(logits, tgt, True)  # loss, gradient, accuracies: one kernel
+            else:
+                loss = self.criterion(logits, tgt)
         loss.backward()
         if self.flips is not None:
             self.flips.valid = False
@@ -111,10 +120,11 @@ class TrainStep:
                     dst.copy_(src.detach())
             self.loss.copy_(loss.detach().float())
             if self.metrics is not None:
-                tgt = self.static_target.reshape(-1) if self.hidden is not None else self.static_target
-                o = out.reshape(-1, out.size(-1)) if self.hidden is not None else out
-                perf = self.metrics.evaluate(loss, o.float(), tgt)
-                self.perf.copy_(torch.stack([p.float() for p in perf]))
+                if stats is not None and self.metrics.task == "classification":
+                    self.perf.copy_(stats[1:1 + len(self.metrics.metric_names)])
+                else:
+                    perf = self.metrics.evaluate(loss, logits.float(), tgt)
+                    self.perf.copy_(torch.stack([p.float() for p in perf]))
         return loss
 
     def prime(self):
