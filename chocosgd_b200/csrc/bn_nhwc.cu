@@ -372,6 +372,18 @@ extern "C" int bn_forward(const BnArgs* args, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
+// Forward when the producer of x already left per-CTA (sum, sum of squares) rows in args->partial
+// ([n_partials][2C], e.g. the convolution epilogue): no reduction pass over x at all.
+extern "C" int bn_forward_partials(const BnArgs* args, int n_partials, cudaStream_t st) {
+  BnArgs a = *args;
+  if (a.C % 4 != 0 || BN_THREADS % (a.C / 4) != 0 || a.C / 4 > BN_THREADS || a.C > BN_MAX_C) return -1;
+  if (n_partials < 1 || (long long)n_partials * 2 * a.C > BN_FUSED_LIMIT || a.partial == nullptr) return -2;
+  a.n_partials = n_partials;
+  a.fused_finalize = 1;
+  bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4), BN_THREADS, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int bn_backward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (bn_prepare(a) != 0) return -1;

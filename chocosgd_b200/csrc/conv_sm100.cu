@@ -15,6 +15,7 @@
 // filter flipped and its channel roles exchanged (conv_flip_weights), so one kernel serves
 // forward and dgrad.  Bounded mbarrier waits as in the GEMM kernel; no cluster multicast.
 #include "tc_common.cuh"
+#include <stdlib.h>
 
 #define CONV_THREADS 192
 #define CONV_STAGES 6
@@ -131,6 +132,227 @@ conv3x3_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   }
 }
 
+// ---- persistent variant ---------------------------------------------------------------------------
+// One CTA per SM walks over several 128-pixel tiles.  The TMA producer keeps running ahead across
+// tile boundaries, the accumulator is double-buffered in TMEM (tile t+1 is multiplied while the
+// epilogue warps drain tile t), and the epilogue can also produce the per-channel sum and sum of
+// squares of everything the CTA wrote - the batch-norm statistics of the layer that follows - as
+// ONE row [2 C_out] of partials per CTA, added in a fixed order (reproducible).  The batch-norm
+// forward then needs no reduction pass over the activation tensor.
+struct ConvPArgs {
+  float* y;        // [N*H*W, C_out]
+  float* stats;    // optional [gridDim.x][2 C_out]: sum, sum of squares per channel
+  int* error;
+  int H, W, Cin;
+  int TH, TN;
+  int tiles_h;
+  int n_tiles;
+  int relu;
+};
+
+// One CTA per SM has a single MMA-issuing thread and a single barrier round trip per pipeline
+// slot, so a slot holds GK k-blocks (all 9 filter taps for 16 channels, 3 otherwise): one wait,
+// 2 GK .. 4 GK tensor-core instructions, one commit.  GK lanes of the producer warp issue the
+// loads of a slot in parallel.  As many slots as fit beside the epilogue tile in ~200 KB.
+template <int COUT, int KC>
+struct ConvPCfg {
+  static constexpr int TSTRIDE = COUT + 4;  // floats per row of the epilogue tile (bank-conflict free)
+  static constexpr int KB_BYTES = 128 * KC * 4 + COUT * KC * 4;
+  static constexpr int ROOM = 200 * 1024 - 128 * TSTRIDE * 4;
+  static constexpr int GK = 2 * 9 * KB_BYTES <= ROOM ? 9 : (2 * 3 * KB_BYTES <= ROOM ? 3 : 1);
+  static constexpr int FIT = ROOM / (GK * KB_BYTES);
+  static constexpr int STAGES = FIT > 8 ? 8 : (FIT < 2 ? 2 : FIT);
+};
+
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// barrier of the 128 epilogue threads that also ORs a flag: every thread gets the same answer
+__device__ __forceinline__ bool epi_bar_or(bool flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r) : "r"((uint32_t)flag) : "memory");
+  return r != 0;
+}
+
+template <int COUT, int KC>
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ConvPArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int S = ConvPCfg<COUT, KC>::STAGES, TS = ConvPCfg<COUT, KC>::TSTRIDE, GK = ConvPCfg<COUT, KC>::GK;
+  constexpr int ROW = KC * 4;
+  constexpr int A_BYTES = 128 * ROW;
+  constexpr int B_BYTES = COUT * ROW;
+  constexpr uint32_t LAYOUT = ROW == 128 ? 2u : 4u;
+  constexpr uint32_t SBO = 8 * ROW;
+  uint8_t* sA = smem;                          // [S][GK][A_BYTES]
+  uint8_t* sB = smem + S * GK * A_BYTES;        // [S][GK][B_BYTES]
+  float* sT = reinterpret_cast<float*>(sB + S * GK * B_BYTES);     // [128][TS] epilogue tile
+  uint64_t* full = reinterpret_cast<uint64_t*>(sT + 128 * TS);
+  uint64_t* empty = full + S;
+  uint64_t* acc_full = empty + S;    // [2]
+  uint64_t* acc_empty = acc_full + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cblocks = g.Cin / KC;
+  const int n_kb = 9 * cblocks;
+  const int n_grp = n_kb / GK;                  // slots per tile (9 cblocks is a multiple of GK)
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + b, 1);
+      mbar_init(acc_empty + b, 4);   // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  constexpr uint32_t TMEM_COLS = 2 * COUT < 32 ? 32 : 2 * COUT;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    const int my_tiles = (g.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const uint32_t total = (uint32_t)my_tiles * (uint32_t)n_grp;
+    for (uint32_t gi = 0; gi < total; ++gi) {
+      const uint32_t s = gi % S;
+      int ok = 1;
+      if (lane == 0) {
+        if (gi >= (uint32_t)S && !mbar_wait(empty + s, ((gi / S) - 1) & 1)) ok = 0;
+        if (*abort_flag) ok = 0;
+        if (ok) mbar_expect_tx(full + s, GK * (A_BYTES + B_BYTES));
+        else *abort_flag = 1;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < GK) {
+        const int tile = (int)blockIdx.x + (int)(gi / n_grp) * (int)gridDim.x;
+        const int i = (int)(gi % n_grp) * GK + lane;
+        const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
+        const int tap = i / cblocks, c0 = (i % cblocks) * KC;
+        const int r = tap / 3, t = tap % 3;
+        tma_load_4d(sA + (s * GK + lane) * A_BYTES, &map_x, full + s, c0, t - 1, h0 + r - 1, n0);
+        tma_load_2d(sB + (s * GK + lane) * B_BYTES, &map_w, full + s, tap * g.Cin + c0, 0);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 5 && lane == 0) {
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(COUT >> 3) << 17) | ((128u >> 4) << 24);
+    uint32_t it = 0, lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < g.n_tiles && ok; tile += gridDim.x, ++lt) {
+      const uint32_t buf = lt & 1;
+      if (lt >= 2 && !mbar_wait(acc_empty + buf, ((lt >> 1) - 1) & 1)) { *abort_flag = 1; ok = false; break; }
+      tc_fence_after();
+      const uint32_t d = tmem_base + buf * COUT;
+      for (int gq = 0; gq < n_grp; ++gq, ++it) {
+        const uint32_t s = it % S;
+        if (!mbar_wait(full + s, (it / S) & 1)) { *abort_flag = 1; ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int j = 0; j < GK; ++j) {
+          const uint32_t a_addr = smem_u32(sA + (s * GK + j) * A_BYTES), b_addr = smem_u32(sB + (s * GK + j) * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < KC / 8; ++k)
+            umma_tf32(d, make_desc(a_addr + k * 32, 16, SBO, LAYOUT), make_desc(b_addr + k * 32, 16, SBO, LAYOUT), idesc,
+                      (gq > 0 || j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(empty + s);
+      }
+      if (ok) tc_commit(acc_full + buf);
+    }
+  } else if (warp < 4) {
+    const int t128 = threadIdx.x;                 // 0..127
+    constexpr int NSEG = 128 / COUT > 0 ? 128 / COUT : 1;
+    const int sc = t128 % COUT, sseg = t128 / COUT;   // statistics: this thread's channel and pixel segment
+    float s0 = 0.f, s1 = 0.f;
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < g.n_tiles; tile += gridDim.x, ++lt) {
+      const uint32_t buf = lt & 1;
+      const bool bad = !mbar_wait(acc_full + buf, (lt >> 1) & 1) || *abort_flag != 0;
+      if (epi_bar_or(bad)) {                       // the same decision in all 128 epilogue threads
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
+      const size_t pix = ((size_t)n0 * g.H + h0) * g.W + t128;
+      float* out = g.y + pix * COUT;
+      float* trow = sT + t128 * TS;
+#pragma unroll 1
+      for (int c = 0; c < COUT; c += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * COUT + (uint32_t)c, v);
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                 __uint_as_float(v[j + 3]));
+          if (g.relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
+          *reinterpret_cast<float4*>(out + c + j) = o;
+          if (g.stats != nullptr) *reinterpret_cast<float4*>(trow + c + j) = o;
+        }
+      }
+      // the accumulator buffer may be overwritten by the tile after next
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + buf);
+      if (g.stats != nullptr) {
+        epi_bar();
+        if (sseg < NSEG) {
+          const float* col = sT + (size_t)(sseg * COUT) * TS + sc;
+#pragma unroll 8
+          for (int i = 0; i < COUT; ++i) {
+            const float x = col[(size_t)i * TS];
+            s0 += x;
+            s1 = fmaf(x, x, s1);
+          }
+        }
+        epi_bar();
+      }
+    }
+    if (g.stats != nullptr && ok) {
+      if (sseg < NSEG) {
+        sT[(sseg * COUT + sc) * 2] = s0;
+        sT[(sseg * COUT + sc) * 2 + 1] = s1;
+      }
+      epi_bar();
+      if (t128 < COUT) {
+        float a0 = 0.f, a1 = 0.f;
+        for (int sg = 0; sg < NSEG; ++sg) {
+          a0 += sT[(sg * COUT + t128) * 2];
+          a1 += sT[(sg * COUT + t128) * 2 + 1];
+        }
+        g.stats[(size_t)blockIdx.x * 2 * COUT + t128] = a0;
+        g.stats[(size_t)blockIdx.x * 2 * COUT + COUT + t128] = a1;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(g.error, 1);
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // W'[ci, r, s, co] = W[co, 2 - r, 2 - s, ci]   (both KRSC): the filter of the input-gradient convolution
 __global__ void conv_flip_weights_kernel(const float* __restrict__ w, float* __restrict__ out, int cout, int cin) {
   const int total = cout * 9 * cin;
@@ -203,6 +425,20 @@ static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, const ConvA
   return (int)cudaGetLastError();
 }
 
+template <int COUT, int KC>
+static int launch_conv_persist(const CUtensorMap& mx, const CUtensorMap& mw, const ConvPArgs& g, int grid, cudaStream_t st) {
+  using Cfg = ConvPCfg<COUT, KC>;
+  constexpr int smem = Cfg::STAGES * Cfg::GK * Cfg::KB_BYTES + 128 * Cfg::TSTRIDE * 4 + 1024 + 512;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(conv3x3_persist_kernel<COUT, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  conv3x3_persist_kernel<COUT, KC><<<grid, CONV_THREADS, smem, st>>>(mx, mw, g);
+  return (int)cudaGetLastError();
+}
+
 // 1 when conv3x3_tf32 handles this shape
 extern "C" int conv3x3_supported(int N, int H, int W, int Cin, int Cout) {
   if (!(W == 8 || W == 16 || W == 32)) return 0;
@@ -217,9 +453,57 @@ extern "C" int conv3x3_supported(int N, int H, int W, int Cin, int Cout) {
   return 1;
 }
 
+static int conv_use_persistent() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("CHOCO_CONV_PERSISTENT");
+    v = e == nullptr || atoi(e) != 0;
+  }
+  return v;
+}
+
+// CTAs of the persistent kernel: one per SM at most, and few enough that the rows of statistics
+// partials (2 C_out floats per CTA) can be added by every CTA of the batch-norm kernel itself.
+extern "C" int conv3x3_grid(int N, int H, int W, int Cout) {
+  int th = 128 / W;
+  if (th > H) th = H;
+  const int tn = 128 / (W * th);
+  if (tn < 1 || th < 1) return 0;
+  const int tiles = (N / tn) * (H / th);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+  }
+  int g = tiles < sms ? tiles : sms;
+  const int cap = 8192 / (2 * Cout);
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  // even out the tiles per CTA (e.g. 256 tiles on 128 CTAs rather than 148 with one or two each)
+  const int per = (tiles + g - 1) / g;
+  g = (tiles + per - 1) / per;
+  return g;
+}
+
+static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N, int H, int W, int Cin, int Cout,
+                       int relu, cudaStream_t st);
+
 // x [N,H,W,Cin], w [Cout,3,3,Cin], y [N,H,W,Cout], all fp32 NHWC / KRSC
 extern "C" int conv3x3_tf32(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout, int relu,
                             cudaStream_t st) {
+  return conv3x3_run(x, w, y, nullptr, N, H, W, Cin, Cout, relu, st);
+}
+
+// same, and stats[conv3x3_grid()][2 Cout] receives per-CTA (sum, sum of squares) of y per channel
+extern "C" int conv3x3_tf32_stats(const void* x, const void* w, void* y, void* stats, int N, int H, int W, int Cin,
+                                  int Cout, cudaStream_t st) {
+  if (stats == nullptr) return -1;
+  return conv3x3_run(x, w, y, stats, N, H, W, Cin, Cout, 0, st);
+}
+
+static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N, int H, int W, int Cin, int Cout,
+                       int relu, cudaStream_t st) {
   if (!conv3x3_supported(N, H, W, Cin, Cout)) return -1;
   int th = 128 / W;
   if (th > H) th = H;
@@ -247,6 +531,17 @@ extern "C" int conv3x3_tf32(const void* x, const void* w, void* y, int N, int H,
   if (g.error == nullptr) return -13;
   g.H = H; g.W = W; g.Cin = Cin; g.TH = th; g.TN = tn; g.tiles_h = H / th; g.relu = relu;
   const int tiles = (N / tn) * (H / th);
+  if (stats != nullptr || conv_use_persistent()) {
+    ConvPArgs pg;
+    pg.y = g.y; pg.stats = reinterpret_cast<float*>(stats); pg.error = g.error;
+    pg.H = H; pg.W = W; pg.Cin = Cin; pg.TH = th; pg.TN = tn; pg.tiles_h = H / th; pg.n_tiles = tiles; pg.relu = relu;
+    const int grid = conv3x3_grid(N, H, W, Cout);
+#define CONVP_CASE(CO)                                                             \
+  if (Cout == CO) return kc == 32 ? launch_conv_persist<CO, 32>(mx, mw, pg, grid, st) : launch_conv_persist<CO, 16>(mx, mw, pg, grid, st);
+    CONVP_CASE(16) CONVP_CASE(32) CONVP_CASE(64) CONVP_CASE(128)
+#undef CONVP_CASE
+    return -1;
+  }
 #define CONV_CASE(CO)                                                              \
   if (Cout == CO) return kc == 32 ? launch_conv<CO, 32>(mx, mw, g, tiles, st) : launch_conv<CO, 16>(mx, mw, g, tiles, st);
   CONV_CASE(16) CONV_CASE(32) CONV_CASE(64) CONV_CASE(128)

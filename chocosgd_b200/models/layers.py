@@ -31,6 +31,14 @@ def bn_act(bn, x, residual=None, relu=True):
     return _f(bn, x, residual, relu)
 
 
+def conv_bn_act(conv, bn, x, residual=None, relu=True):
+    """relu(bn(conv(x)) + residual); on the native path the convolution epilogue also yields the
+    batch statistics, so no reduction pass runs over the activation."""
+    from ..ops.bn import conv_bn_act as _f
+
+    return _f(conv, bn, x, residual, relu)
+
+
 def conv3x3(in_planes, out_planes, stride=1):
     return Conv2d(in_planes, out_planes, kernel_size=3, stride=stride, padding=1, bias=False)
 

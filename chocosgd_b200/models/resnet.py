@@ -26,8 +26,8 @@ class BasicBlock(nn.Module):
 
     def forward(self, x):
         residual = x if self.downsample is None else self.downsample(x)
-        out = L.bn_act(self.bn1, self.conv1(x))
-        return L.bn_act(self.bn2, self.conv2(out), residual=residual)
+        out = L.conv_bn_act(self.conv1, self.bn1, x)
+        return L.conv_bn_act(self.conv2, self.bn2, out, residual=residual)
 
 
 class Bottleneck(nn.Module):
@@ -47,9 +47,9 @@ class Bottleneck(nn.Module):
 
     def forward(self, x):
         residual = x if self.downsample is None else self.downsample(x)
-        out = L.bn_act(self.bn1, self.conv1(x))
-        out = L.bn_act(self.bn2, self.conv2(out))
-        return L.bn_act(self.bn3, self.conv3(out), residual=residual)
+        out = L.conv_bn_act(self.conv1, self.bn1, x)
+        out = L.conv_bn_act(self.conv2, self.bn2, out)
+        return L.conv_bn_act(self.conv3, self.bn3, out, residual=residual)
 
 
 class _ResNetBase(nn.Module):
@@ -87,7 +87,7 @@ class ResNetCifar(_ResNetBase):
         L.he_init(self)
 
     def forward(self, x):
-        x = L.bn_act(self.bn1, self.conv1(x))
+        x = L.conv_bn_act(self.conv1, self.bn1, x)
         x = self.layer3(self.layer2(self.layer1(x)))
         x = self.avgpool(x)
         return self.fc(x.reshape(x.size(0), -1))
@@ -121,7 +121,7 @@ class ResNetImagenet(_ResNetBase):
         L.he_init(self)
 
     def forward(self, x):
-        x = self.maxpool(L.bn_act(self.bn1, self.conv1(x)))
+        x = self.maxpool(L.conv_bn_act(self.conv1, self.bn1, x))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = self.avgpool(x)
         return self.fc(x.reshape(x.size(0), -1))

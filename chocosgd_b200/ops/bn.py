@@ -30,6 +30,8 @@ def _lib_bn():
             fn = getattr(lib, name)
             fn.argtypes = [ctypes.POINTER(BnArgsC), ctypes.c_void_p]
             fn.restype = ctypes.c_int
+        lib.bn_forward_partials.argtypes = [ctypes.POINTER(BnArgsC), ctypes.c_int, ctypes.c_void_p]
+        lib.bn_forward_partials.restype = ctypes.c_int
         lib.bn_reduce_grid.argtypes = [ctypes.c_int, ctypes.c_int]
         lib.bn_reduce_grid.restype = ctypes.c_int
         lib.bn_args_size.restype = ctypes.c_int
@@ -58,7 +60,7 @@ def supported(x, C) -> bool:
 
 class _BnActFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gamma, beta, residual, running_mean, running_var, relu, momentum, eps):
+    def forward(ctx, x, gamma, beta, residual, running_mean, running_var, relu, momentum, eps, stats=None):
         lib = _lib_bn()
         N, C, H, W = x.shape
         P = N * H * W
@@ -74,7 +76,12 @@ class _BnActFn(torch.autograd.Function):
         a.running_var = running_var.data_ptr() if running_var is not None else 0
         a.partial, a.counter = partial.data_ptr(), counter.data_ptr()
         a.P, a.C, a.relu, a.eps, a.momentum = P, C, int(relu), float(eps), float(momentum)
-        rc = lib.bn_forward(ctypes.byref(a), _lib.stream_ptr())
+        if stats is not None:
+            # per-CTA (sum, sum of squares) rows left by the producing convolution's epilogue
+            a.partial = stats.data_ptr()
+            rc = lib.bn_forward_partials(ctypes.byref(a), stats.shape[0], _lib.stream_ptr())
+        else:
+            rc = lib.bn_forward(ctypes.byref(a), _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"bn_forward failed ({rc})")
         ctx.save_for_backward(x, y, gamma, mean, invstd)
@@ -103,11 +110,12 @@ class _BnActFn(torch.autograd.Function):
         rc = lib.bn_backward(ctypes.byref(a), _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"bn_backward failed ({rc})")
-        return dx, dgamma, dbeta, dres, None, None, None, None, None
+        return dx, dgamma, dbeta, dres, None, None, None, None, None, None
 
 
-def bn_act(bn, x, residual=None, relu=True):
-    """``relu(bn(x) + residual)`` with one fused kernel pair when possible."""
+def bn_act(bn, x, residual=None, relu=True, stats=None):
+    """``relu(bn(x) + residual)`` with one fused kernel pair when possible.  ``stats``: rows of
+    per-channel (sum, sum of squares) partials of ``x`` from its producer (``conv_bn_act``)."""
     from . import nn as native_nn
 
     if (native_nn.native_enabled("bn") and bn.training and bn.track_running_stats is not None
@@ -118,11 +126,26 @@ def bn_act(bn, x, residual=None, relu=True):
         mom = bn.momentum if bn.momentum is not None else 0.1
         rm = bn.running_mean if bn.track_running_stats else None
         rv = bn.running_var if bn.track_running_stats else None
-        return _BnActFn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps)
+        return _BnActFn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps, stats)
     out = stock_forward(bn, x)
     if residual is not None:
         out = out + residual
     return F.relu(out, inplace=True) if relu else out
+
+
+def conv_bn_act(conv, bn, x, residual=None, relu=True):
+    """``relu(bn(conv(x)) + residual)``.  When both layers run their native kernels the convolution
+    epilogue also produces the batch statistics, so the batch-norm needs no reduction pass."""
+    from . import nn as native_nn
+
+    if (native_nn.native_enabled("conv") and native_nn.native_enabled("bn") and bn.training and x.is_cuda
+            and bn.affine and bn.track_running_stats is not None and torch.is_grad_enabled()):
+        from .conv import conv2d_native, conv_supported
+
+        if conv_supported(conv, x) and (conv.out_channels // 4) <= 256 and 256 % (conv.out_channels // 4) == 0:
+            y, stats = conv2d_native(conv, x, want_stats=True)
+            return bn_act(bn, y, residual, relu, stats=stats)
+    return bn_act(bn, conv(x), residual, relu)
 
 
 def stock_forward(bn, x):

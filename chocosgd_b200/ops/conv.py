@@ -32,6 +32,10 @@ def _declare():
         lib.conv3x3_wgrad_last_error.restype = i
         lib.conv_flip_weights_multi.argtypes = [vp, i, i, vp]
         lib.conv_flip_weights_multi.restype = i
+        lib.conv3x3_tf32_stats.argtypes = [vp, vp, vp, vp, i, i, i, i, i, vp]
+        lib.conv3x3_tf32_stats.restype = i
+        lib.conv3x3_grid.argtypes = [i, i, i, i]
+        lib.conv3x3_grid.restype = i
         lib._conv_declared = True
     return lib
 
@@ -60,6 +64,20 @@ def conv3x3(x, w_krsc_ptr_tensor, cout, relu=False):
     if rc != 0:
         raise RuntimeError(f"conv3x3_tf32 failed ({rc})")
     return y
+
+
+def conv3x3_with_stats(x, weight, cout):
+    """``(y, stats)``: the convolution and, from the same kernel's epilogue, one row per CTA of
+    per-channel (sum, sum of squares) of ``y`` - the batch statistics of the layer that follows."""
+    lib = _declare()
+    n, cin, h, w = x.shape
+    y = torch.empty((n, cout, h, w), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+    stats = torch.empty((lib.conv3x3_grid(n, h, w, cout), 2 * cout), dtype=torch.float32, device=x.device)
+    rc = lib.conv3x3_tf32_stats(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), _lib.ptr(stats), n, h, w, cin, cout,
+                                _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"conv3x3_tf32_stats failed ({rc})")
+    return y, stats
 
 
 def last_error() -> int:
@@ -131,12 +149,21 @@ def set_active_flips(f):
 
 class _Conv3x3Fn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight):
+    def forward(ctx, x, weight, want_stats=False):
         ctx.save_for_backward(x, weight)
+        if want_stats:
+            y, stats = conv3x3_with_stats(x, weight, weight.shape[0])
+            ctx.mark_non_differentiable(stats)
+            return y, stats
         return conv3x3(x, weight, weight.shape[0])
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, _dstats=None):
+        dx, dw = _Conv3x3Fn._backward(ctx, dy)
+        return dx, dw, None
+
+    @staticmethod
+    def _backward(ctx, dy):
         x, weight = ctx.saved_tensors
         lib = _declare()
         dy = dy.contiguous(memory_format=torch.channels_last)
@@ -231,5 +258,5 @@ def set_wgrad_side_stream(on: bool):
     _WGRAD_STREAM.enabled = bool(on)
 
 
-def conv2d_native(m, x):
-    return _Conv3x3Fn.apply(x, m.weight)
+def conv2d_native(m, x, want_stats=False):
+    return _Conv3x3Fn.apply(x, m.weight, want_stats)

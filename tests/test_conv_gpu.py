@@ -46,3 +46,91 @@ def test_unsupported_shapes_fall_back():
     assert not conv_supported(conv, x)
     s2 = nnn.Conv2d(16, 32, 3, stride=2, padding=1, bias=False).cuda().to(memory_format=torch.channels_last)
     assert not conv_supported(s2, torch.randn(2, 16, 32, 32, device="cuda").contiguous(memory_format=torch.channels_last))
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout", SHAPES + [(128, 32, 16, 16, 32), (128, 64, 8, 8, 64)])
+def test_conv_epilogue_statistics(n, cin, h, w, cout):
+    """The persistent kernel's per-CTA (sum, sum of squares) rows add up to the statistics of y."""
+    from chocosgd_b200.ops.conv import conv3x3_with_stats, last_error
+
+    torch.manual_seed(1)
+    x = torch.randn(n, cin, h, w, device="cuda").contiguous(memory_format=torch.channels_last)
+    wt = (torch.randn(cout, cin, 3, 3, device="cuda") * 0.1).contiguous(memory_format=torch.channels_last)
+    y, stats = conv3x3_with_stats(x, wt, cout)
+    torch.cuda.synchronize()
+    assert last_error() == 0
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        ref = F.conv2d(x, wt, padding=1)
+    finally:
+        torch.backends.cudnn.allow_tf32 = True
+    assert (y - ref).abs().max() <= 5e-3 * ref.abs().max() + 1e-3
+    assert stats.shape[1] == 2 * cout and stats.shape[0] * 2 * cout <= 8192
+    tot = stats.double().sum(0)
+    s0 = y.double().sum(dim=(0, 2, 3))
+    s1 = (y.double() ** 2).sum(dim=(0, 2, 3))
+    torch.testing.assert_close(tot[:cout], s0, rtol=1e-4, atol=1e-2)
+    torch.testing.assert_close(tot[cout:], s1, rtol=1e-4, atol=1e-2)
+
+
+def _conv_bn_setup(seed=2):
+    from chocosgd_b200.ops import nn as nnn
+
+    torch.manual_seed(seed)
+    conv = nnn.Conv2d(32, 32, 3, padding=1, bias=False).cuda().to(memory_format=torch.channels_last)
+    bn = nnn.BatchNorm2d(32).cuda()
+    bn.weight.data.uniform_(0.5, 1.5)
+    bn.bias.data.uniform_(-0.5, 0.5)
+    x = torch.randn(16, 32, 16, 16, device="cuda").contiguous(memory_format=torch.channels_last).requires_grad_()
+    res = torch.randn(16, 32, 16, 16, device="cuda").contiguous(memory_format=torch.channels_last)
+    return conv, bn, x, res
+
+
+@pytest.mark.parametrize("residual", [False, True])
+def test_conv_bn_matches_library_composition(residual):
+    """conv -> batch-norm with the statistics taken from the convolution epilogue (+ residual),
+    forward and backward, against the library ops.  No ReLU here: a TF32-sized difference in a
+    pre-activation near zero flips its mask and changes the gradients by O(1) in either path."""
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.bn import conv_bn_act
+
+    conv, bn, x, res = _conv_bn_setup()
+    res = res if residual else None
+    bn_ref = torch.nn.BatchNorm2d(32).cuda()
+    bn_ref.load_state_dict(bn.state_dict())
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        r = bn_ref(F.conv2d(x, conv.weight, padding=1))
+        r = r + res if residual else r
+        g = torch.randn_like(r)
+        ref = torch.autograd.grad(r, (x, conv.weight, bn_ref.weight, bn_ref.bias), g)
+        nnn.set_native(True, which=("conv", "wgrad", "bn"))
+        out = conv_bn_act(conv, bn, x, res, relu=False)
+        got = torch.autograd.grad(out, (x, conv.weight, bn.weight, bn.bias), g)
+    finally:
+        nnn.set_native(False)
+        torch.backends.cudnn.allow_tf32 = True
+    pairs = [(out, r)] + list(zip(got, ref)) + [(bn.running_var, bn_ref.running_var), (bn.running_mean, bn_ref.running_mean)]
+    for a, b in pairs:
+        err = (a - b).abs().max().item()
+        assert err <= 5e-3 * b.abs().max().item() + 1e-3, (err, b.abs().max().item())
+
+
+def test_conv_bn_act_fused_equals_unfused_native():
+    """With ReLU and residual: statistics from the convolution epilogue against the batch-norm
+    kernel's own reduction over the same convolution output."""
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.bn import bn_act, conv_bn_act
+
+    conv, bn, x, res = _conv_bn_setup(3)
+    g = torch.randn(16, 32, 16, 16, device="cuda").contiguous(memory_format=torch.channels_last)
+    nnn.set_native(True, which=("conv", "wgrad", "bn"))
+    try:
+        a = conv_bn_act(conv, bn, x, res, relu=True)
+        ga = torch.autograd.grad(a, (x, conv.weight, bn.weight, bn.bias), g)
+        b = bn_act(bn, conv(x), res, True)
+        gb = torch.autograd.grad(b, (x, conv.weight, bn.weight, bn.bias), g)
+    finally:
+        nnn.set_native(False)
+    for u, v in [(a, b)] + list(zip(ga, gb)):
+        assert (u - v).abs().max().item() <= 1e-4 * v.abs().max().item() + 1e-5
