@@ -50,12 +50,15 @@ class _CrossEntropyFn(torch.autograd.Function):
                                            _lib.ptr(stats), _lib.ptr(loss), B, C, int(bool(may_ignore)),
                                            _lib.stream_ptr()), "cross_entropy_fused")
         ctx.save_for_backward(dz)
+        ctx.set_materialize_grads(False)  # no zero tensor for the statistics output
         ctx.mark_non_differentiable(stats)
         return loss, stats
 
     @staticmethod
     def backward(ctx, g_loss, _g_stats):
         (dz,) = ctx.saved_tensors
+        if g_loss is None:
+            return None, None, None
         return dz * g_loss, None, None
 
 

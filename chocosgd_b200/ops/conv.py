@@ -36,6 +36,12 @@ def _declare():
         lib.conv3x3_tf32_stats.restype = i
         lib.conv3x3_grid.argtypes = [i, i, i, i]
         lib.conv3x3_grid.restype = i
+        lib.conv3x3_wgrad16.argtypes = [vp, vp, vp, vp, i, i, i, vp]
+        lib.conv3x3_wgrad16.restype = i
+        lib.conv3x3_wgrad16_parts.argtypes = [i, i, i]
+        lib.conv3x3_wgrad16_parts.restype = i
+        lib.conv3x3_wgrad16_supported.argtypes = [i, i, i]
+        lib.conv3x3_wgrad16_supported.restype = i
         lib._conv_declared = True
     return lib
 
@@ -85,11 +91,26 @@ def last_error() -> int:
     return lib.conv3x3_last_error() | lib.conv3x3_wgrad_last_error()
 
 
+def wgrad_supported(n, h, w, cin, cout) -> bool:
+    """True when a native weight-gradient kernel covers the shape: tcgen05 for 32 / 64 channels,
+    the warp-level tensor-core kernel for 16 channels."""
+    lib = _declare()
+    if cin == cout == 16:
+        return bool(lib.conv3x3_wgrad16_supported(n, h, w))
+    return bool(lib.conv3x3_wgrad_supported(n, h, w, cin, cout))
+
+
 def conv3x3_wgrad(x, dy, weight):
-    """dW (same memory order as ``weight``: [C_out, 3, 3, C_in]) by the tcgen05 kernel."""
+    """dW (same memory order as ``weight``: [C_out, 3, 3, C_in]) by the native kernels."""
     lib = _declare()
     n, c, h, w = x.shape
     dw = torch.empty_like(weight)
+    if c == 16:
+        scratch = torch.empty(lib.conv3x3_wgrad16_parts(n, h, w) * 2304, dtype=torch.float32, device=x.device)
+        rc = lib.conv3x3_wgrad16(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, h, w, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"conv3x3_wgrad16 failed ({rc})")
+        return dw
     scratch = torch.empty(lib.conv3x3_wgrad_parts(n, h, w) * 9 * c * c, dtype=torch.float32, device=x.device)
     rc = lib.conv3x3_wgrad_tf32(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, h, w, c,
                                 _lib.stream_ptr())
@@ -151,6 +172,7 @@ class _Conv3x3Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, want_stats=False):
         ctx.save_for_backward(x, weight)
+        ctx.set_materialize_grads(False)  # no zero-filled gradient tensor for the statistics output
         if want_stats:
             y, stats = conv3x3_with_stats(x, weight, weight.shape[0])
             ctx.mark_non_differentiable(stats)
@@ -159,6 +181,8 @@ class _Conv3x3Fn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, _dstats=None):
+        if dy is None:
+            return None, None, None
         dx, dw = _Conv3x3Fn._backward(ctx, dy)
         return dx, dw, None
 
@@ -174,7 +198,7 @@ class _Conv3x3Fn(torch.autograd.Function):
 
         # the weight gradient is forked first so that it does not wait for this layer's dgrad
         if ctx.needs_input_grad[1]:
-            if native_nn.native_enabled("wgrad") and lib.conv3x3_wgrad_supported(n, h, w, cin, cout):
+            if native_nn.native_enabled("wgrad") and wgrad_supported(n, h, w, cin, cout):
                 fn = lambda: conv3x3_wgrad(x, dy, weight)
             else:
                 fn = lambda: torch.ops.aten.convolution_backward(
