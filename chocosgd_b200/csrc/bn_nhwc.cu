@@ -327,9 +327,17 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnArgs a) {
   }
 }
 
-static int grid_for(long long n4) {
+// CTAs of the elementwise kernels.  Every CTA first reads the rows of partials (fused finalize),
+// so their number is kept lower when there are partials to read: 4 per SM instead of 8.
+static int grid_for(long long n4, int fused = 0) {
+  static int cap_fused = 0;
+  if (cap_fused == 0) {
+    const char* e = getenv("CHOCO_BN_APPLY_CTAS");
+    cap_fused = e != nullptr && atoi(e) > 0 ? atoi(e) : 148 * 4;
+  }
+  const long long cap = fused ? cap_fused : 148 * 8;
   long long b = (n4 + BN_THREADS - 1) / BN_THREADS;
-  if (b > 148 * 8) b = 148 * 8;
+  if (b > cap) b = cap;
   return (int)(b < 1 ? 1 : b);
 }
 
@@ -368,7 +376,7 @@ extern "C" int bn_forward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (bn_prepare(a) != 0) return -1;
   bn_reduce_kernel<false><<<a.n_partials, BN_THREADS, 0, st>>>(a);
-  bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4), BN_THREADS, 0, st>>>(a);
+  bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4, a.fused_finalize), BN_THREADS, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
 
@@ -380,7 +388,7 @@ extern "C" int bn_forward_partials(const BnArgs* args, int n_partials, cudaStrea
   if (n_partials < 1 || (long long)n_partials * 2 * a.C > BN_FUSED_LIMIT || a.partial == nullptr) return -2;
   a.n_partials = n_partials;
   a.fused_finalize = 1;
-  bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4), BN_THREADS, 0, st>>>(a);
+  bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4, a.fused_finalize), BN_THREADS, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
 
@@ -388,7 +396,7 @@ extern "C" int bn_backward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (bn_prepare(a) != 0) return -1;
   bn_reduce_kernel<true><<<a.n_partials, BN_THREADS, 0, st>>>(a);
-  bn_bwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4), BN_THREADS, 0, st>>>(a);
+  bn_bwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4, a.fused_finalize), BN_THREADS, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
 

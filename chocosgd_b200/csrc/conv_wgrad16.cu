@@ -161,13 +161,18 @@ __global__ void __launch_bounds__(WG16_THREADS) conv3x3_wgrad16_kernel(Wg16Args 
     out[i] = ((red[i] + red[WG16_OUT + i]) + red[2 * WG16_OUT + i]) + red[3 * WG16_OUT + i];
 }
 
-__global__ void wgrad16_reduce_kernel(const float* __restrict__ partial, int n_parts, float* __restrict__ dw) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= WG16_OUT) return;
+// 64 outputs per CTA, 4 threads per output (slices q, q + 4, ... in order, then the four sub-sums)
+__global__ void __launch_bounds__(256) wgrad16_reduce_kernel(const float* __restrict__ partial, int n_parts,
+                                                             float* __restrict__ dw) {
+  __shared__ float sub[4][64];
+  const int il = threadIdx.x & 63, q = threadIdx.x >> 6;
+  const int i = blockIdx.x * 64 + il;
   float acc = 0.f;
 #pragma unroll 8
-  for (int s = 0; s < n_parts; ++s) acc += __ldcg(partial + (size_t)s * WG16_OUT + i);
-  dw[i] = acc;
+  for (int s = q; s < n_parts; s += 4) acc += __ldcg(partial + (size_t)s * WG16_OUT + i);
+  sub[q][il] = acc;
+  __syncthreads();
+  if (q == 0) dw[i] = ((sub[0][il] + sub[1][il]) + sub[2][il]) + sub[3][il];
 }
 
 extern "C" int conv3x3_wgrad16_supported(int N, int H, int W) {
@@ -218,7 +223,7 @@ extern "C" int conv3x3_wgrad16(const void* x, const void* dy, void* dw, void* sc
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  wgrad16_reduce_kernel<<<(WG16_OUT + 255) / 256, 256, 0, st>>>(reinterpret_cast<const float*>(scratch), grid,
+  wgrad16_reduce_kernel<<<WG16_OUT / 64, 256, 0, st>>>(reinterpret_cast<const float*>(scratch), grid,
                                                                reinterpret_cast<float*>(dw));
   return (int)cudaGetLastError();
 }

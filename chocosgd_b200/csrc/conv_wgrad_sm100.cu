@@ -200,14 +200,21 @@ static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const Wgr
   return (int)cudaGetLastError();
 }
 
-// dw[i] = sum over slices of partial[slice][i], slices added in index order
-__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, int n_parts, int n, float* __restrict__ dw) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
+// dw[i] = sum over slices of partial[slice][i].  64 outputs per CTA, 4 threads per output: thread q
+// adds the slices q, q + 4, ... in order, then the four sub-sums are added in order (reproducible).
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, int n_parts, int n,
+                                                           float* __restrict__ dw) {
+  __shared__ float sub[4][64];
+  const int il = threadIdx.x & 63, q = threadIdx.x >> 6;
+  const int i = blockIdx.x * 64 + il;
   float acc = 0.f;
+  if (i < n) {
 #pragma unroll 8
-  for (int s = 0; s < n_parts; ++s) acc += __ldcg(partial + (size_t)s * n + i);
-  dw[i] = acc;
+    for (int s = q; s < n_parts; s += 4) acc += __ldcg(partial + (size_t)s * n + i);
+  }
+  sub[q][il] = acc;
+  __syncthreads();
+  if (q == 0 && i < n) dw[i] = ((sub[0][il] + sub[1][il]) + sub[2][il]) + sub[3][il];
 }
 
 extern "C" int conv3x3_wgrad_parts(int N, int H, int W) {
@@ -253,7 +260,7 @@ extern "C" int conv3x3_wgrad_tf32(const void* x, const void* dy, void* dw, void*
   const int rc = C == 32 ? launch_wgrad<32>(mdy, mx, g, grid, st) : launch_wgrad<64>(mdy, mx, g, grid, st);
   if (rc) return rc;
   const int n = C * 9 * C;
-  wgrad_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(reinterpret_cast<const float*>(scratch), (int)grid.x, n,
+  wgrad_reduce_kernel<<<(n + 63) / 64, 256, 0, st>>>(reinterpret_cast<const float*>(scratch), (int)grid.x, n,
                                                        reinterpret_cast<float*>(dw));
   return (int)cudaGetLastError();
 }
