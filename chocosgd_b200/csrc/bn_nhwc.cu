@@ -327,6 +327,137 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnArgs a) {
   }
 }
 
+// ---- backward in ONE kernel ---------------------------------------------------------------------
+// One CTA per SM keeps its rows of x and of the masked gradient g in shared memory: phase 1 reads
+// x, dy, y once and leaves per-CTA partial sums, a grid-wide barrier follows (all CTAs are
+// co-resident: at most one per SM; bounded wait), then every CTA adds the partials in the same
+// fixed order and writes dx (and dresidual) from shared memory.  Half the global traffic and one
+// launch instead of two.  barrier[0] = arrivals, barrier[1] = generation, barrier[2] = error flag.
+__device__ __forceinline__ unsigned bn_ld_acquire(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(BN_THREADS, 1) bn_bwd_fused_kernel(BnArgs a, unsigned* barrier, int rows_per_cta) {
+  extern __shared__ float bn_dyn[];
+  __shared__ float st0[BN_MAX_C], st1[BN_MAX_C];
+  __shared__ double tot[2 * BN_MAX_C], shd[BN_THREADS];
+  __shared__ float sh[BN_THREADS * 8];
+  __shared__ int ok_flag;
+  const int C = a.C, tpr = C >> 2, rpb = BN_THREADS / tpr;
+  const int col = (threadIdx.x % tpr) * 4, rsub = threadIdx.x / tpr;
+  const int r0 = blockIdx.x * rows_per_cta;
+  const int r1 = min(a.P, r0 + rows_per_cta);
+  float* xs = bn_dyn;                                   // [rows_per_cta][C]
+  float* gs = bn_dyn + (size_t)rows_per_cta * C;
+  const unsigned my_gen = (threadIdx.x == 0) ? bn_ld_acquire(barrier + 1) : 0u;
+
+  const float4 m4 = *reinterpret_cast<const float4*>(a.mean + col);
+  const float4 i4 = *reinterpret_cast<const float4*>(a.invstd + col);
+  const float mu[4] = {m4.x, m4.y, m4.z, m4.w}, is[4] = {i4.x, i4.y, i4.z, i4.w};
+  float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int r = r0 + rsub; r < r1; r += 4 * rpb) {
+    float4 xv[4], gv[4], yv[4];
+    bool in[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int rr = r + u * rpb;
+      in[u] = rr < r1;
+      const size_t off = (size_t)(in[u] ? rr : r) * C + col;
+      xv[u] = *reinterpret_cast<const float4*>(a.x + off);
+      gv[u] = *reinterpret_cast<const float4*>(a.dy + off);
+      if (a.relu) yv[u] = *reinterpret_cast<const float4*>(a.y + off);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (!in[u]) continue;
+      const float xa[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+      float ga[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
+      if (a.relu) {
+        const float ya[4] = {yv[u].x, yv[u].y, yv[u].z, yv[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ga[e] = ya[e] > 0.f ? ga[e] : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        s0[e] += ga[e];
+        s1[e] = fmaf(ga[e], (xa[e] - mu[e]) * is[e], s1[e]);
+      }
+      const size_t lo = (size_t)(r + u * rpb - r0) * C + col;
+      *reinterpret_cast<float4*>(xs + lo) = xv[u];
+      *reinterpret_cast<float4*>(gs + lo) = make_float4(ga[0], ga[1], ga[2], ga[3]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    sh[threadIdx.x * 8 + e] = s0[e];
+    sh[threadIdx.x * 8 + 4 + e] = s1[e];
+  }
+  __syncthreads();
+  for (int stride = rpb >> 1; stride > 0; stride >>= 1) {
+    if (rsub < stride) {
+      float* mine = sh + threadIdx.x * 8;
+      const float* other = sh + (threadIdx.x + stride * tpr) * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mine[e] += other[e];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x < tpr) {
+    float* dst = a.partial + (size_t)blockIdx.x * 2 * C;
+    const float* p = sh + threadIdx.x * 8;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      dst[col + e] = p[e];
+      dst[C + col + e] = p[4 + e];
+    }
+  }
+  __syncthreads();
+  // ---- grid barrier (bounded) ---------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    __threadfence();
+    if (atomicAdd(barrier, 1u) == gridDim.x - 1) {
+      *barrier = 0;
+      __threadfence();
+      atomicAdd(barrier + 1, 1u);
+    } else {
+      unsigned spins = 0;
+      while (bn_ld_acquire(barrier + 1) == my_gen) {
+        __nanosleep(32);
+        if (++spins > (1u << 24)) { ok = 0; atomicExch(barrier + 2, 1u); break; }
+      }
+    }
+    ok_flag = ok;
+  }
+  __syncthreads();
+  if (!ok_flag) return;
+  // ---- statistics from the partials, then dx from shared memory -------------------------------------
+  bn_stats_to_smem<true>(a, st0, st1, tot, shd);
+  const float4 g4 = *reinterpret_cast<const float4*>(a.gamma + col);
+  const float ga4[4] = {g4.x, g4.y, g4.z, g4.w};
+  const float inv_p = 1.f / (float)a.P;
+  float cb[4], cg[4], sc[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    cb[e] = st0[col + e] * inv_p;
+    cg[e] = st1[col + e] * inv_p;
+    sc[e] = ga4[e] * is[e];
+  }
+  for (int r = r0 + rsub; r < r1; r += rpb) {
+    const size_t lo = (size_t)(r - r0) * C + col, off = (size_t)r * C + col;
+    const float4 xv = *reinterpret_cast<const float4*>(xs + lo);
+    const float4 gv = *reinterpret_cast<const float4*>(gs + lo);
+    const float xa[4] = {xv.x, xv.y, xv.z, xv.w}, gg[4] = {gv.x, gv.y, gv.z, gv.w};
+    float dx[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dx[e] = sc[e] * (gg[e] - cb[e] - (xa[e] - mu[e]) * is[e] * cg[e]);
+    *reinterpret_cast<float4*>(a.out + off) = make_float4(dx[0], dx[1], dx[2], dx[3]);
+    if (a.out2 != nullptr) *reinterpret_cast<float4*>(a.out2 + off) = gv;
+  }
+}
+
 // CTAs of the elementwise kernels.  Every CTA first reads the rows of partials (fused finalize),
 // so their number is kept lower when there are partials to read: 4 per SM instead of 8.
 static int grid_for(long long n4, int fused = 0) {
@@ -392,9 +523,61 @@ extern "C" int bn_forward_partials(const BnArgs* args, int n_partials, cudaStrea
   return (int)cudaGetLastError();
 }
 
+static unsigned* g_bn_barrier[64];
+
+static unsigned* bn_barrier_words() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (g_bn_barrier[dev] == nullptr) {
+    if (cudaMalloc(&g_bn_barrier[dev], 4 * sizeof(unsigned)) != cudaSuccess) return nullptr;
+    cudaMemset(g_bn_barrier[dev], 0, 4 * sizeof(unsigned));
+  }
+  return g_bn_barrier[dev];
+}
+
+// 1 when a grid barrier of the one-kernel backward gave up (reads the flag; synchronises)
+extern "C" int bn_last_error() {
+  unsigned* w = bn_barrier_words();
+  unsigned v[4] = {0, 0, 0, 0};
+  if (w == nullptr || cudaMemcpy(v, w, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return (int)v[2];
+}
+
 extern "C" int bn_backward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (bn_prepare(a) != 0) return -1;
+  static int fused_ok = -1, sms = 0;
+  if (fused_ok < 0) {
+    // opt-in: with the weight-gradient kernels of the same step running on a second stream the
+    // barrier has to wait until every SM is free, which measured slower (1.39 against 1.31 ms per
+    // ResNet-20 step) than the two-kernel form; alone on the GPU it halves the traffic
+    const char* e = getenv("CHOCO_BN_BWD_FUSED");
+    fused_ok = e != nullptr && atoi(e) != 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+  }
+  // one CTA per SM; its rows of x and g must fit in shared memory, its partial rows in the finalize
+  int G = sms;
+  while ((long long)G * 2 * a.C > BN_FUSED_LIMIT && G > 1) G >>= 1;
+  const int rows = (a.P + G - 1) / G;
+  G = (a.P + rows - 1) / rows;
+  const size_t dyn = (size_t)rows * a.C * 2 * sizeof(float);
+  if (fused_ok && a.fused_finalize && dyn <= 150 * 1024) {
+    unsigned* bar = bn_barrier_words();
+    if (bar == nullptr) return -13;
+    static size_t configured = 0;
+    if (dyn > configured) {
+      cudaError_t e = cudaFuncSetAttribute(bn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(150 * 1024));
+      if (e != cudaSuccess) return (int)e;
+      configured = 150 * 1024;
+    }
+    a.n_partials = G;
+    a.fused_finalize = 1;
+    bn_bwd_fused_kernel<<<G, BN_THREADS, dyn, st>>>(a, bar, rows);
+    return (int)cudaGetLastError();
+  }
   bn_reduce_kernel<true><<<a.n_partials, BN_THREADS, 0, st>>>(a);
   bn_bwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4, a.fused_finalize), BN_THREADS, 0, st>>>(a);
   return (int)cudaGetLastError();

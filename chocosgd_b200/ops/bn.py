@@ -34,6 +34,7 @@ def _lib_bn():
         lib.bn_forward_partials.restype = ctypes.c_int
         lib.bn_reduce_grid.argtypes = [ctypes.c_int, ctypes.c_int]
         lib.bn_reduce_grid.restype = ctypes.c_int
+        lib.bn_last_error.restype = ctypes.c_int
         lib.bn_args_size.restype = ctypes.c_int
         assert lib.bn_args_size() == ctypes.sizeof(BnArgsC)
         lib._bn_declared = True
@@ -51,6 +52,11 @@ def _get_scratch(device, P, C, lib):
                torch.zeros(1, dtype=torch.int32, device=device))
         _scratch[key] = buf
     return buf
+
+
+def last_error() -> int:
+    """Non-zero when a grid barrier of the one-kernel backward ran out of its wait budget."""
+    return _lib_bn().bn_last_error()
 
 
 def supported(x, C) -> bool:

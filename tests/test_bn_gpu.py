@@ -8,7 +8,8 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("shape,use_res,relu", [((8, 16, 32, 32), False, True), ((128, 16, 32, 32), True, True),
                                                 ((16, 64, 8, 8), True, True), ((4, 32, 16, 16), False, False),
-                                                ((3, 128, 5, 7), True, True)])
+                                                ((3, 128, 5, 7), True, True), ((128, 32, 16, 16), True, True),
+                                                ((256, 64, 32, 32), False, True)])
 def test_bn_act_matches_torch(shape, use_res, relu):
     from chocosgd_b200.ops import nn as nnn
     from chocosgd_b200.ops.bn import bn_act
@@ -44,3 +45,6 @@ def test_bn_act_matches_torch(shape, use_res, relu):
     torch.testing.assert_close(bn_b.running_mean, bn_a.running_mean, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(bn_b.running_var, bn_a.running_var, rtol=1e-4, atol=1e-5)
     assert int(bn_b.num_batches_tracked) == 1
+    from chocosgd_b200.ops.bn import last_error
+
+    assert last_error() == 0  # the grid barrier of the one-kernel backward never gave up
