@@ -146,9 +146,10 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True):
 
     if (native_nn.native_enabled("conv") and native_nn.native_enabled("bn") and bn.training and x.is_cuda
             and bn.affine and bn.track_running_stats is not None and torch.is_grad_enabled()):
-        from .conv import conv2d_native, conv_supported
+        from .conv import conv2d_native, conv_supported, first_conv_supported
 
-        if conv_supported(conv, x) and (conv.out_channels // 4) <= 256 and 256 % (conv.out_channels // 4) == 0:
+        if ((conv_supported(conv, x) or first_conv_supported(conv, x)) and (conv.out_channels // 4) <= 256
+                and 256 % (conv.out_channels // 4) == 0):
             y, stats = conv2d_native(conv, x, want_stats=True)
             return bn_act(bn, y, residual, relu, stats=stats)
     return bn_act(bn, conv(x), residual, relu)

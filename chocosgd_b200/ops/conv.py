@@ -282,5 +282,84 @@ def set_wgrad_side_stream(on: bool):
     _WGRAD_STREAM.enabled = bool(on)
 
 
+def _declare_first():
+    lib = _lib.load()
+    if not getattr(lib, "_conv_first_declared", False):
+        vp, i = ctypes.c_void_p, ctypes.c_int
+        lib.conv_first_supported.argtypes = [i, i]
+        lib.conv_first_grid.argtypes = [i, i, i, i]
+        lib.conv_first_wgrad_parts.argtypes = [i, i, i, i]
+        lib.conv_first_forward.argtypes = [vp, vp, vp, vp, i, i, i, i, vp]
+        lib.conv_first_wgrad.argtypes = [vp, vp, vp, vp, i, i, i, i, vp]
+        for n in ("conv_first_supported", "conv_first_grid", "conv_first_wgrad_parts", "conv_first_forward",
+                  "conv_first_wgrad"):
+            getattr(lib, n).restype = i
+        lib._conv_first_declared = True
+    return lib
+
+
+def first_conv_supported(m, x) -> bool:
+    """3x3 / stride 1 / pad 1 convolution of a 3-channel NHWC image (``csrc/conv_first.cu``)."""
+    if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 4 and m.weight.dtype == torch.float32):
+        return False
+    if m.kernel_size != (3, 3) or m.stride != (1, 1) or m.padding != (1, 1) or m.dilation != (1, 1):
+        return False
+    if m.groups != 1 or m.bias is not None or m.padding_mode != "zeros" or x.requires_grad:
+        return False
+    if not (x.is_contiguous(memory_format=torch.channels_last) and m.weight.is_contiguous(memory_format=torch.channels_last)):
+        return False
+    return bool(_declare_first().conv_first_supported(x.shape[1], m.out_channels))
+
+
+class _ConvFirstFn(torch.autograd.Function):
+    """First-layer convolution: fp32 FMA kernels, weight gradient only (the input is the image)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, want_stats=False):
+        lib = _declare_first()
+        n, _, h, w = x.shape
+        cout = weight.shape[0]
+        ctx.save_for_backward(x, weight)
+        ctx.set_materialize_grads(False)
+        y = torch.empty((n, cout, h, w), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+        stats = None
+        if want_stats:
+            stats = torch.empty((lib.conv_first_grid(n, h, w, cout), 2 * cout), dtype=torch.float32, device=x.device)
+        rc = lib.conv_first_forward(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), _lib.ptr(stats) if want_stats else None,
+                                    n, h, w, cout, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"conv_first_forward failed ({rc})")
+        if want_stats:
+            ctx.mark_non_differentiable(stats)
+            return y, stats
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, _dstats=None):
+        if dy is None or not ctx.needs_input_grad[1]:
+            return None, None, None
+        x, weight = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+
+        def fn():
+            lib = _declare_first()
+            n, _, h, w = x.shape
+            cout = weight.shape[0]
+            dw = torch.empty_like(weight)
+            scratch = torch.empty(lib.conv_first_wgrad_parts(n, h, w, cout) * cout * 27, dtype=torch.float32,
+                                  device=x.device)
+            rc = lib.conv_first_wgrad(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, h, w, cout,
+                                      _lib.stream_ptr())
+            if rc != 0:
+                raise RuntimeError(f"conv_first_wgrad failed ({rc})")
+            return dw
+
+        fork = _WGRAD_STREAM.enabled and weight.grad is None and not torch.is_grad_enabled()
+        dw = _WGRAD_STREAM.run(fn, (x, dy), x.device) if fork else fn()
+        return None, dw, None
+
+
 def conv2d_native(m, x, want_stats=False):
+    if m.in_channels == 3:
+        return _ConvFirstFn.apply(x, m.weight, want_stats)
     return _Conv3x3Fn.apply(x, m.weight, want_stats)

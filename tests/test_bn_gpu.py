@@ -48,3 +48,38 @@ def test_bn_act_matches_torch(shape, use_res, relu):
     from chocosgd_b200.ops.bn import last_error
 
     assert last_error() == 0  # the grid barrier of the one-kernel backward never gave up
+
+
+def test_one_kernel_backward_opt_in():
+    """The grid-barrier backward (CHOCO_BN_BWD_FUSED=1, read once per process) against PyTorch."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import torch, torch.nn.functional as F
+from chocosgd_b200.ops import nn as nnn
+from chocosgd_b200.ops.bn import bn_act, last_error
+torch.manual_seed(0)
+for shape in ((128, 16, 32, 32), (64, 32, 16, 16), (16, 64, 8, 8)):
+    C = shape[1]
+    x = (torch.randn(shape, device="cuda") * 2 + 0.5).contiguous(memory_format=torch.channels_last).requires_grad_()
+    res = torch.randn(shape, device="cuda").contiguous(memory_format=torch.channels_last).requires_grad_()
+    a, b = torch.nn.BatchNorm2d(C).cuda(), torch.nn.BatchNorm2d(C).cuda()
+    ref = F.relu(a(x) + res)
+    g = torch.randn_like(ref)
+    gr = torch.autograd.grad(ref, (x, a.weight, a.bias, res), g)
+    nnn.set_native(True, which=("bn",))
+    for _ in range(2):
+        out = bn_act(b, x, res, True)
+        gn = torch.autograd.grad(out, (x, b.weight, b.bias, res), g)
+    nnn.set_native(False)
+    for u, v in zip(gn, gr):
+        torch.testing.assert_close(u, v, rtol=2e-3, atol=2e-3 * float(v.abs().max()))
+assert last_error() == 0
+print("ok")
+"""
+    env = dict(os.environ, CHOCO_BN_BWD_FUSED="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]

@@ -134,3 +134,30 @@ def test_conv_bn_act_fused_equals_unfused_native():
         nnn.set_native(False)
     for u, v in [(a, b)] + list(zip(ga, gb)):
         assert (u - v).abs().max().item() <= 1e-4 * v.abs().max().item() + 1e-5
+
+
+@pytest.mark.parametrize("n,h,w,cout", [(4, 32, 32, 16), (128, 32, 32, 16), (3, 17, 9, 32), (2, 8, 8, 64)])
+def test_first_layer_convolution(n, h, w, cout):
+    """3-channel first convolution (fp32 FMA kernels): forward, statistics rows, weight gradient."""
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.conv import conv2d_native, first_conv_supported
+
+    torch.manual_seed(4)
+    conv = nnn.Conv2d(3, cout, 3, padding=1, bias=False).cuda().to(memory_format=torch.channels_last)
+    x = torch.randn(n, 3, h, w, device="cuda").contiguous(memory_format=torch.channels_last)
+    assert first_conv_supported(conv, x)
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        ref = F.conv2d(x, conv.weight, padding=1)
+        g = torch.randn_like(ref)
+        (gw_ref,) = torch.autograd.grad(ref, (conv.weight,), g)
+    finally:
+        torch.backends.cudnn.allow_tf32 = True
+    y, stats = conv2d_native(conv, x, want_stats=True)
+    (gw,) = torch.autograd.grad(y, (conv.weight,), g)
+    torch.testing.assert_close(y, ref, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(gw, gw_ref, rtol=1e-3, atol=1e-3 * float(gw_ref.abs().max()))
+    tot = stats.double().sum(0)
+    torch.testing.assert_close(tot[:cout], y.double().sum(dim=(0, 2, 3)), rtol=1e-4, atol=1e-2)
+    torch.testing.assert_close(tot[cout:], (y.double() ** 2).sum(dim=(0, 2, 3)), rtol=1e-4, atol=1e-2)
+    assert stats.shape[0] * 2 * cout <= 8192
