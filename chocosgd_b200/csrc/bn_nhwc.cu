@@ -218,13 +218,14 @@ __device__ void bn_stats_to_smem(const BnArgs& a, float* st0, float* st1, double
     const int col = cbase + threadIdx.x % cw, sub = threadIdx.x / cw;
     double t = 0.0;
     if (sub < nsub) {
+      // eight independent loads per trip; the adds keep a fixed order
       int b = sub;
-      for (; b + 3 * nsub < G; b += 4 * nsub) {
-        float u[4];
+      for (; b + 7 * nsub < G; b += 8 * nsub) {
+        float u[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) u[q] = __ldcg(a.partial + (size_t)(b + q * nsub) * C2 + col);
+        for (int q = 0; q < 8; ++q) u[q] = __ldcg(a.partial + (size_t)(b + q * nsub) * C2 + col);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) t += (double)u[q];
+        for (int q = 0; q < 8; ++q) t += (double)u[q];
       }
       for (; b < G; b += nsub) t += (double)__ldcg(a.partial + (size_t)b * C2 + col);
     }
