@@ -159,7 +159,10 @@ struct ConvPCfg {
   static constexpr int TSTRIDE = COUT + 4;  // floats per row of the epilogue tile (bank-conflict free)
   static constexpr int KB_BYTES = 128 * KC * 4 + COUT * KC * 4;
   static constexpr int ROOM = 200 * 1024 - 128 * TSTRIDE * 4;
-  static constexpr int GK = 2 * 9 * KB_BYTES <= ROOM ? 9 : (2 * 3 * KB_BYTES <= ROOM ? 3 : 1);
+#ifndef CONV_GK_MAX
+#define CONV_GK_MAX 9
+#endif
+  static constexpr int GK = (CONV_GK_MAX >= 9 && 2 * 9 * KB_BYTES <= ROOM) ? 9 : (2 * 3 * KB_BYTES <= ROOM ? 3 : 1);
   static constexpr int FIT = ROOM / (GK * KB_BYTES);
   static constexpr int STAGES = FIT > 8 ? 8 : (FIT < 2 ? 2 : FIT);
 };

@@ -17,7 +17,7 @@
 #include "tc_common.cuh"
 
 #define WG_THREADS 192
-#define WG_BSTAGES 6
+#define WG_BSTAGES 9
 
 struct WgradArgs {
   float* dw;       // partial results: [gridDim.x][C, 9, C]
@@ -73,19 +73,27 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
 
   if (n_my > 0) {
-    if (warp == 4 && lane == 0) {
+    if (warp == 4) {
       // ---------------- TMA producer ----------------
-      int bcount = 0;
-      for (int i = 0; i < n_my && !*abort_flag; ++i) {
-        const int tile = t_begin + i;
-        const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
-        const int p0 = (n0 * g.H + h0) * g.W;       // first pixel of the tile
-        const int ab = i & 1;
-        if (i >= 2 && !mbar_wait(a_empty + ab, ((i >> 1) - 1) & 1)) { *abort_flag = 1; break; }
-        mbar_expect_tx(a_full + ab, A_BYTES);
-        for (int j = 0; j < A_BLOCKS; ++j)
-          tma_load_2d(sA + ab * A_BYTES + j * TILE, &map_dy, a_full + ab, 32 * j, p0);
-        for (int tap = 0; tap < 9; ++tap, ++bcount) {
+      // lane 9 loads the dY tiles, lanes 0..8 one filter tap each: ten threads issue in parallel
+      // (a single thread cannot issue bulk-tensor loads fast enough to keep one SM busy)
+      if (lane == 9) {
+        for (int i = 0; i < n_my && !*abort_flag; ++i) {
+          const int tile = t_begin + i;
+          const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
+          const int p0 = (n0 * g.H + h0) * g.W;       // first pixel of the tile
+          const int ab = i & 1;
+          if (i >= 2 && !mbar_wait(a_empty + ab, ((i >> 1) - 1) & 1)) { *abort_flag = 1; break; }
+          mbar_expect_tx(a_full + ab, A_BYTES);
+          for (int j = 0; j < A_BLOCKS; ++j)
+            tma_load_2d(sA + ab * A_BYTES + j * TILE, &map_dy, a_full + ab, 32 * j, p0);
+        }
+      } else if (lane < 9) {
+        const int tap = lane;
+        for (int i = 0; i < n_my && !*abort_flag; ++i) {
+          const int tile = t_begin + i;
+          const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
+          const int bcount = i * 9 + tap;
           const int s = bcount % WG_BSTAGES;
           if (bcount >= WG_BSTAGES && !mbar_wait(b_empty + s, ((bcount / WG_BSTAGES) - 1) & 1)) { *abort_flag = 1; break; }
           mbar_expect_tx(b_full + s, TILE);

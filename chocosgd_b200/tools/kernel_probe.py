@@ -4,6 +4,7 @@
     python -m chocosgd_b200.tools.kernel_probe --case sign --elements 67108864
     python -m chocosgd_b200.tools.kernel_probe --case gemm --m 4096 --n 4096 --k 4096
     python -m chocosgd_b200.tools.kernel_probe --case conv --batch 128 --hw 32 --channels 16
+    python -m chocosgd_b200.tools.kernel_probe --case wgrad --batch 128 --hw 32 --channels 16
     python -m chocosgd_b200.tools.kernel_probe --case bn --batch 128 --hw 32 --channels 16
 """
 from __future__ import annotations
@@ -34,7 +35,7 @@ def timed(fn, iters):
 
 def main(argv=None):
     p = argparse.ArgumentParser()
-    p.add_argument("--case", required=True, choices=("sign", "topk", "qsgd", "randk", "gemm", "conv", "bn"))
+    p.add_argument("--case", required=True, choices=("sign", "topk", "qsgd", "randk", "gemm", "conv", "wgrad", "bn"))
     p.add_argument("--elements", type=int, default=64 * 1024 * 1024)
     p.add_argument("--m", type=int, default=4096)
     p.add_argument("--n", type=int, default=4096)
@@ -89,6 +90,23 @@ def main(argv=None):
         flops = 2.0 * a.batch * a.hw * a.hw * c * c * 9
         out.update(batch=a.batch, hw=a.hw, channels=c, ms=ms, tflops=flops / ms / 1e9, ms_cudnn=ms_lib,
                    io_GBps=2 * x.numel() * 4 / ms / 1e6, error=last_error())
+    elif a.case == "wgrad":
+        import os
+
+        from ..ops.conv import conv3x3_wgrad, last_error, wgrad_supported
+
+        os.environ["CHOCO_WGRAD_TCGEN05"] = "1"
+        c = a.channels
+        assert wgrad_supported(a.batch, a.hw, a.hw, c, c)
+        x = torch.randn(a.batch, c, a.hw, a.hw, device=dev).contiguous(memory_format=torch.channels_last)
+        dy = torch.randn(a.batch, c, a.hw, a.hw, device=dev).contiguous(memory_format=torch.channels_last)
+        w = torch.randn(c, c, 3, 3, device=dev).contiguous(memory_format=torch.channels_last)
+        ms = timed(lambda: conv3x3_wgrad(x, dy, w), a.iters)
+        torch.backends.cudnn.benchmark = True
+        ms_lib = timed(lambda: torch.ops.aten.convolution_backward(
+            dy, x, w, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1, (False, True, False)), a.iters)
+        out.update(batch=a.batch, hw=a.hw, channels=c, ms=ms, ms_cudnn=ms_lib, io_GBps=2 * x.numel() * 4 / ms / 1e6,
+                   error=last_error())
     else:
         from ..ops import nn as nnn
         from ..ops.bn import bn_act

@@ -11,8 +11,10 @@ SHAPES = [(4, 16, 32, 32, 16), (2, 32, 16, 16, 32), (4, 64, 8, 8, 64), (8, 32, 3
 
 @pytest.mark.parametrize("wgrad", [False, True])
 @pytest.mark.parametrize("n,cin,h,w,cout", SHAPES)
-def test_conv3x3_forward_and_dgrad(n, cin, h, w, cout, wgrad):
+def test_conv3x3_forward_and_dgrad(n, cin, h, w, cout, wgrad, monkeypatch):
     from chocosgd_b200.ops import nn as nnn
+
+    monkeypatch.setenv("CHOCO_WGRAD_TCGEN05", "1")  # exercise the tcgen05 weight-gradient kernel too
     from chocosgd_b200.ops.conv import conv_supported, last_error
 
     torch.manual_seed(0)
