@@ -56,7 +56,7 @@ def _mix32_int(x: int) -> int:
 def counter_uniform(seed: int, step: int, positions: torch.Tensor) -> torch.Tensor:
     """U[0,1) with 24 random bits, a pure function of (seed, step, flat position)."""
     base = _mix32_int((step * 0x9E3779B9 + 0x7F4A7C15) & _M32) ^ (seed & _M32)
-    h = mix32(mix32(positions.to(torch.int64) ^ base) + 0x85EBCA6B)
+    h = mix32(positions.to(torch.int64) ^ base)
     return (h >> 8).to(torch.float32) * (1.0 / 16777216.0)
 
 
@@ -141,7 +141,7 @@ def qsgd_quantize(x: torch.Tensor, s: int, u: torch.Tensor):
     flat = x.reshape(-1).to(torch.float32)
     norm = torch.sqrt(torch.sum(flat * flat))
     safe = torch.where(norm > 0, norm, torch.ones_like(norm))
-    lvl = (s * flat.abs()) / safe
+    lvl = flat.abs() * (float(s) / safe)  # one fp32 division per tensor, one multiply per element
     fl = torch.floor(lvl)
     lv = fl + (u < (lvl - fl)).to(torch.float32)
     lv = torch.where(norm > 0, lv, torch.zeros_like(lv))

@@ -35,20 +35,23 @@ __device__ __forceinline__ float qsgd_value(const uint32_t* planes, int nbits, i
 __device__ __forceinline__ void qsgd_accumulate4(const uint32_t* __restrict__ src, int nbits, int bit0, int n_valid,
                                                  float unit, float* acc, float* acc2, float w2) {
   if (nbits <= 7) {
-    uint32_t pw[8];
+    // The four positions' bits of one plane are a nibble; multiplying it by 0x00204081 and masking
+    // with 0x01010101 drops bit e into byte e, so the four levels are assembled side by side in
+    // one register with a handful of operations per plane (not per plane and position).
+    uint32_t levels = 0, sgn = 0;
 #pragma unroll
-    for (int b = 0; b < 8; ++b) pw[b] = (b <= nbits) ? __ldcg(src + b) : 0u;
-    uint32_t sgn = 0;
-#pragma unroll
-    for (int b = 0; b < 8; ++b) sgn = (b == nbits) ? pw[b] : sgn;
+    for (int b = 0; b < 8; ++b) {
+      if (b <= nbits) {
+        const uint32_t nib = (__ldcg(src + b) >> bit0) & 0xFu;
+        if (b < nbits) levels |= ((nib * 0x00204081u) & 0x01010101u) << b;
+        else sgn = nib;
+      }
+    }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       if (e < n_valid) {
-        uint32_t lv = 0;
-#pragma unroll
-        for (int b = 0; b < 7; ++b) lv |= (b < nbits) ? (((pw[b] >> (bit0 + e)) & 1u) << b) : 0u;
-        float q = unit * (float)lv;
-        q = ((sgn >> (bit0 + e)) & 1u) ? -q : q;
+        float q = unit * (float)((levels >> (8 * e)) & 0xFFu);
+        q = ((sgn >> e) & 1u) ? -q : q;
         acc[e] += q;
         if (acc2 != nullptr) acc2[e] += w2 * q;
       }
@@ -214,7 +217,7 @@ extern "C" int choco_dense_prep(const void* params_dev, int n_chunks, int n_rank
 }
 
 // ---- QSGD quantize + bit-slice + push ------------------------------------------------------
-__global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_kernel(const ChocoParams* __restrict__ params) {
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_generic_kernel(const ChocoParams* __restrict__ params) {
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -252,7 +255,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_kernel(const Ch
       const float d = dv[u];
       uint32_t lv = 0;
       if (ok && norm > 0.f) {
-        const float lvl = (s_f * fabsf(d)) / norm;
+        const float lvl = fabsf(d) * (s_f / norm);
         const float fl = floorf(lvl);
         const float u01 = counter_uniform(ubase, (uint32_t)pos);
         lv = (uint32_t)fl + ((u01 < (lvl - fl)) ? 1u : 0u);
@@ -284,9 +287,88 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_kernel(const Ch
   }
 }
 
+// Fast path, NBITS known at compile time (1..8): level = floor(|d| * (s / norm)) + [u < frac] with no
+// branch (padding and zero-norm tensors come out as level 0 by construction), fully unrolled
+// ballots, one multiply instead of a division per element.
+template <int NBITS>
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_kernel(const ChocoParams* __restrict__ params) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  const int chunk = blockIdx.x;
+  const int seg = tb.chunk_seg[chunk];
+  const int start = tb.chunk_start[chunk];
+  const int valid = tb.chunk_valid[chunk];
+  const int span = (valid + 31) & ~31;
+  const uint32_t t = p.step[0];
+  const int PW = p.payload_words;
+  const int par_cur = t & 1;
+  constexpr int PL = NBITS + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float norm = __uint_as_float(__ldcg(p.outbox + par_cur * PW + seg));
+  const float scale = norm > 0.f ? (float)p.qsgd_s / norm : 0.f;
+  const uint32_t ubase = uniform_base(p.seed, t);
+  const float* dptr = p.scratch_d + start;
+  const int out0 = par_cur * PW + p.body_off + (start >> 5) * PL + lane;
+  const int n_peers = p.n_peers;
+
+  for (int base0 = warp * 32; base0 < span; base0 += CHOCO_THREADS * 4) {
+    float dv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = base0 + u * CHOCO_THREADS + lane;
+      dv[u] = i < valid ? dptr[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int base = base0 + u * CHOCO_THREADS;
+      if (base >= span) break;  // uniform over the warp
+      const float d = dv[u];
+      const float a = fabsf(d) * scale;
+      const float fl = floorf(a);
+      const float u01 = counter_uniform(ubase, (uint32_t)(start + base + lane));
+      const uint32_t lv = (uint32_t)fl + ((u01 < (a - fl)) ? 1u : 0u);
+      uint32_t mine = __ballot_sync(0xffffffffu, d < 0.f);   // plane NBITS: signs
+#pragma unroll
+      for (int b = 0; b < NBITS; ++b) {
+        const uint32_t w = __ballot_sync(0xffffffffu, (lv >> b) & 1u);
+        mine = (lane == b) ? w : mine;
+      }
+      if (lane < PL) {
+        const int off = out0 + (base >> 5) * PL;
+        p.outbox[off] = mine;
+        for (int k = 0; k < n_peers; ++k) p.peer_inbox[k][off] = mine;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(p.done_count, 1u) == (uint32_t)tb.n_chunks - 1) {
+      __threadfence_system();
+      p.done_count[0] = 0;
+      for (int k = 0; k < n_peers; ++k) st_release_sys(p.peer_flag[k], t + 1);
+      __threadfence();
+      p.step[0] = t + 1;
+    }
+  }
+}
+
+extern "C" int choco_qsgd_pack_nbits(const void* params_dev, int n_chunks, int n_ranks, int nbits, cudaStream_t stream) {
+  dim3 grid(n_chunks, n_ranks);
+  const ChocoParams* pp = reinterpret_cast<const ChocoParams*>(params_dev);
+  switch (nbits) {
+#define QSGD_CASE(B) case B: choco_qsgd_pack_kernel<B><<<grid, CHOCO_THREADS, 0, stream>>>(pp); break;
+    QSGD_CASE(1) QSGD_CASE(2) QSGD_CASE(3) QSGD_CASE(4) QSGD_CASE(5) QSGD_CASE(6) QSGD_CASE(7) QSGD_CASE(8)
+#undef QSGD_CASE
+    default: choco_qsgd_pack_generic_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(pp);
+  }
+  return (int)cudaGetLastError();
+}
+
+// nbits unknown to the caller: the generic kernel (reads it from the parameter block)
 extern "C" int choco_qsgd_pack(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  choco_qsgd_pack_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  choco_qsgd_pack_generic_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
   return (int)cudaGetLastError();
 }
 

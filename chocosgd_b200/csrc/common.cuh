@@ -100,7 +100,9 @@ __host__ __device__ __forceinline__ uint32_t uniform_base(uint32_t seed, uint32_
   return mix32(step * 0x9E3779B9u + 0x7F4A7C15u) ^ seed;
 }
 __host__ __device__ __forceinline__ float counter_uniform(uint32_t base, uint32_t pos) {
-  uint32_t h = mix32(mix32(pos ^ base) + 0x85EBCA6Bu);
+  // one round of the avalanche hash: consecutive positions under a per-step base decorrelate
+  // well enough for stochastic rounding, and the quantizer is bound by its instruction count
+  uint32_t h = mix32(pos ^ base);
   return (float)(h >> 8) * (1.0f / 16777216.0f);
 }
 __host__ __device__ __forceinline__ uint32_t feistel_key(uint32_t seed, uint32_t step, uint32_t seg, uint32_t r) {

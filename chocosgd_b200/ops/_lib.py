@@ -159,6 +159,7 @@ def _declare(lib):
     for name, args in {
         "choco_dense_prep": [vp, i, i, i, i, vp],
         "choco_qsgd_pack": [vp, i, i, vp],
+        "choco_qsgd_pack_nbits": [vp, i, i, i, vp],
         "choco_qsgd_decode": [vp, i, i, vp],
         "choco_topk_hist": [vp, i, i, i, vp],
         "choco_topk_count": [vp, i, i, vp],

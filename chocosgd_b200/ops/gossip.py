@@ -305,7 +305,7 @@ class ChocoEngine:
             self._chk(L.choco_sign_step(pp, nc, nr, MODE_DECODE | MODE_PUSH, self.peers_hint, sp), "choco_sign_step")
         elif self.codec == 0:
             self._chk(L.choco_dense_prep(pp, nc, nr, MODE_DECODE, 0, sp), "choco_dense_prep")
-            self._chk(L.choco_qsgd_pack(pp, nc, nr, sp), "choco_qsgd_pack")
+            self._chk(L.choco_qsgd_pack_nbits(pp, nc, nr, int(self.nbits), sp), "choco_qsgd_pack")
         else:
             self._launch_sparse_decode(sp)
             self._chk(L.choco_dense_prep(pp, nc, nr, 0, self.codec, sp), "choco_dense_prep")
