@@ -68,6 +68,35 @@ __device__ __forceinline__ void qsgd_accumulate4(const uint32_t* __restrict__ sr
   }
 }
 
+// Warp-cooperative form (nbits <= 7): a warp covers 128 consecutive positions = 4 groups; the
+// 4 (nbits + 1) plane words are loaded ONCE (lane j loads word j) and handed out by shuffles, so
+// the payload is read with one load per lane instead of nbits + 1 loads per thread.
+// `words_valid` bounds the load at the end of a chunk / of the payload.  All 32 lanes must call.
+__device__ __forceinline__ void qsgd_accumulate4_warp(const uint32_t* __restrict__ wsrc, int nbits, int lane,
+                                                      int words_valid, int n_valid, float unit, float* acc,
+                                                      float* acc2, float w2) {
+  const int pl = nbits + 1;
+  const uint32_t mine = lane < words_valid ? __ldcg(wsrc + lane) : 0u;
+  const int gsel = (lane >> 3) * pl, bit0 = (lane & 7) * 4;
+  uint32_t levels = 0, sgn = 0;
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    const uint32_t w = __shfl_sync(0xffffffffu, mine, (gsel + b) & 31);
+    const uint32_t nib = (w >> bit0) & 0xFu;
+    if (b < nbits) levels |= ((nib * 0x00204081u) & 0x01010101u) << b;
+    else if (b == nbits) sgn = nib;
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    if (e < n_valid) {
+      float q = unit * (float)((levels >> (8 * e)) & 0xFFu);
+      q = ((sgn >> e) & 1u) ? -q : q;
+      acc[e] += q;
+      if (acc2 != nullptr) acc2[e] += w2 * q;
+    }
+  }
+}
+
 // codec: 0 = qsgd (fused decode + L2 norm), 1 = top-k (first radix histogram), 2 = random-k
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_dense_prep_kernel(const ChocoParams* __restrict__ params,
                                                                        int mode, int codec) {
@@ -127,22 +156,44 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_dense_prep_kernel(const C
   const float wd = tb.seg_wd[seg];
 
   float sq = 0.f;
-  for (int base = threadIdx.x * 4; base < span; base += CHOCO_THREADS * 4) {
-    const int pos = start + base;
+  const int lane = threadIdx.x & 31;
+  const bool warp_decode = do_decode && nbits <= 7;   // plane words shared through shuffles
+  // all lanes of a warp iterate together (the cooperative decode shuffles across the warp)
+  for (int wb = (threadIdx.x & ~31) * 4; wb < span; wb += CHOCO_THREADS * 4) {
+    const int base = wb + lane * 4;
+    const bool act = base < span;
+    const int pos = start + (act ? base : wb);
     const int group = pos >> 5, bit0 = pos & 31;
-    const float4 xh = *reinterpret_cast<const float4*>(p.x_hat + pos);
-    const float4 sv = *reinterpret_cast<const float4*>(p.s + pos);
+    float4 xh = make_float4(0.f, 0.f, 0.f, 0.f), sv = xh;
+    if (act) {
+      xh = *reinterpret_cast<const float4*>(p.x_hat + pos);
+      sv = *reinterpret_cast<const float4*>(p.s + pos);
+    }
     float xh_a[4] = {xh.x, xh.y, xh.z, xh.w}, s_a[4] = {sv.x, sv.y, sv.z, sv.w};
     if (do_decode) {
-      const int nv = valid - base < 4 ? valid - base : 4;
+      const int nv = !act ? 0 : (valid - base < 4 ? valid - base : 4);
       // own payload: x_hat += q, s += w_ii q ; neighbours: s += w_ij q_j (weight folded into unit)
-      qsgd_accumulate4(p.outbox + par_prev * PW + body + group * pl, nbits, bit0, nv, unit_own, xh_a, s_a, p.w_self);
-      for (int k = 0; k < n_peers; ++k)
-        qsgd_accumulate4(p.my_inbox[k] + par_prev * PW + body + group * pl, nbits, bit0, nv, unit_peer[k], s_a, nullptr,
-                         0.f);
-      *reinterpret_cast<float4*>(p.x_hat + pos) = make_float4(xh_a[0], xh_a[1], xh_a[2], xh_a[3]);
-      *reinterpret_cast<float4*>(p.s + pos) = make_float4(s_a[0], s_a[1], s_a[2], s_a[3]);
+      if (warp_decode) {
+        const int wgroup = (start + wb) >> 5;
+        const int groups_here = (span - wb) >= 128 ? 4 : ((span - wb + 31) >> 5);
+        const int words_valid = groups_here * pl;
+        qsgd_accumulate4_warp(p.outbox + par_prev * PW + body + wgroup * pl, nbits, lane, words_valid, nv, unit_own,
+                              xh_a, s_a, p.w_self);
+        for (int k = 0; k < n_peers; ++k)
+          qsgd_accumulate4_warp(p.my_inbox[k] + par_prev * PW + body + wgroup * pl, nbits, lane, words_valid, nv,
+                                unit_peer[k], s_a, nullptr, 0.f);
+      } else if (act) {
+        qsgd_accumulate4(p.outbox + par_prev * PW + body + group * pl, nbits, bit0, nv, unit_own, xh_a, s_a, p.w_self);
+        for (int k = 0; k < n_peers; ++k)
+          qsgd_accumulate4(p.my_inbox[k] + par_prev * PW + body + group * pl, nbits, bit0, nv, unit_peer[k], s_a, nullptr,
+                           0.f);
+      }
+      if (act) {
+        *reinterpret_cast<float4*>(p.x_hat + pos) = make_float4(xh_a[0], xh_a[1], xh_a[2], xh_a[3]);
+        *reinterpret_cast<float4*>(p.s + pos) = make_float4(s_a[0], s_a[1], s_a[2], s_a[3]);
+      }
     }
+    if (!act) continue;
     const float4 xv = *reinterpret_cast<const float4*>(p.x + pos);
     const float4 gv = load_grad4(p, seg, pos, base, valid);
     float x_a[4] = {xv.x, xv.y, xv.z, xv.w}, g_a[4] = {gv.x, gv.y, gv.z, gv.w};
