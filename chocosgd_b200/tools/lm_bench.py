@@ -19,7 +19,7 @@ def main(argv=None):
     p.add_argument("--steps", type=int, default=50)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--no_graph", action="store_true")
-    p.add_argument("--native", default="off", help="comma list of native layer kinds (lstm, linear) or off")
+    p.add_argument("--native", default="off", help="comma list of native layer kinds (ce, lstm, linear) or off")
     a = p.parse_args(argv)
     from ..config import get_args
     from ..models import define_model
