@@ -205,10 +205,13 @@ def run_ours(args, rank, world, local):
     optimizer.engine.check()
     losses = loss_host[:args.steps]
     assert torch.isfinite(losses).all(), "training diverged"
-    launches = optimizer.engine.launches_per_step * args.steps
+    # kernels of the native library per step: counted by the Python wrappers while the step was
+    # captured (convolutions, batch-norm, weight gradients, loss, gossip); library kernels excluded
+    per_step = step.kernel_launches_per_step or optimizer.engine.launches_per_step
+    launches = per_step * args.steps
     return dev_ms, e2e_ms, clocks, launches, float(losses[-1]), step.h2d_bytes, {
         "graph": step.use_graph, "native_layers": args.native_layers,
-        "kernels_per_step": optimizer.engine.launches_per_step}
+        "gossip_kernels_per_step": optimizer.engine.launches_per_step, "native_kernels_per_step": per_step}
 
 
 def run_reference(args, rank, world, local):

@@ -55,6 +55,14 @@ def check(code: int, what: str = ""):
 
 MAX_PEERS = 16
 
+#: kernels of this library launched so far by this process (the Python wrappers add their
+#: launches; a training step captured in a CUDA graph replays the count taken while capturing)
+LAUNCHES = [0]
+
+
+def count(n: int = 1):
+    LAUNCHES[0] += n
+
 
 class SegTableC(Structure):
     _fields_ = [

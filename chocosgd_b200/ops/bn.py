@@ -86,8 +86,10 @@ class _BnActFn(torch.autograd.Function):
             # per-CTA (sum, sum of squares) rows left by the producing convolution's epilogue
             a.partial = stats.data_ptr()
             rc = lib.bn_forward_partials(ctypes.byref(a), stats.shape[0], _lib.stream_ptr())
+            _lib.count(1)
         else:
             rc = lib.bn_forward(ctypes.byref(a), _lib.stream_ptr())
+            _lib.count(2)
         if rc != 0:
             raise RuntimeError(f"bn_forward failed ({rc})")
         ctx.save_for_backward(x, y, gamma, mean, invstd)
@@ -114,6 +116,7 @@ class _BnActFn(torch.autograd.Function):
         a.partial, a.counter = partial.data_ptr(), counter.data_ptr()
         a.P, a.C, a.relu = P, C, int(ctx.relu)
         rc = lib.bn_backward(ctypes.byref(a), _lib.stream_ptr())
+        _lib.count(2)
         if rc != 0:
             raise RuntimeError(f"bn_backward failed ({rc})")
         return dx, dgamma, dbeta, dres, None, None, None, None, None, None

@@ -49,6 +49,7 @@ class _CrossEntropyFn(torch.autograd.Function):
         _lib.check(lib.cross_entropy_fused(_lib.ptr(z), _lib.ptr(target.contiguous()), _lib.ptr(dz), _lib.ptr(scratch),
                                            _lib.ptr(stats), _lib.ptr(loss), B, C, int(bool(may_ignore)),
                                            _lib.stream_ptr()), "cross_entropy_fused")
+        _lib.count(2 if may_ignore else 1)
         ctx.save_for_backward(dz)
         ctx.set_materialize_grads(False)  # no zero tensor for the statistics output
         ctx.mark_non_differentiable(stats)

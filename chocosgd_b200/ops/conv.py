@@ -70,6 +70,7 @@ def conv3x3(x, w_krsc_ptr_tensor, cout, relu=False):
                           _lib.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"conv3x3_tf32 failed ({rc})")
+    _lib.count(1)
     return y
 
 
@@ -84,6 +85,7 @@ def conv3x3_with_stats(x, weight, cout):
                                 _lib.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"conv3x3_tf32_stats failed ({rc})")
+    _lib.count(1)
     return y, stats
 
 
@@ -115,12 +117,14 @@ def conv3x3_wgrad(x, dy, weight):
         rc = lib.conv3x3_wgrad16(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, h, w, _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"conv3x3_wgrad16 failed ({rc})")
+        _lib.count(2)
         return dw
     scratch = torch.empty(lib.conv3x3_wgrad_parts(n, h, w) * 9 * c * c, dtype=torch.float32, device=x.device)
     rc = lib.conv3x3_wgrad_tf32(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, h, w, c,
                                 _lib.stream_ptr())
     if rc != 0:
         raise RuntimeError(f"conv3x3_wgrad_tf32 failed ({rc})")
+    _lib.count(2)
     return dw
 
 
@@ -159,6 +163,7 @@ class FlippedWeights:
         rc = _declare().conv_flip_weights_multi(_lib.ptr(self.table), self.n, self.max_elems, _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"conv_flip_weights_multi failed ({rc})")
+        _lib.count(1)
         self.valid = True
 
     def get(self, weight):
@@ -334,6 +339,7 @@ class _ConvFirstFn(torch.autograd.Function):
                                     n, h, w, cout, _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"conv_first_forward failed ({rc})")
+        _lib.count(1)
         if want_stats:
             ctx.mark_non_differentiable(stats)
             return y, stats
@@ -357,6 +363,7 @@ class _ConvFirstFn(torch.autograd.Function):
                                       _lib.stream_ptr())
             if rc != 0:
                 raise RuntimeError(f"conv_first_wgrad failed ({rc})")
+            _lib.count(2)
             return dw
 
         fork = _WGRAD_STREAM.enabled and weight.grad is None and not torch.is_grad_enabled()

@@ -294,6 +294,7 @@ class ChocoEngine:
 
     def _chk(self, code, what):
         self._n_launch += 1
+        _lib.count(1)
         _lib.check(code, what)
 
     def launch_step(self, stream=None):

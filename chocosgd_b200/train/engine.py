@@ -69,6 +69,7 @@ class TrainStep:
         self.flips = None
         self.bn_counters = None
         self._fused_ce = False
+        self._copy_stream = None
         if self.is_cuda:
             from ..ops import nn as native_nn
 
@@ -161,11 +162,16 @@ class TrainStep:
             p.grad = None
         self.graph = torch.cuda.CUDAGraph()
         self.opt.prepare_step()
+        from ..ops import _lib
+
+        n0 = _lib.LAUNCHES[0]
         with torch.cuda.graph(self.graph, stream=s):
             self._forward_backward()
             if self.clip is not None:
                 grad_clip_(eng, self.clip)
             self.opt.launch()
+        # kernels of the native library inside one replay (library kernels are not counted)
+        self.kernel_launches_per_step = _lib.LAUNCHES[0] - n0
         self._captured_grads = [p.grad for p in self.opt.arena.params]
         self._fill_table(table)
         torch.cuda.synchronize()
@@ -184,8 +190,30 @@ class TrainStep:
 
     # ---- public call -----------------------------------------------------------------------------
     def load_batch(self, inp: torch.Tensor, tgt: torch.Tensor):
-        self.static_input.copy_(inp, non_blocking=True)
-        self.static_target.copy_(tgt, non_blocking=True)
+        """Host batch -> static device buffers.  On CUDA the host-to-device copy runs on its own
+        stream into a staging buffer, so the copy of batch i overlaps the (asynchronously running)
+        step i-1; the step's stream then only does a device-to-device copy (which also converts to
+        channels_last)."""
+        if not self.is_cuda or inp.is_cuda:
+            self.static_input.copy_(inp, non_blocking=True)
+            self.static_target.copy_(tgt, non_blocking=True)
+            return
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+            self._stage_in = torch.empty(inp.shape, dtype=self.static_input.dtype, device=self.device)
+            self._stage_tgt = torch.empty(tgt.shape, dtype=self.static_target.dtype, device=self.device)
+            self._ready, self._consumed = torch.cuda.Event(), torch.cuda.Event()
+            self._consumed.record(torch.cuda.current_stream(self.device))
+        cs, main = self._copy_stream, torch.cuda.current_stream(self.device)
+        cs.wait_event(self._consumed)  # the staging buffers are free once the previous batch was taken over
+        with torch.cuda.stream(cs):
+            self._stage_in.copy_(inp, non_blocking=True)
+            self._stage_tgt.copy_(tgt, non_blocking=True)
+            self._ready.record(cs)
+        main.wait_event(self._ready)
+        self.static_input.copy_(self._stage_in)
+        self.static_target.copy_(self._stage_tgt)
+        self._consumed.record(main)
 
     def __call__(self, inp: Optional[torch.Tensor] = None, tgt: Optional[torch.Tensor] = None, **step_kw):
         """Run one training step; returns the loss as a 0-d device tensor (no host sync)."""
