@@ -1,8 +1,10 @@
-"""Native LSTM layer stack: gate GEMMs + fused cell kernels (``csrc/lstm_cell.cu``).
+"""Native LSTM layer stack: gate GEMMs + recurrent kernels (``csrc/lstm_persistent.cu``,
+``csrc/lstm_cell.cu``).
 
 Per layer the input projection of all time steps is ONE GEMM (the tcgen05 kernel when the
-dimensions are multiples of 4, the library GEMM otherwise, e.g. hidden size 650); each time step is
-one recurrent GEMM plus one fused pointwise kernel.  Backward runs the cell kernel in reverse and
+dimensions are multiples of 4, the library GEMM otherwise, e.g. hidden size 650); the recurrence over
+the time steps is ONE persistent kernel per direction for batch <= 32 and hidden sizes whose
+weight slices fit in shared memory, else one recurrent GEMM plus one fused pointwise kernel per step.  Backward runs the cell kernel in reverse and
 forms dW_ih, dW_hh and dX with three GEMMs over the whole sequence.  Same parameters, gate order and
 results as ``torch.nn.LSTM`` (``dl_code/pcode/models/rnn_lm.py:29,53-61``); dropout between layers as there."""
 from __future__ import annotations
@@ -23,8 +25,24 @@ def _declare():
         lib.lstm_cell_fwd.argtypes = [vp, vp, vp, vp, i, i, vp]
         lib.lstm_cell_bwd.argtypes = [vp, vp, vp, vp, vp, i, i, vp]
         lib.lstm_cell_fwd.restype = lib.lstm_cell_bwd.restype = i
+        lib.lstm_rec_supported.argtypes = [i, i, i]
+        lib.lstm_rec_forward.argtypes = [vp, vp, vp, vp, i, i, i, vp]
+        lib.lstm_rec_backward.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
+        lib.lstm_rec_bwd_scratch.argtypes = [i]
+        lib.lstm_rec_bwd_scratch.restype = ctypes.c_longlong
+        lib.lstm_rec_supported.restype = lib.lstm_rec_forward.restype = lib.lstm_rec_backward.restype = i
+        lib.lstm_rec_last_error.restype = i
         lib._lstm_declared = True
     return lib
+
+
+#: one persistent kernel per layer and direction (``csrc/lstm_persistent.cu``) when the shape fits
+PERSISTENT = [True]
+
+
+def last_error() -> int:
+    """Non-zero when a grid barrier of the persistent kernels ran out of its wait budget."""
+    return _declare().lstm_rec_last_error()
 
 
 def _mm_nt(a, b):
@@ -46,10 +64,17 @@ class _LSTMLayerFn(torch.autograd.Function):
         hs[0].copy_(h0)
         cs[0].copy_(c0)
         sp = _lib.stream_ptr()
-        for t in range(T):
-            gates[t].addmm_(hs[t], w_hh.t())
-            _lib.check(lib.lstm_cell_fwd(_lib.ptr(gates[t]), _lib.ptr(cs[t]), _lib.ptr(cs[t + 1]), _lib.ptr(hs[t + 1]),
-                                         B, H, sp), "lstm_cell_fwd")
+        w_hh_c = w_hh.contiguous()
+        if PERSISTENT[0] and lib.lstm_rec_supported(T, B, H):
+            # all T steps in one persistent kernel (grid barrier per step)
+            _lib.check(lib.lstm_rec_forward(_lib.ptr(gates), _lib.ptr(w_hh_c), _lib.ptr(hs), _lib.ptr(cs), T, B, H, sp),
+                       "lstm_rec_forward")
+            _lib.count(1)
+        else:
+            for t in range(T):
+                gates[t].addmm_(hs[t], w_hh.t())
+                _lib.check(lib.lstm_cell_fwd(_lib.ptr(gates[t]), _lib.ptr(cs[t]), _lib.ptr(cs[t + 1]),
+                                             _lib.ptr(hs[t + 1]), B, H, sp), "lstm_cell_fwd")
         ctx.save_for_backward(x, w_ih, w_hh, gates, hs, cs)
         return hs[1:], hs[T].clone(), cs[T].clone()
 
@@ -64,12 +89,20 @@ class _LSTMLayerFn(torch.autograd.Function):
         dc = d_cn.clone() if d_cn is not None else torch.zeros(B, H, dtype=x.dtype, device=x.device)
         d_out = d_out.contiguous() if d_out is not None else None
         sp = _lib.stream_ptr()
-        for t in range(T - 1, -1, -1):
-            if d_out is not None:
-                dh = dh + d_out[t]
-            _lib.check(lib.lstm_cell_bwd(_lib.ptr(dgates[t]), _lib.ptr(cs[t]), _lib.ptr(cs[t + 1]), _lib.ptr(dh),
-                                         _lib.ptr(dc), B, H, sp), "lstm_cell_bwd")
-            dh = dgates[t] @ w_hh
+        if PERSISTENT[0] and lib.lstm_rec_supported(T, B, H):
+            scratch = torch.zeros(lib.lstm_rec_bwd_scratch(H), dtype=torch.float32, device=x.device)
+            dh, dc = dh.contiguous(), dc.contiguous()
+            _lib.check(lib.lstm_rec_backward(_lib.ptr(dgates), _lib.ptr(w_hh.contiguous()), _lib.ptr(cs), _lib.ptr(d_out),
+                                             _lib.ptr(dh), _lib.ptr(dc), _lib.ptr(scratch), T, B, H, sp),
+                       "lstm_rec_backward")
+            _lib.count(1)
+        else:
+            for t in range(T - 1, -1, -1):
+                if d_out is not None:
+                    dh = dh + d_out[t]
+                _lib.check(lib.lstm_cell_bwd(_lib.ptr(dgates[t]), _lib.ptr(cs[t]), _lib.ptr(cs[t + 1]), _lib.ptr(dh),
+                                             _lib.ptr(dc), B, H, sp), "lstm_cell_bwd")
+                dh = dgates[t] @ w_hh
         dg2 = dgates.view(T * B, 4 * H)
         dx = (dg2 @ w_ih).view_as(x)
         dw_ih = dg2.t() @ x.reshape(T * B, -1)

@@ -34,3 +34,46 @@ def test_lstm_matches_torch(inp, hid, layers):
     tol = 5e-3 if inp % 4 == 0 else 1e-4  # the tcgen05 GEMM rounds its inputs to TF32
     for a, b in [(out, out_ref), (hn, hn_ref), (cn, cn_ref)] + list(zip(grads, grads_ref)):
         assert (a - b).abs().max() <= tol * (b.abs().max() + 1e-3), (a - b).abs().max()
+
+
+@pytest.mark.parametrize("T,B,inp,hid", [(35, 32, 650, 650), (12, 20, 40, 200), (5, 32, 16, 17)])
+def test_persistent_recurrence_matches_torch(T, B, inp, hid):
+    """One persistent kernel per direction (grid barrier per time step) against torch.nn.LSTM in
+    strict fp32, and against the per-step native path."""
+    from chocosgd_b200.ops import lstm as native_lstm
+    from chocosgd_b200.ops import nn as nnn
+
+    torch.manual_seed(1)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    m = nnn.LSTM(inp, hid, 1).cuda()
+    x = torch.randn(T, B, inp, device="cuda", requires_grad=True)
+    h0 = torch.randn(1, B, hid, device="cuda") * 0.1
+    c0 = torch.randn(1, B, hid, device="cuda") * 0.1
+    params = [x] + list(m.parameters())
+
+    def run():
+        out, (hn, cn) = m(x, (h0, c0))
+        g = torch.ones_like(out) * 0.01
+        loss = (out * g).sum() + hn.sum() * 0.3 + cn.sum() * 0.2
+        return [out, hn, cn] + list(torch.autograd.grad(loss, params))
+
+    try:
+        ref = run()
+        nnn.set_native(True, which=("lstm",))
+        native_lstm.PERSISTENT[0] = True
+        got = run()
+        got2 = run()  # second call: the barrier words were left consistent
+        native_lstm.PERSISTENT[0] = False
+        step = run()
+    finally:
+        native_lstm.PERSISTENT[0] = True
+        nnn.set_native(False)
+        torch.backends.cuda.matmul.allow_tf32 = True
+        torch.backends.cudnn.allow_tf32 = True
+    assert native_lstm.last_error() == 0
+    tol = 5e-3 if inp % 4 == 0 else 2e-4  # the tcgen05 input GEMM rounds to TF32
+    for a, a2, s, b in zip(got, got2, step, ref):
+        assert (a - b).abs().max() <= tol * (b.abs().max() + 1e-3), (a - b).abs().max()
+        assert (s - b).abs().max() <= tol * (b.abs().max() + 1e-3)
+        assert torch.equal(a, a2)
