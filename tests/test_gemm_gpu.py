@@ -40,6 +40,13 @@ def test_gemm_ragged_edges_and_bias():
     _check(100, 40, 1000, True, True)
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_wide_tiles(a_mn, b_mn):
+    """Shapes large enough for the 128 x 256 tiles (at least 120 of them), ragged N and K included."""
+    _check(2048, 2048, 256, a_mn, b_mn)
+    _check(1920, 2300, 200, a_mn, b_mn, bias=True)
+
+
 def test_gemm_split_k():
     _check(64, 144, 8192, True, True, split_k=8)
     _check(128, 128, 4096, False, False, split_k=4)
