@@ -95,7 +95,7 @@ def run(args):
                         s.add_(q, alpha=w)
                     state["t"] += 1
 
-                nbits, payload_bytes = getattr(codec, "nbits", 0), 4 * codec.payload_words()
+                nbits, payload_bytes, launches = getattr(codec, "nbits", 0), 4 * codec.payload_words(), None
             for _ in range(args.warmup):
                 step()
             torch.cuda.synchronize()
