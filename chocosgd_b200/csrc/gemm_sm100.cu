@@ -15,6 +15,7 @@
 // Every mbarrier wait is bounded: on expiry the CTA records an error code, skips to the
 // teardown (TMEM is always freed) and returns.
 #include "tc_common.cuh"
+#include <stdlib.h>
 
 #define GEMM_BM 128
 #define GEMM_BK 32          // tf32 elements per k-block = 128 bytes = one swizzle row
@@ -159,6 +160,184 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
+// ---- persistent variant ---------------------------------------------------------------------------
+// One CTA per SM walks over output tiles (tile t = blockIdx.x, + gridDim.x, ...; M-tiles vary
+// fastest so that the CTAs running at one time share B panels in L2).  The TMA producer keeps
+// running ahead across tile boundaries and the accumulator is double-buffered in TMEM (2 x BN of
+// the 512 columns), so the epilogue of tile t overlaps the multiplications of tile t + 1.
+// Used when there is no split-K and the tile count covers the machine a few times.
+__device__ __forceinline__ bool gemm_epi_bar_or(bool flag) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r) : "r"((uint32_t)flag) : "memory");
+  return r != 0;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int A_BYTES = GEMM_BM * GEMM_BK * 4;
+  constexpr int B_BYTES = BN * GEMM_BK * 4;
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + GEMM_STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sB + GEMM_STAGES * B_BYTES);
+  uint64_t* empty = full + GEMM_STAGES;
+  uint64_t* acc_full = empty + GEMM_STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (g.M + GEMM_BM - 1) / GEMM_BM, tiles_n = (g.N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int n_kb = (g.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GEMM_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full + b, 1);
+      mbar_init(acc_empty + b, 4);   // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ---------------- TMA producer: lane 0 waits and arms the barrier, lanes 0..P-1 issue one box each ------------
+    constexpr int PA = A_MN ? GEMM_BM / 32 : 1, PB = B_MN ? BN / 32 : 1;
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      const int m0 = (tile % tiles_m) * GEMM_BM, n0 = (tile / tiles_m) * BN;
+      int ok = 1;
+      for (int i = 0; i < n_kb; ++i, ++it) {
+        const uint32_t s = it % GEMM_STAGES;
+        if (lane == 0) {
+          if (it >= GEMM_STAGES && !mbar_wait(empty + s, ((it / GEMM_STAGES) - 1) & 1)) ok = 0;
+          if (*abort_flag) ok = 0;
+          if (ok) mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+          else *abort_flag = 1;
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        const int k0 = i * GEMM_BK;
+        if (lane < PA) {
+          if (!A_MN) tma_load_2d(sA + s * A_BYTES, &map_a, full + s, k0, m0);
+          else tma_load_2d(sA + s * A_BYTES + lane * 4096, &map_a, full + s, m0 + 32 * lane, k0);
+        } else if (lane < PA + PB) {
+          const int j = lane - PA;
+          if (!B_MN) tma_load_2d(sB + s * B_BYTES, &map_b, full + s, k0, n0);
+          else tma_load_2d(sB + s * B_BYTES + j * 4096, &map_b, full + s, n0 + 32 * j, k0);
+        }
+        __syncwarp();
+      }
+      if (!ok) break;
+    }
+  } else if (warp == 5 && lane == 0) {
+    // ---------------- MMA issuer ----------------
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GEMM_BM >> 4) << 24);
+    uint32_t it = 0, lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++lt) {
+      const uint32_t buf = lt & 1;
+      if (lt >= 2 && !mbar_wait(acc_empty + buf, ((lt >> 1) - 1) & 1)) { *abort_flag = 1; ok = false; break; }
+      tc_fence_after();
+      const uint32_t d = tmem_base + buf * BN;
+      for (int i = 0; i < n_kb; ++i, ++it) {
+        const uint32_t s = it % GEMM_STAGES;
+        if (!mbar_wait(full + s, (it / GEMM_STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+        for (int k = 0; k < GEMM_BK / 8; ++k) {
+          const uint64_t da = A_MN ? make_desc(a_addr + k * 1024, 4096, 512, 1) : make_desc(a_addr + k * 32, 16, 1024);
+          const uint64_t db = B_MN ? make_desc(b_addr + k * 1024, 4096, 512, 1) : make_desc(b_addr + k * 32, 16, 1024);
+          umma_tf32(d, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(empty + s);
+      }
+      if (ok) tc_commit(acc_full + buf);
+    }
+  } else if (warp < 4) {
+    // ---------------- epilogue: TMEM -> registers -> global, overlapped with the next tile ----------------
+    uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++lt) {
+      const uint32_t buf = lt & 1;
+      const bool bad = !mbar_wait(acc_full + buf, (lt >> 1) & 1) || *abort_flag != 0;
+      if (gemm_epi_bar_or(bad)) {   // the same decision in all 128 epilogue threads
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int m0 = (tile % tiles_m) * GEMM_BM, n0 = (tile / tiles_m) * BN;
+      const int row = m0 + warp * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BN + (uint32_t)c, r);
+        if (row < g.M && n0 + c < g.N) {
+          float* out = g.d + (size_t)row * g.ldd + n0 + c;
+          if (n0 + c + 16 <= g.N && (g.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(g.d) & 15) == 0 &&
+              (reinterpret_cast<uintptr_t>(g.bias) & 15) == 0) {   // n0 + c is a multiple of 16
+            // full chunk: four 16-byte stores
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                     __uint_as_float(r[j + 3]));
+              if (g.bias != nullptr) {
+                const float4 bv = *reinterpret_cast<const float4*>(g.bias + n0 + c + j);
+                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+              }
+              if (g.relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+              *reinterpret_cast<float4*>(out + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int col = n0 + c + j;
+              if (col < g.N) {
+                float v = __uint_as_float(r[j]);
+                if (g.bias != nullptr) v += g.bias[col];
+                out[j] = g.relu ? fmaxf(v, 0.f) : v;
+              }
+            }
+          }
+        }
+      }
+      // the accumulator buffer may be overwritten by the tile after next
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + buf);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(g.error, GEMM_ERR_TIMEOUT);
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ---------------------------------- host side ----------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -229,6 +408,29 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
   return (int)cudaGetLastError();
 }
 
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm_persist(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int grid, cudaStream_t st) {
+  constexpr int smem = GEMM_STAGES * (GEMM_BM * GEMM_BK * 4 + BN * GEMM_BK * 4) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_persist_kernel<BN, A_MN, B_MN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  gemm_tf32_persist_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, g);
+  return (int)cudaGetLastError();
+}
+
+template <int BN>
+static int dispatch_persist(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
+                            int grid, cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_gemm_persist<BN, false, false>(ma, mb, g, grid, st);
+  if (!a_mn && b_mn) return launch_gemm_persist<BN, false, true>(ma, mb, g, grid, st);
+  if (a_mn && !b_mn) return launch_gemm_persist<BN, true, false>(ma, mb, g, grid, st);
+  return launch_gemm_persist<BN, true, true>(ma, mb, g, grid, st);
+}
+
 template <int BN>
 static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
                           int splits, cudaStream_t st) {
@@ -264,6 +466,23 @@ extern "C" int gemm_tf32(const void* a, const void* b, void* d, const void* bias
   if (splits > total_kb) splits = total_kb;
   g.k_blocks_per_split = (total_kb + splits - 1) / splits;
   splits = (total_kb + g.k_blocks_per_split - 1) / g.k_blocks_per_split;
+  if (splits == 1 && (BN == 128 || BN == 256)) {
+    // persistent form when the tiles cover the machine at least twice (epilogue / multiply overlap)
+    static int sms = 0, enabled = -1;
+    if (enabled < 0) {
+      const char* e = getenv("CHOCO_GEMM_PERSISTENT");
+      enabled = e != nullptr && atoi(e) != 0;   // opt-in until it has been measured against the one-tile kernel
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+    }
+    const long long tiles = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+    if (enabled && tiles >= 2LL * sms) {
+      const int grid = sms;
+      return BN == 256 ? dispatch_persist<256>(a_mn, b_mn, ma, mb, g, grid, stream)
+                       : dispatch_persist<128>(a_mn, b_mn, ma, mb, g, grid, stream);
+    }
+  }
   if (BN == 32) return dispatch_major<32>(a_mn, b_mn, ma, mb, g, splits, stream);
   if (BN == 64) return dispatch_major<64>(a_mn, b_mn, ma, mb, g, splits, stream);
   if (BN == 256) return dispatch_major<256>(a_mn, b_mn, ma, mb, g, splits, stream);
