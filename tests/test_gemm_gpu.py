@@ -69,3 +69,37 @@ def test_linear_native_matches_torch():
         nnn.set_native(False)
     for a, b in ((y, y_ref), (gx, gx_ref), (gw, gw_ref), (gb, gb_ref)):
         assert (a - b).abs().max() <= 5e-3 * b.abs().max() + 1e-3
+
+
+def test_gemm_persistent_variant():
+    """The persistent kernel (default for large tile counts; CHOCO_GEMM_PERSISTENT is read once per process): all four operand
+    layouts, ragged M / N / K, bias, 128- and 256-wide tiles, against float64."""
+    import os
+    import subprocess
+    import sys
+
+    code = r"""
+import torch
+from chocosgd_b200.ops.gemm import gemm, last_error
+g = torch.Generator(device="cuda").manual_seed(5)
+for (M, N, K, bias) in ((4736, 2080, 160, False), (4700, 2300, 100, True), (9600, 200, 72, True)):
+    for a_mn in (False, True):
+        for b_mn in (False, True):
+            a = torch.randn((K, M) if a_mn else (M, K), device="cuda", generator=g)
+            b = torch.randn((K, N) if b_mn else (N, K), device="cuda", generator=g)
+            bv = torch.randn(N, device="cuda", generator=g) if bias else None
+            out = gemm(a, b, bv, a_mn=a_mn, b_mn=b_mn)
+            out2 = gemm(a, b, bv, a_mn=a_mn, b_mn=b_mn)
+            A = (a.t() if a_mn else a).double(); B = (b.t() if b_mn else b).double()
+            ref = A @ B.t() + (bv.double() if bias else 0)
+            err = (out.double() - ref).abs().max().item()
+            assert err <= 4e-3 * ref.abs().max().item() + 1e-3, (M, N, K, a_mn, b_mn, err)
+            assert torch.equal(out, out2)
+torch.cuda.synchronize()
+assert last_error() == 0
+print("ok")
+"""
+    env = dict(os.environ, CHOCO_GEMM_PERSISTENT="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, (r.stdout[-500:], r.stderr[-2000:])
