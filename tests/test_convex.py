@@ -93,3 +93,14 @@ def test_experiment_driver(tmp_path):
     res = run_experiment(str(tmp_path), (A, y), ps, nproc=2)
     assert len(res) == 2 and (tmp_path / "results.pickle").exists() and (tmp_path / "params.pickle").exists()
     assert len(epsilon_final_params()) == 2 * 5 * 9
+
+
+def test_convex_bench_tool_runs(capsys):
+    import json
+
+    from chocosgd_b200.tools import convex_bench
+
+    convex_bench.main(["--samples", "300", "--features", "100", "--nodes", "3", "--epochs", "1"])
+    lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert [l["method"] for l in lines] == ["choco", "plain"]
+    assert all(0.0 < l["final_loss"] < 1.0 for l in lines)
