@@ -14,6 +14,7 @@
 // The input gradient of such a convolution is the same operation applied to dy with the
 // filter flipped and its channel roles exchanged (conv_flip_weights), so one kernel serves
 // forward and dgrad.  Bounded mbarrier waits as in the GEMM kernel; no cluster multicast.
+// Two kernels follow: the one-tile-per-CTA form and the persistent form (default) further down.
 #include "tc_common.cuh"
 #include <stdlib.h>
 

@@ -8,7 +8,7 @@
 // The only shared-memory layout the tensor core accepts for MN-major 32-bit operands is the 128-byte
 // swizzle with 32-byte units, which TMA produces (SWIZZLE_128B_ATOM_32B) for rows of exactly 32 floats:
 // the kernel therefore covers C = 32 and C = 64 (two 32-channel blocks); 16-channel layers use the
-// library weight gradient.
+// warp-level kernel of conv_wgrad16.cu.
 //
 // One CTA reduces a contiguous range of 128-pixel tiles: the dY tile is loaded once per tile and
 // multiplied with the 9 shifted X tiles into 9 accumulators of 32 columns in TMEM (M = 128 with the

@@ -1,8 +1,9 @@
-"""Native convolution path: 3x3 / stride 1 / pad 1 NHWC fp32 convolutions run the tcgen05
-implicit-GEMM kernel (``csrc/conv_sm100.cu``) for the forward pass and for the input gradient
-(same kernel on dy with the flipped filter), and ``csrc/conv_wgrad_sm100.cu`` for the weight
-gradient when C_in == C_out in {16, 32, 64}.  All other convolution shapes (strided, 1x1, first
-layer with 3 input channels) use the library convolution."""
+"""Native convolution path: 3x3 / stride 1 / pad 1 NHWC fp32 convolutions run the persistent
+tcgen05 implicit-GEMM kernel (``csrc/conv_sm100.cu``) for the forward pass (optionally with the
+batch-norm statistics of its output) and for the input gradient (same kernel on dy with the flipped
+filter).  Weight gradients: ``csrc/conv_wgrad16.cu`` for 16 channels, ``csrc/conv_wgrad_sm100.cu``
+(tcgen05, opt-in) or the library for 32 / 64 channels, forked onto a second stream.  The 3-channel
+first layer runs ``csrc/conv_first.cu``.  Strided and 1x1 convolutions use the library."""
 from __future__ import annotations
 
 import ctypes
