@@ -245,10 +245,27 @@ def run_reference(args, rank, world, local):
     return ms, ms, clocks, 0, out["loss"], BATCH * 3 * 32 * 32 * 4 + BATCH * 8, {}
 
 
+_JSON_OUT = None
+
+
+def claim_stdout():
+    """Keep the real stdout for the ONE JSON line: libraries that write to file descriptor 1
+    themselves (NCCL prints its version there) are sent to stderr from here on."""
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit(obj):
+    print(json.dumps(obj), file=_JSON_OUT if _JSON_OUT is not None else sys.stdout, flush=True)
+
+
 def main():
     args = parse()
+    claim_stdout()
     if not torch.cuda.is_available():
-        print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
+        emit({"impl": args.impl, "unavailable": "no CUDA device"})
         return
     rank, world, local = init_dist(args.gpus)
     if args.impl == "reference":
@@ -259,7 +276,7 @@ def main():
         if res is None or res[0] == "error":
             if rank == 0:
                 why = "reference not installed under baseline/_ref" if res is None else res[1]
-                print(json.dumps({"impl": "reference", "unavailable": why}))
+                emit({"impl": "reference", "unavailable": why})
             return
     else:
         res = run_ours(args, rank, world, local)
@@ -284,7 +301,7 @@ def main():
             "gpu_launches": launches,
             "last_loss": last_loss,
         }
-        print(json.dumps(line))
+        emit(line)
     if dist.is_initialized():
         try:
             torch.cuda.synchronize()
