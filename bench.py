@@ -47,10 +47,14 @@ def parse():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs.
+
+    ``nvidia-smi`` needs a second or more to come up on a multi-GPU machine, so the sampler is
+    started before the warm-up steps; ``mark()`` (called at the start of the timed region) waits
+    for its first line and remembers how many lines precede the region."""
 
     def __init__(self, enabled, gpu_index):
-        self.proc, self.path = None, None
+        self.proc, self.path, self.skip = None, None, 0
         if not enabled:
             return
         try:
@@ -62,6 +66,24 @@ class ClockSampler:
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+
+    def _lines(self):
+        try:
+            with open(self.path) as fh:
+                return sum(1 for _ in fh)
+        except Exception:
+            return 0
+
+    def mark(self, wait_s=15.0):
+        if self.proc is None:
+            return
+        t0 = time.time()
+        while self._lines() == 0 and time.time() - t0 < wait_s:
+            time.sleep(0.05)
+        self.skip = self._lines()
+
+    def samples_in_region(self):
+        return max(0, self._lines() - self.skip) if self.proc is not None else 0
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
@@ -75,7 +97,9 @@ class ClockSampler:
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         try:
-            for line in open(self.path):
+            for n_line, line in enumerate(open(self.path)):
+                if n_line < self.skip:
+                    continue
                 f = [x.strip() for x in line.split(",")]
                 if len(f) < 9:
                     continue
@@ -152,6 +176,27 @@ def timed(fn, steps, world, quiesce=None):
     return max_over_ranks(ms, world)
 
 
+def keep_load_until_sampled(sampler, fn, world, quiesce=None, want=3, limit_s=6.0):
+    """A short timed region can end before nvidia-smi (one line per 100 ms) has printed three
+    lines: keep running the same step, untimed, until it has.  Rank 0 owns the sampler and
+    decides; all ranks run the same number of extra steps (the steps exchange payloads)."""
+    t0 = time.time()
+    while True:
+        more = 1 if (sampler.proc is not None and sampler.samples_in_region() < want
+                     and time.time() - t0 < limit_s) else 0
+        if world > 1:
+            flag = torch.tensor([more], dtype=torch.int32, device="cuda")
+            if quiesce is not None:
+                quiesce()
+            dist.broadcast(flag, 0)
+            more = int(flag.item())
+        if not more:
+            return
+        for i in range(20):
+            fn(i)
+        torch.cuda.synchronize()
+
+
 def run_ours(args, rank, world, local):
     from chocosgd_b200.config import get_args
     from chocosgd_b200.models import define_model
@@ -185,13 +230,14 @@ def run_ours(args, rank, world, local):
     loss_host = torch.zeros(args.steps + args.warmup + 8, dtype=torch.float32).pin_memory()
 
     # warm-up: graph capture + W untimed steps through the public call
+    sampler = ClockSampler(rank == 0, local)
     for i in range(max(args.warmup, 3)):
         step(xs[i % N_HOST_BATCHES], ys[i % N_HOST_BATCHES])
     torch.cuda.synchronize()
     optimizer.engine.check()
+    sampler.mark()
 
     # (1) device-timed steps: the batch is already in the static device buffers
-    sampler = ClockSampler(rank == 0, local)
     dev_ms = timed(lambda i: step(), args.steps, world)
 
     # (2) end to end through the public API: pinned host batch -> device, step, loss -> host
@@ -200,6 +246,7 @@ def run_ours(args, rank, world, local):
         loss_host[i:i + 1].copy_(loss.reshape(1), non_blocking=True)
 
     e2e_ms = timed(e2e, args.steps, world)
+    keep_load_until_sampled(sampler, lambda i: step(), world)
     clocks = sampler.stop()
     optimizer.finalize()
     optimizer.engine.check()
@@ -235,11 +282,13 @@ def run_reference(args, rank, world, local):
         it.n += 1
 
     it.n = 0
+    sampler = ClockSampler(rank == 0, local)
     for i in range(max(args.warmup, 3)):
         it(i)
     torch.cuda.synchronize()
-    sampler = ClockSampler(rank == 0, local)
+    sampler.mark()
     ms = timed(it, args.steps, world, quiesce=lambda: ref.finish(state))
+    keep_load_until_sampled(sampler, it, world, quiesce=lambda: ref.finish(state))
     clocks = sampler.stop()
     ref.finish(state)
     return ms, ms, clocks, 0, out["loss"], BATCH * 3 * 32 * 32 * 4 + BATCH * 8, {}
@@ -293,8 +342,8 @@ def main():
             "config": {"model": "resnet20", "global_batch": BATCH * world, "seq_len": None,
                        "parallelism": f"gossip-dp{world} ring", "optimizer": "CHOCO-SGD", "comm_op": args.comm_op,
                        "compress_ratio": 0.99, "consensus_stepsize": GAMMA[args.comm_op], "nesterov": 0.9, "weight_decay": 1e-4,
-                       "l2": "per-step working set (activations + gradients, ~0.3 GB) exceeds the 126 MB L2",
-                       **extra},
+                       "l2": "per-step working set (activations + gradients, ~0.3 GB) exceeds the 126 MB L2"},
+            "impl_detail": extra,
             "clocks": clocks,
             "e2e": {"value": imgs / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},

@@ -1,11 +1,11 @@
 """Run one hand-written kernel a few times on a small, fixed case: the program that is put under
 ``ncu`` for the committed profile summaries, and a quick CUDA-event timing of the same case.
 
-    python -m chocosgd_b200.tools.kernel_probe --case sign --elements 67108864
-    python -m chocosgd_b200.tools.kernel_probe --case gemm --m 4096 --n 4096 --k 4096
-    python -m chocosgd_b200.tools.kernel_probe --case conv --batch 128 --hw 32 --channels 16
-    python -m chocosgd_b200.tools.kernel_probe --case wgrad --batch 128 --hw 32 --channels 16
-    python -m chocosgd_b200.tools.kernel_probe --case bn --batch 128 --hw 32 --channels 16
+    python -m chocosgd_b200.tools.kernel_bench --case sign --elements 67108864
+    python -m chocosgd_b200.tools.kernel_bench --case gemm --m 4096 --n 4096 --k 4096
+    python -m chocosgd_b200.tools.kernel_bench --case conv --batch 128 --hw 32 --channels 16
+    python -m chocosgd_b200.tools.kernel_bench --case wgrad --batch 128 --hw 32 --channels 16
+    python -m chocosgd_b200.tools.kernel_bench --case bn --batch 128 --hw 32 --channels 16
 """
 from __future__ import annotations
 
