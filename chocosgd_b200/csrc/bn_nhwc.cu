@@ -14,6 +14,7 @@
 //
 // Layout: x is [P, C] with C contiguous, C a multiple of 4, C/4 a power of two <= 256.
 #include <cuda_runtime.h>
+#include "launch.cuh"
 #include <stdint.h>
 #include <stdlib.h>
 
@@ -45,6 +46,8 @@ struct BnArgs {
 // per-channel sums of (a, b) over this CTA's rows -> partial; last CTA finalises
 template <bool BACKWARD>
 __global__ void __launch_bounds__(BN_THREADS) bn_reduce_kernel(BnArgs a) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sh[BN_THREADS * 8];
   __shared__ int last;
   const int C = a.C, tpr = C >> 2;            // threads per row
@@ -269,6 +272,8 @@ __device__ void bn_stats_to_smem(const BnArgs& a, float* st0, float* st1, double
 }
 
 __global__ void __launch_bounds__(BN_THREADS) bn_fwd_apply_kernel(BnArgs a) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float st0[BN_MAX_C], st1[BN_MAX_C];
   __shared__ double tot[2 * BN_MAX_C], shd[BN_THREADS];
   bn_stats_to_smem<false>(a, st0, st1, tot, shd);
@@ -298,6 +303,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_fwd_apply_kernel(BnArgs a) {
 }
 
 __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(BnArgs a) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float st0[BN_MAX_C], st1[BN_MAX_C];
   __shared__ double tot[2 * BN_MAX_C], shd[BN_THREADS];
   bn_stats_to_smem<true>(a, st0, st1, tot, shd);
@@ -341,6 +348,8 @@ __device__ __forceinline__ unsigned bn_ld_acquire(const unsigned* p) {
 }
 
 __global__ void __launch_bounds__(BN_THREADS, 1) bn_bwd_fused_kernel(BnArgs a, unsigned* barrier, int rows_per_cta) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float bn_dyn[];
   __shared__ float st0[BN_MAX_C], st1[BN_MAX_C];
   __shared__ double tot[2 * BN_MAX_C], shd[BN_THREADS];
@@ -507,8 +516,8 @@ static int bn_prepare(BnArgs& a) {
 extern "C" int bn_forward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (bn_prepare(a) != 0) return -1;
-  bn_reduce_kernel<false><<<a.n_partials, BN_THREADS, 0, st>>>(a);
-  bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4, a.fused_finalize), BN_THREADS, 0, st>>>(a);
+  launch_k(bn_reduce_kernel<false>, dim3(a.n_partials), dim3(BN_THREADS), 0, st, a);
+  launch_k(bn_fwd_apply_kernel, dim3(grid_for((long long)a.P * a.C / 4, a.fused_finalize)), dim3(BN_THREADS), 0, st, a);
   return (int)cudaGetLastError();
 }
 
@@ -520,7 +529,7 @@ extern "C" int bn_forward_partials(const BnArgs* args, int n_partials, cudaStrea
   if (n_partials < 1 || (long long)n_partials * 2 * a.C > BN_FUSED_LIMIT || a.partial == nullptr) return -2;
   a.n_partials = n_partials;
   a.fused_finalize = 1;
-  bn_fwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4, a.fused_finalize), BN_THREADS, 0, st>>>(a);
+  launch_k(bn_fwd_apply_kernel, dim3(grid_for((long long)a.P * a.C / 4, a.fused_finalize)), dim3(BN_THREADS), 0, st, a);
   return (int)cudaGetLastError();
 }
 
@@ -576,11 +585,11 @@ extern "C" int bn_backward(const BnArgs* args, cudaStream_t st) {
     }
     a.n_partials = G;
     a.fused_finalize = 1;
-    bn_bwd_fused_kernel<<<G, BN_THREADS, dyn, st>>>(a, bar, rows);
+    launch_k(bn_bwd_fused_kernel, dim3(G), dim3(BN_THREADS), dyn, st, a, bar, rows);
     return (int)cudaGetLastError();
   }
-  bn_reduce_kernel<true><<<a.n_partials, BN_THREADS, 0, st>>>(a);
-  bn_bwd_apply_kernel<<<grid_for((long long)a.P * a.C / 4, a.fused_finalize), BN_THREADS, 0, st>>>(a);
+  launch_k(bn_reduce_kernel<true>, dim3(a.n_partials), dim3(BN_THREADS), 0, st, a);
+  launch_k(bn_bwd_apply_kernel, dim3(grid_for((long long)a.P * a.C / 4, a.fused_finalize)), dim3(BN_THREADS), 0, st, a);
   return (int)cudaGetLastError();
 }
 

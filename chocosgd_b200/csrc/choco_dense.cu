@@ -13,60 +13,10 @@
 // Quantizer: dl_code/pcode/utils/sparsification.py:87-98 (which ships the de-quantized fp32
 // tensor; here (nbits + 1) bits per element travel).  A zero tensor quantizes to zeros.
 #include "common.cuh"
+#include "launch.cuh"
+#include "codec_dev.cuh"
 
 #define MODE_DECODE 1
-
-__device__ __forceinline__ float qsgd_scale_of(int n, int s, int biased) {
-  if (!biased) return 1.f;
-  const float a = (float)n / ((float)s * (float)s), b = sqrtf((float)n) / (float)s;
-  return 1.f / (fminf(a, b) + 1.f);
-}
-
-// value of element `bit` of a 32-position group given its plane words
-__device__ __forceinline__ float qsgd_value(const uint32_t* planes, int nbits, int bit, float unit) {
-  uint32_t lv = 0;
-  for (int b = 0; b < nbits; ++b) lv |= ((planes[b] >> bit) & 1u) << b;
-  const float mag = unit * (float)lv;
-  return ((planes[nbits] >> bit) & 1u) ? -mag : mag;
-}
-
-// Decode 4 consecutive positions of one group and accumulate  acc[e] += unit * level * sign.
-// Up to 8 plane words (nbits <= 7) stay in registers (fully unrolled, predicated loads).
-__device__ __forceinline__ void qsgd_accumulate4(const uint32_t* __restrict__ src, int nbits, int bit0, int n_valid,
-                                                 float unit, float* acc, float* acc2, float w2) {
-  if (nbits <= 7) {
-    // The four positions' bits of one plane are a nibble; multiplying it by 0x00204081 and masking
-    // with 0x01010101 drops bit e into byte e, so the four levels are assembled side by side in
-    // one register with a handful of operations per plane (not per plane and position).
-    uint32_t levels = 0, sgn = 0;
-#pragma unroll
-    for (int b = 0; b < 8; ++b) {
-      if (b <= nbits) {
-        const uint32_t nib = (__ldcg(src + b) >> bit0) & 0xFu;
-        if (b < nbits) levels |= ((nib * 0x00204081u) & 0x01010101u) << b;
-        else sgn = nib;
-      }
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      if (e < n_valid) {
-        float q = unit * (float)((levels >> (8 * e)) & 0xFFu);
-        q = ((sgn >> e) & 1u) ? -q : q;
-        acc[e] += q;
-        if (acc2 != nullptr) acc2[e] += w2 * q;
-      }
-    }
-  } else {
-    uint32_t planes[33];
-    for (int b = 0; b <= nbits; ++b) planes[b] = __ldcg(src + b);
-    for (int e = 0; e < 4; ++e)
-      if (e < n_valid) {
-        const float q = qsgd_value(planes, nbits, bit0 + e, unit);
-        acc[e] += q;
-        if (acc2 != nullptr) acc2[e] += w2 * q;
-      }
-  }
-}
 
 // Warp-cooperative form (nbits <= 7): a warp covers 128 consecutive positions = 4 groups; the
 // 4 (nbits + 1) plane words are loaded ONCE (lane j loads word j) and handed out by shuffles, so
@@ -100,6 +50,8 @@ __device__ __forceinline__ void qsgd_accumulate4_warp(const uint32_t* __restrict
 // codec: 0 = qsgd (fused decode + L2 norm), 1 = top-k (first radix histogram), 2 = random-k
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_dense_prep_kernel(const ChocoParams* __restrict__ params,
                                                                        int mode, int codec) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -262,13 +214,15 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_dense_prep_kernel(const C
 extern "C" int choco_dense_prep(const void* params_dev, int n_chunks, int n_ranks, int mode, int codec,
                                 cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  choco_dense_prep_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev),
+  launch_k(choco_dense_prep_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev),
                                                              mode, codec);
   return (int)cudaGetLastError();
 }
 
 // ---- QSGD quantize + bit-slice + push ------------------------------------------------------
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_generic_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -343,6 +297,8 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_generic_kernel(
 // ballots, one multiply instead of a division per element.
 template <int NBITS>
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -408,10 +364,10 @@ extern "C" int choco_qsgd_pack_nbits(const void* params_dev, int n_chunks, int n
   dim3 grid(n_chunks, n_ranks);
   const ChocoParams* pp = reinterpret_cast<const ChocoParams*>(params_dev);
   switch (nbits) {
-#define QSGD_CASE(B) case B: choco_qsgd_pack_kernel<B><<<grid, CHOCO_THREADS, 0, stream>>>(pp); break;
+#define QSGD_CASE(B) case B: launch_k(choco_qsgd_pack_kernel<B>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, pp); break;
     QSGD_CASE(1) QSGD_CASE(2) QSGD_CASE(3) QSGD_CASE(4) QSGD_CASE(5) QSGD_CASE(6) QSGD_CASE(7) QSGD_CASE(8)
 #undef QSGD_CASE
-    default: choco_qsgd_pack_generic_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(pp);
+    default: launch_k(choco_qsgd_pack_generic_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, pp);
   }
   return (int)cudaGetLastError();
 }
@@ -419,12 +375,14 @@ extern "C" int choco_qsgd_pack_nbits(const void* params_dev, int n_chunks, int n
 // nbits unknown to the caller: the generic kernel (reads it from the parameter block)
 extern "C" int choco_qsgd_pack(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  choco_qsgd_pack_generic_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  launch_k(choco_qsgd_pack_generic_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev));
   return (int)cudaGetLastError();
 }
 
 // decode-only (flush after the last training step): x_hat, s += payloads of step t-1
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_decode_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -481,6 +439,6 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_decode_kernel(const 
 
 extern "C" int choco_qsgd_decode(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  choco_qsgd_decode_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  launch_k(choco_qsgd_decode_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev));
   return (int)cudaGetLastError();
 }

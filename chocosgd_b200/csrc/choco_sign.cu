@@ -20,6 +20,7 @@
 // gridDim.y enumerates logical ranks whose state lives on this GPU (1 in production; n
 // in the single-GPU loopback used by the tests, where "peer" pointers are local).
 #include "common.cuh"
+#include "launch.cuh"
 
 #define MODE_DECODE 1
 #define MODE_PUSH 2
@@ -31,6 +32,8 @@ __device__ __forceinline__ float sel_sign(uint32_t word, int bit, float mag) {
 // NP = number of peers known at compile time (unrolled register arrays), or -1 = runtime.
 template <int NP>
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_sign_kernel(const ChocoParams* __restrict__ params, int mode) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -237,12 +240,12 @@ extern "C" int choco_sign_step(const void* params_dev, int n_chunks, int n_ranks
   dim3 grid(n_chunks, n_ranks);
   const ChocoParams* p = reinterpret_cast<const ChocoParams*>(params_dev);
   switch (n_peers_hint) {
-    case 0: choco_sign_kernel<0><<<grid, CHOCO_THREADS, 0, stream>>>(p, mode); break;
-    case 1: choco_sign_kernel<1><<<grid, CHOCO_THREADS, 0, stream>>>(p, mode); break;
-    case 2: choco_sign_kernel<2><<<grid, CHOCO_THREADS, 0, stream>>>(p, mode); break;
-    case 4: choco_sign_kernel<4><<<grid, CHOCO_THREADS, 0, stream>>>(p, mode); break;
-    case 7: choco_sign_kernel<7><<<grid, CHOCO_THREADS, 0, stream>>>(p, mode); break;
-    default: choco_sign_kernel<-1><<<grid, CHOCO_THREADS, 0, stream>>>(p, mode); break;
+    case 0: launch_k(choco_sign_kernel<0>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
+    case 1: launch_k(choco_sign_kernel<1>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
+    case 2: launch_k(choco_sign_kernel<2>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
+    case 4: launch_k(choco_sign_kernel<4>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
+    case 7: launch_k(choco_sign_kernel<7>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
+    default: launch_k(choco_sign_kernel<-1>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
   }
   return (int)cudaGetLastError();
 }

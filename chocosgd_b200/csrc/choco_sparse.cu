@@ -16,6 +16,7 @@
 // decode: one launch per source payload (indices inside one payload are distinct, so no
 //   atomics are needed and the result is bitwise reproducible).
 #include "common.cuh"
+#include "launch.cuh"
 
 __device__ __forceinline__ uint32_t key_of(float d) { return __float_as_uint(d) & 0x7FFFFFFFu; }
 
@@ -59,6 +60,8 @@ __device__ void find_bucket(const uint32_t* __restrict__ hist, int nbins, uint32
 // pass 3: digit-3 histogram of keys whose digits 1 and 2 equal the selected buckets
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_hist_kernel(const ChocoParams* __restrict__ params,
                                                                       int pass) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -102,12 +105,14 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_hist_kernel(const Ch
 
 extern "C" int choco_topk_hist(const void* params_dev, int n_chunks, int n_ranks, int pass, cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  choco_topk_hist_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev), pass);
+  launch_k(choco_topk_hist_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev), pass);
   return (int)cudaGetLastError();
 }
 
 // threshold key and per-chunk counts
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_count_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -171,7 +176,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_count_kernel(const C
 
 extern "C" int choco_topk_count(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  choco_topk_count_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  launch_k(choco_topk_count_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev));
   return (int)cudaGetLastError();
 }
 
@@ -192,6 +197,8 @@ __device__ __forceinline__ void publish_if_last(const ChocoParams& p, uint32_t n
 
 // ordered compaction: payload = [sum_k int32 indices][sum_k fp32 values]
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -322,7 +329,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const Ch
 
 extern "C" int choco_topk_emit(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  choco_topk_emit_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  launch_k(choco_topk_emit_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev));
   return (int)cudaGetLastError();
 }
 
@@ -337,6 +344,8 @@ __device__ __forceinline__ int segment_of_entry(const SegTable& tb, int e) {
 
 // random-k: payload = [sum_k fp32 values]; entry e of tensor `seg` is element perm(e - koff)
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_randk_emit_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const uint32_t t = p.step[0];
@@ -358,12 +367,14 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_randk_emit_kernel(const C
 
 extern "C" int choco_randk_emit(const void* params_dev, int n_blocks, int n_ranks, cudaStream_t stream) {
   dim3 grid(n_blocks, n_ranks);
-  choco_randk_emit_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  launch_k(choco_randk_emit_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev));
   return (int)cudaGetLastError();
 }
 
 // Bounded wait for the neighbours' flags of step t-1 (one CTA per logical rank).
 __global__ void choco_wait_flags_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.x];
   const uint32_t t = p.step[0];
   if (t == 0 || p.step[2] >= t) return;
@@ -373,7 +384,7 @@ __global__ void choco_wait_flags_kernel(const ChocoParams* __restrict__ params) 
 }
 
 extern "C" int choco_wait_flags(const void* params_dev, int n_ranks, cudaStream_t stream) {
-  choco_wait_flags_kernel<<<n_ranks, 32, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev));
+  launch_k(choco_wait_flags_kernel, dim3(n_ranks), dim3(32), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev));
   return (int)cudaGetLastError();
 }
 
@@ -382,6 +393,8 @@ extern "C" int choco_wait_flags(const void* params_dev, int n_ranks, cudaStream_
 // mark_done: this is the last source; record that step t-1 has been applied.
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_decode_kernel(const ChocoParams* __restrict__ params,
                                                                           int src, int codec, int mark_done) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const uint32_t t = p.step[0];
@@ -420,6 +433,8 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_decode_kernel(cons
 }
 
 __global__ void choco_mark_decoded_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.x];
   const uint32_t t = p.step[0];
   if (threadIdx.x == 0 && t > 0 && p.step[2] < t && p.status[0] == CHOCO_OK) p.step[2] = t;
@@ -429,10 +444,10 @@ extern "C" int choco_sparse_decode(const void* params_dev, int n_blocks, int n_r
                                    cudaStream_t stream) {
   const ChocoParams* p = reinterpret_cast<const ChocoParams*>(params_dev);
   if (src == 1000) {  // all sources applied: record it
-    choco_mark_decoded_kernel<<<n_ranks, 32, 0, stream>>>(p);
+    launch_k(choco_mark_decoded_kernel, dim3(n_ranks), dim3(32), 0, stream, p);
     return (int)cudaGetLastError();
   }
   dim3 grid(n_blocks, n_ranks);
-  choco_sparse_decode_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(p, src, codec, 0);
+  launch_k(choco_sparse_decode_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, src, codec, 0);
   return (int)cudaGetLastError();
 }

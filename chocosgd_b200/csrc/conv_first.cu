@@ -11,6 +11,7 @@
 // Replaces the library's direct-convolution and wgrad kernels for this layer
 // (dl_code/pcode/models/resnet.py:189, the first convolution of the CIFAR ResNet).
 #include <cuda_runtime.h>
+#include "launch.cuh"
 #include <stdint.h>
 
 #define CF_THREADS 256
@@ -44,6 +45,8 @@ __device__ __forceinline__ void cf_load_patch(const ConvFirstArgs& a, int n, int
 
 template <int COUT>
 __global__ void __launch_bounds__(CF_THREADS) conv_first_fwd_kernel(ConvFirstArgs a) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int Q = COUT / 4;                 // channel quads per pixel
   constexpr int PPB = CF_THREADS / Q;         // pixels per CTA per trip
   __shared__ float red[CF_THREADS * 8];
@@ -100,6 +103,8 @@ __global__ void __launch_bounds__(CF_THREADS) conv_first_fwd_kernel(ConvFirstArg
 
 template <int COUT>
 __global__ void __launch_bounds__(CF_THREADS) conv_first_wgrad_kernel(ConvFirstArgs a) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int Q = COUT / 2;                 // channel pairs per pixel
   constexpr int PPB = CF_THREADS / Q;
   extern __shared__ float cf_red[];           // [CF_THREADS][54]
@@ -138,6 +143,8 @@ __global__ void __launch_bounds__(CF_THREADS) conv_first_wgrad_kernel(ConvFirstA
 }
 
 __global__ void conv_first_reduce_kernel(const float* __restrict__ partial, int n_parts, int n, float* __restrict__ dw) {
+  pdl_wait();
+  pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float acc = 0.f;
@@ -177,9 +184,9 @@ extern "C" int conv_first_forward(const void* x, const void* w, void* y, void* s
   a.stats = reinterpret_cast<float*>(stats);
   a.N = N; a.H = H; a.W = W;
   const int grid = conv_first_grid(N, H, W, Cout);
-  if (Cout == 16) conv_first_fwd_kernel<16><<<grid, CF_THREADS, 0, st>>>(a);
-  else if (Cout == 32) conv_first_fwd_kernel<32><<<grid, CF_THREADS, 0, st>>>(a);
-  else conv_first_fwd_kernel<64><<<grid, CF_THREADS, 0, st>>>(a);
+  if (Cout == 16) launch_k(conv_first_fwd_kernel<16>, dim3(grid), dim3(CF_THREADS), 0, st, a);
+  else if (Cout == 32) launch_k(conv_first_fwd_kernel<32>, dim3(grid), dim3(CF_THREADS), 0, st, a);
+  else launch_k(conv_first_fwd_kernel<64>, dim3(grid), dim3(CF_THREADS), 0, st, a);
   return (int)cudaGetLastError();
 }
 
@@ -202,13 +209,13 @@ extern "C" int conv_first_wgrad(const void* x, const void* dy, void* dw, void* s
     if (e != cudaSuccess) return (int)e;
     cfg = true;
   }
-  if (Cout == 16) conv_first_wgrad_kernel<16><<<grid, CF_THREADS, smem, st>>>(a);
-  else if (Cout == 32) conv_first_wgrad_kernel<32><<<grid, CF_THREADS, smem, st>>>(a);
-  else conv_first_wgrad_kernel<64><<<grid, CF_THREADS, smem, st>>>(a);
+  if (Cout == 16) launch_k(conv_first_wgrad_kernel<16>, dim3(grid), dim3(CF_THREADS), smem, st, a);
+  else if (Cout == 32) launch_k(conv_first_wgrad_kernel<32>, dim3(grid), dim3(CF_THREADS), smem, st, a);
+  else launch_k(conv_first_wgrad_kernel<64>, dim3(grid), dim3(CF_THREADS), smem, st, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   const int n = Cout * 27;
-  conv_first_reduce_kernel<<<(n + 127) / 128, 128, 0, st>>>(reinterpret_cast<const float*>(scratch), grid, n,
+  launch_k(conv_first_reduce_kernel, dim3((n + 127) / 128), dim3(128), 0, st, reinterpret_cast<const float*>(scratch), grid, n,
                                                            reinterpret_cast<float*>(dw));
   return (int)cudaGetLastError();
 }

@@ -16,6 +16,7 @@
 // forward and dgrad.  Bounded mbarrier waits as in the GEMM kernel; no cluster multicast.
 // Two kernels follow: the one-tile-per-CTA form and the persistent form (default) further down.
 #include "tc_common.cuh"
+#include "launch.cuh"
 #include <stdlib.h>
 
 #define CONV_THREADS 192
@@ -73,6 +74,8 @@ conv3x3_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // set-up above touched shared memory and TMEM only
+  pdl_trigger();
 
   if (warp == 4 && lane == 0) {
     for (int i = 0; i < n_kb; ++i) {
@@ -229,6 +232,8 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // set-up above touched shared memory and TMEM only
+  pdl_trigger();
 
   if (warp == 4) {
     const int my_tiles = (g.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -359,6 +364,8 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 
 // W'[ci, r, s, co] = W[co, 2 - r, 2 - s, ci]   (both KRSC): the filter of the input-gradient convolution
 __global__ void conv_flip_weights_kernel(const float* __restrict__ w, float* __restrict__ out, int cout, int cin) {
+  pdl_wait();
+  pdl_trigger();
   const int total = cout * 9 * cin;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const int co = i % cout, tap = (i / cout) % 9, ci = i / (9 * cout);
@@ -374,6 +381,8 @@ struct FlipEntry {
 };
 
 __global__ void conv_flip_weights_multi_kernel(const FlipEntry* __restrict__ table) {
+  pdl_wait();
+  pdl_trigger();
   const FlipEntry e = table[blockIdx.y];
   const int total = e.cout * 9 * e.cin;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -384,13 +393,13 @@ __global__ void conv_flip_weights_multi_kernel(const FlipEntry* __restrict__ tab
 
 extern "C" int conv_flip_weights_multi(const void* table, int n_layers, int max_elems, cudaStream_t st) {
   dim3 grid((max_elems + 255) / 256 > 64 ? 64 : (max_elems + 255) / 256, n_layers);
-  conv_flip_weights_multi_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const FlipEntry*>(table));
+  launch_k(conv_flip_weights_multi_kernel, dim3(grid), dim3(256), 0, st, reinterpret_cast<const FlipEntry*>(table));
   return (int)cudaGetLastError();
 }
 
 extern "C" int conv_flip_weights(const void* w, void* out, int cout, int cin, cudaStream_t st) {
   const int total = cout * 9 * cin;
-  conv_flip_weights_kernel<<<(total + 255) / 256, 256, 0, st>>>(reinterpret_cast<const float*>(w),
+  launch_k(conv_flip_weights_kernel, dim3((total + 255) / 256), dim3(256), 0, st, reinterpret_cast<const float*>(w),
                                                                  reinterpret_cast<float*>(out), cout, cin);
   return (int)cudaGetLastError();
 }
@@ -425,7 +434,7 @@ static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, const ConvA
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  conv3x3_tf32_kernel<COUT, KC><<<tiles, CONV_THREADS, smem, st>>>(mx, mw, g);
+  launch_k(conv3x3_tf32_kernel<COUT, KC>, dim3(tiles), dim3(CONV_THREADS), smem, st, mx, mw, g);
   return (int)cudaGetLastError();
 }
 
@@ -439,7 +448,7 @@ static int launch_conv_persist(const CUtensorMap& mx, const CUtensorMap& mw, con
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  conv3x3_persist_kernel<COUT, KC><<<grid, CONV_THREADS, smem, st>>>(mx, mw, g);
+  launch_k(conv3x3_persist_kernel<COUT, KC>, dim3(grid), dim3(CONV_THREADS), smem, st, mx, mw, g);
   return (int)cudaGetLastError();
 }
 

@@ -17,6 +17,7 @@
 //   * the warps' accumulators are added in a fixed order, each CTA writes one slice of partial
 //     results, and a second small kernel adds the slices in index order (reproducible, no atomics).
 #include <cuda_runtime.h>
+#include "launch.cuh"
 #include <stdint.h>
 
 #define WG16_THREADS 256
@@ -50,6 +51,8 @@ __device__ __forceinline__ void wg16_cp16(float* dst, const float* src, bool val
 
 template <int W>
 __global__ void __launch_bounds__(WG16_THREADS) conv3x3_wgrad16_kernel(Wg16Args g) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int TH = 128 / W, HW = W + 2, HH = TH + 2;
   constexpr int DY_FLOATS = 128 * WG16_PS, X_FLOATS = HH * HW * WG16_PS;
   extern __shared__ float wg16_smem[];
@@ -164,6 +167,8 @@ __global__ void __launch_bounds__(WG16_THREADS) conv3x3_wgrad16_kernel(Wg16Args 
 // 64 outputs per CTA, 4 threads per output (slices q, q + 4, ... in order, then the four sub-sums)
 __global__ void __launch_bounds__(256) wgrad16_reduce_kernel(const float* __restrict__ partial, int n_parts,
                                                              float* __restrict__ dw) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sub[4][64];
   const int il = threadIdx.x & 63, q = threadIdx.x >> 6;
   const int i = blockIdx.x * 64 + il;
@@ -211,7 +216,7 @@ extern "C" int conv3x3_wgrad16(const void* x, const void* dy, void* dw, void* sc
       if (e != cudaSuccess) return (int)e;
       cfg = true;
     }
-    conv3x3_wgrad16_kernel<32><<<grid, WG16_THREADS, smem, st>>>(g);
+    launch_k(conv3x3_wgrad16_kernel<32>, dim3(grid), dim3(WG16_THREADS), smem, st, g);
   } else {
     static bool cfg = false;
     if (!cfg) {
@@ -219,11 +224,11 @@ extern "C" int conv3x3_wgrad16(const void* x, const void* dy, void* dw, void* sc
       if (e != cudaSuccess) return (int)e;
       cfg = true;
     }
-    conv3x3_wgrad16_kernel<16><<<grid, WG16_THREADS, smem, st>>>(g);
+    launch_k(conv3x3_wgrad16_kernel<16>, dim3(grid), dim3(WG16_THREADS), smem, st, g);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  wgrad16_reduce_kernel<<<WG16_OUT / 64, 256, 0, st>>>(reinterpret_cast<const float*>(scratch), grid,
+  launch_k(wgrad16_reduce_kernel, dim3(WG16_OUT / 64), dim3(256), 0, st, reinterpret_cast<const float*>(scratch), grid,
                                                                reinterpret_cast<float*>(dw));
   return (int)cudaGetLastError();
 }

@@ -15,6 +15,7 @@
 // 32- or 64-row operand replicated, N = 32).  Each CTA stores its partial dW into its own slice of a
 // scratch buffer; a second small kernel adds the slices in a fixed order (reproducible, no atomics).
 #include "tc_common.cuh"
+#include "launch.cuh"
 
 #define WG_THREADS 192
 #define WG_BSTAGES 9
@@ -71,6 +72,8 @@ conv3x3_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // set-up above touched shared memory and TMEM only
+  pdl_trigger();
 
   if (n_my > 0) {
     if (warp == 4) {
@@ -204,7 +207,7 @@ static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const Wgr
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  conv3x3_wgrad_kernel<C><<<grid, WG_THREADS, smem, st>>>(mdy, mx, g);
+  launch_k(conv3x3_wgrad_kernel<C>, dim3(grid), dim3(WG_THREADS), smem, st, mdy, mx, g);
   return (int)cudaGetLastError();
 }
 
@@ -212,6 +215,8 @@ static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const Wgr
 // adds the slices q, q + 4, ... in order, then the four sub-sums are added in order (reproducible).
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, int n_parts, int n,
                                                            float* __restrict__ dw) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float sub[4][64];
   const int il = threadIdx.x & 63, q = threadIdx.x >> 6;
   const int i = blockIdx.x * 64 + il;
@@ -268,7 +273,7 @@ extern "C" int conv3x3_wgrad_tf32(const void* x, const void* dy, void* dw, void*
   const int rc = C == 32 ? launch_wgrad<32>(mdy, mx, g, grid, st) : launch_wgrad<64>(mdy, mx, g, grid, st);
   if (rc) return rc;
   const int n = C * 9 * C;
-  wgrad_reduce_kernel<<<(n + 63) / 64, 256, 0, st>>>(reinterpret_cast<const float*>(scratch), (int)grid.x, n,
+  launch_k(wgrad_reduce_kernel, dim3((n + 63) / 64), dim3(256), 0, st, reinterpret_cast<const float*>(scratch), (int)grid.x, n,
                                                        reinterpret_cast<float*>(dw));
   return (int)cudaGetLastError();
 }

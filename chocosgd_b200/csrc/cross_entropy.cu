@@ -12,6 +12,7 @@
 // in a fixed order, so the loss is reproducible run to run.  Rows whose label lies outside
 // [0, C) contribute neither loss nor gradient and are not counted in the mean.
 #include <cuda_runtime.h>
+#include "launch.cuh"
 #include <stdint.h>
 
 #define CE_THREADS 128
@@ -31,6 +32,8 @@ __device__ __forceinline__ float ce_warp_sum(float v) {
 __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const float* __restrict__ z, const long long* __restrict__ tgt,
                                                                   float* __restrict__ dz, float* row_loss, int* row_rank,
                                                                   unsigned* counter, float* out, float* loss_out, int B, int C) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[CE_THREADS / 32];
   __shared__ int redi[CE_THREADS / 32];
   __shared__ int last;
@@ -119,6 +122,8 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const float* 
 
 // With ignored rows the mean runs over the counted rows only: rescale the gradient (B / n_valid).
 __global__ void ce_rescale_kernel(float* dz, const float* out, long long n, int B) {
+  pdl_wait();
+  pdl_trigger();
   const float nv = out[3];
   if (nv == (float)B || nv <= 0.f) return;
   const float f = (float)B / nv;
@@ -133,7 +138,7 @@ extern "C" int cross_entropy_fused(const void* logits, const void* target, void*
   float* row_loss = reinterpret_cast<float*>(scratch);
   int* row_rank = reinterpret_cast<int*>(row_loss + B);
   unsigned* counter = reinterpret_cast<unsigned*>(row_rank + B);
-  cross_entropy_kernel<<<B, CE_THREADS, 0, st>>>(reinterpret_cast<const float*>(logits),
+  launch_k(cross_entropy_kernel, dim3(B), dim3(CE_THREADS), 0, st, reinterpret_cast<const float*>(logits),
                                                  reinterpret_cast<const long long*>(target),
                                                  reinterpret_cast<float*>(dlogits), row_loss, row_rank, counter,
                                                  reinterpret_cast<float*>(out), reinterpret_cast<float*>(loss_out), B, C);
@@ -141,7 +146,7 @@ extern "C" int cross_entropy_fused(const void* logits, const void* target, void*
     const long long n = (long long)B * C;
     long long blocks = (n + 255) / 256;
     if (blocks > 1184) blocks = 1184;
-    ce_rescale_kernel<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<float*>(dlogits), reinterpret_cast<const float*>(out), n, B);
+    launch_k(ce_rescale_kernel, dim3((int)blocks), dim3(256), 0, st, reinterpret_cast<float*>(dlogits), reinterpret_cast<const float*>(out), n, B);
   }
   return (int)cudaGetLastError();
 }

@@ -11,8 +11,11 @@
 // kernels multiply into the gradient (torch.nn.utils.clip_grad_norm_ semantics,
 // dl_code/pcode/distributed_running_nlp.py:94-97).
 #include "common.cuh"
+#include "launch.cuh"
 
 __global__ void __launch_bounds__(CHOCO_THREADS) fused_sgd_kernel(const ChocoParams* __restrict__ params, int apply) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -62,13 +65,15 @@ __global__ void __launch_bounds__(CHOCO_THREADS) fused_sgd_kernel(const ChocoPar
 
 extern "C" int fused_sgd_step(const void* params_dev, int n_chunks, int n_ranks, int apply, cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  fused_sgd_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev), apply);
+  launch_k(fused_sgd_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev), apply);
   return (int)cudaGetLastError();
 }
 
 // ---- global gradient-norm clipping --------------------------------------------------------
 __global__ void __launch_bounds__(CHOCO_THREADS) grad_clip_kernel(const ChocoParams* __restrict__ params,
                                                                  float max_norm, float* norm_out) {
+  pdl_wait();
+  pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
   const int chunk = blockIdx.x;
@@ -112,7 +117,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) grad_clip_kernel(const ChocoPar
 extern "C" int grad_clip_coef(const void* params_dev, int n_chunks, int n_ranks, float max_norm, void* norm_out,
                               cudaStream_t stream) {
   dim3 grid(n_chunks, n_ranks);
-  grad_clip_kernel<<<grid, CHOCO_THREADS, 0, stream>>>(reinterpret_cast<const ChocoParams*>(params_dev), max_norm,
+  launch_k(grad_clip_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, reinterpret_cast<const ChocoParams*>(params_dev), max_norm,
                                                       reinterpret_cast<float*>(norm_out));
   return (int)cudaGetLastError();
 }

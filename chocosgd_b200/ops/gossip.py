@@ -36,7 +36,7 @@ from ..utils.error_handler import GossipTimeout
 from . import _lib
 
 MODE_DECODE, MODE_PUSH = 1, 2
-CODEC_ID = {"sign": 3, "quantize_qsgd": 0, "compress_top_k": 1, "compress_random_k": 2}
+CODEC_ID = {"sign": 3, "quantize_qsgd": 0, "compress_top_k": 1, "compress_random_k": 2, "raw": 4}
 HYP_LR, HYP_MOMENTUM, HYP_GAMMA, HYP_NESTEROV, HYP_GSCALE, HYP_N = 0, 1, 2, 3, 4, 8
 
 
@@ -124,6 +124,8 @@ def payload_layout(comm_op: str, seg: Segments, sum_k: int, nbits: int):
         return 2 * sum_k, 0
     if comm_op == "compress_random_k":
         return sum_k, 0
+    if comm_op == "raw":  # full-precision exchange (D-PSGD)
+        return seg.total, 0
     raise NotImplementedError(comm_op)
 
 
@@ -158,6 +160,8 @@ class ChocoEngine:
         self.tables = SegTables(seg, weight_decay, ks, self.device, chunk_elems)
         self.s_levels = qsgd_levels_from(quantize_level, qsgd_levels) if comm_op == "quantize_qsgd" else 1
         self.nbits = qsgd_nbits(self.s_levels) if comm_op == "quantize_qsgd" else 0
+        if not (0 <= self.nbits <= 30 and 0 < self.s_levels < 2 ** 31):
+            raise ValueError(f"QSGD with {self.s_levels} levels does not fit the packed format (at most 30 bits)")
         if comm_op == ALLREDUCE:
             # two-shot all-reduce: one shard of scattered gradients + one shard of averages per slot
             self.n_world = len(neighborhoods[self.ranks[0]])

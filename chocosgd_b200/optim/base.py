@@ -119,6 +119,83 @@ class DistributedOptimizer(Optimizer):
             return self.world_aggregator._agg(payload, communication_scheme="all_gather")
         return self._gather.all_gather(payload)
 
+    # ---- fused kernels of the non-CHOCO algorithms (ops/algos.py) ------------------------
+    engine = None
+    gamma_for_engine = 0.0
+
+    def fused_wanted(self) -> bool:
+        """True when the step should run in the hand-written kernels: a CUDA device, not the
+        ``--gossip_impl nccl`` baseline, and (for more than one node) peer mailboxes available."""
+        want = getattr(self.conf, "gossip_impl", "auto")
+        if self.device.type != "cuda" or want in ("nccl", "torch"):
+            return False
+        if self.identity_quantizer():
+            return False  # 32-bit "quantization" is the identity: nothing for the packed formats to do
+        return self.n_nodes == 1 or self._mailbox_ok()
+
+    def identity_quantizer(self) -> bool:
+        c = self.conf
+        return (c.comm_op == "quantize_qsgd" and getattr(c, "qsgd_levels", None) is None
+                and c.quantize_level is not None and int(c.quantize_level) >= 32)
+
+    def build_algo_engine(self, algo, comm_op, complete=False, hats=None, mem=None, **kw):
+        """Engine of one rank (one process per GPU).  ``complete``: the payload goes to every rank
+        (all-gather by push) instead of the graph neighbours."""
+        from ..ops.algos import AlgoEngine
+        from ..ops.gossip import RankBuffers
+        from ..parallel.symm import DistributedMailbox, LoopbackMailbox
+        from ..parallel.topology import Graph
+
+        conf, r = self.conf, self.rank
+        graph = Graph("complete", self.n_nodes, r) if complete else self.graph
+        nbh = {r: graph.get_neighborhood()}
+        if len(nbh[r]) - 1 > 16:
+            raise ValueError("the fused kernels support at most 16 peers per rank")
+        if self.momentum_buf is None:
+            self.momentum_buf = torch.zeros_like(self.arena.x)
+        dummy = torch.zeros(32, device=self.device)
+        bufs = {r: RankBuffers(self.arena.x, self.arena.g, self.momentum_buf, dummy, dummy)}
+        if self.n_nodes > 1:
+            mailbox = lambda pw: DistributedMailbox(graph, pw, self.device, self.group)
+        else:
+            mailbox = lambda pw: LoopbackMailbox({r: []}, pw, self.device)
+        return AlgoEngine(
+            algo, [r], bufs, nbh, self.seg, [g["weight_decay"] for g in self.param_groups], comm_op, mailbox,
+            self.device, hats={r: hats} if hats is not None else None, mems={r: mem} if mem is not None else None,
+            n_world=self.n_nodes, compress_ratio=conf.compress_ratio, quantize_level=conf.quantize_level,
+            qsgd_levels=getattr(conf, "qsgd_levels", None), is_biased=conf.is_biased,
+            seed=getattr(conf, "random_k_seed", 1234), wait_budget_ms=getattr(conf, "wait_budget_ms", 2000.0), **kw)
+
+    @property
+    def capturable(self) -> bool:
+        return self.engine is not None
+
+    def prepare_step(self):
+        """Host side of a fused step: refresh the device-resident hyper-parameters, account bits."""
+        self.local_index += 1
+        self.engine.set_hyper(self.lr, self.momentum, self.gamma_for_engine, self.nesterov)
+        self.n_bits = self.codec.n_bits() if getattr(self, "codec", None) is not None else 32 * self.seg.n_elements
+        return self.n_bits
+
+    def launch(self, stream=None):
+        """Device side of a fused step: the kernels, nothing else (what a CUDA graph captures)."""
+        self.engine.launch_step(stream)
+
+    def fused_step(self, timer, ep, label):
+        with timer(label, epoch=ep):
+            bits = self.prepare_step()
+            self.launch()
+        return bits
+
+    def check(self):
+        """Raise ``GossipTimeout`` if a bounded device-side wait of any transport of this optimizer
+        ran out (synchronises the device)."""
+        if self.engine is not None:
+            self.engine.check()
+        for ex in (self._exchange, self._gather):
+            if ex is not None and ex is not False and hasattr(ex, "check"):
+                ex.check()
+
     # ---- hyper-parameters ------------------------------------------------------------
     @property
     def lr(self) -> float:
@@ -220,8 +297,11 @@ class DistributedOptimizer(Optimizer):
         algo = dict(sd.get("algo_state", {}))
         self.local_index = int(algo.pop("local_index", 0))
         self.load_algo_state(algo)
+        if self.engine is not None and hasattr(self.engine, "algo"):
+            self.engine.reset_step(self.local_index)
         self.arena.rebind()
 
     def finalize(self):
-        """Complete any communication still in flight (end of training / before a checkpoint)."""
-        return None
+        """Complete any communication still in flight (end of training / before a checkpoint)
+        and surface a timed-out wait."""
+        self.check()

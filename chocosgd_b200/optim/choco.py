@@ -54,8 +54,8 @@ class ChocoSGD(DistributedOptimizer):
         want = getattr(conf, "gossip_impl", "auto") if impl == "auto" else impl
         if want == "auto":
             want = "fused" if (self.device.type == "cuda" and engine is not False) else "torch"
-        if want == "nccl":
-            want = "torch"
+        if want == "nccl" or self.identity_quantizer():
+            want = "torch"  # --quantize_level 32 is the identity codec: no packed format applies
         self.impl = want
         self.engine = None
         if self.impl == "fused":

@@ -28,9 +28,14 @@ class DeepSqueeze(DistributedOptimizer):
         self.codec = self.make_codec()
         self.consensus_stepsize = float(conf.consensus_stepsize)
         self.memory = torch.zeros_like(self.arena.x)
+        self.gamma_for_engine = self.consensus_stepsize
+        if self.fused_wanted():
+            self.engine = self.build_algo_engine("deep_squeeze", conf.comm_op, mem=self.memory)
 
     def step(self, closure=None, **kargs):
         timer, ep, a = self.timer_of(kargs), self.epoch_of(kargs), self.arena
+        if self.engine is not None:
+            return self.fused_step(timer, ep, "grad.sync")
         step = self.local_index
         self.local_index += 1
         with timer("grad.apply_grad", epoch=ep):

@@ -50,6 +50,16 @@ class DGC(DistributedOptimizer):
                 1.0 * i / n * self.compress_warmup_epochs for i in range(1, n + 1)
             ]
         self._codecs = {}
+        # Fused kernels: whenever the selection size is fixed for the whole run (no sparsity
+        # warm-up) and no per-tensor clipping is asked for; otherwise the PyTorch statement below.
+        static_ratio = not self.is_compress_op or self.compress_warmup_epochs <= 0
+        if (self.fused_wanted() and static_ratio and not self.clip_grad and self.n_nodes - 1 <= 16
+                and conf.comm_op in ("compress_top_k", "compress_random_k", "quantize_qsgd")
+                and not (conf.comm_op == "quantize_qsgd" and (conf.quantize_level or 0) >= 32)):
+            self.codec = self._codec(self._get_compress_ratio(0.0))
+            self.engine = self.build_algo_engine(
+                "dgc", conf.comm_op, complete=True, mem=self.memory if self.is_compress_op else None,
+                mask_momentum=bool(self.mask_momentum), use_memory=self.is_compress_op)
 
     def _get_compress_ratio(self, epoch_):
         if not self.is_compress_op:
@@ -86,6 +96,8 @@ class DGC(DistributedOptimizer):
 
     def step(self, closure=None, **kargs):
         timer, ep, a = self.timer_of(kargs), self.epoch_of(kargs), self.arena
+        if self.engine is not None:
+            return self.fused_step(timer, ep, "grad.sync")
         step = self.local_index
         self.local_index += 1
         with timer("grad.apply_grad", epoch=ep):

@@ -28,9 +28,13 @@ class ECD_PSGD(DistributedOptimizer):
         super().__init__(model, conf, graph, group)
         self.codec = self.make_codec()
         self.neighbor_hat_params = {r: self.arena.x.clone() for r in self.neighbors_info}
+        if self.fused_wanted():
+            self.engine = self.build_algo_engine("ecd_psgd", conf.comm_op, hats=self.neighbor_hat_params)
 
     def step(self, closure=None, **kargs):
         timer, ep, a = self.timer_of(kargs), self.epoch_of(kargs), self.arena
+        if self.engine is not None:
+            return self.fused_step(timer, ep, "grad.sync")
         step = self.local_index
         self.local_index += 1
         t = float(self.local_index)

@@ -27,9 +27,13 @@ class EF_SignSGD(DistributedOptimizer):
         self.codec = SignCodec(self.seg)
         self.memory = torch.zeros_like(self.arena.x)
         self.valid = self.arena.valid_mask()
+        if self.fused_wanted() and self.n_nodes - 1 <= 16:
+            self.engine = self.build_algo_engine("ef_sign_sgd", "sign", complete=True, mem=self.memory)
 
     def step(self, closure=None, **kargs):
         timer, ep, a = self.timer_of(kargs), self.epoch_of(kargs), self.arena
+        if self.engine is not None:
+            return self.fused_step(timer, ep, "sync.sync")
         self.local_index += 1
         with timer("sync.apply_grad", epoch=ep):
             d = self.local_direction()

@@ -20,12 +20,17 @@ class SGD(DistributedOptimizer):
         # On a GPU the update runs in the fused kernels (capturable in a CUDA graph):
         #   one node                  fused momentum-SGD
         #   complete graph, n > 1     gradient all-reduce + SGD in ONE kernel over the peer mailboxes
-        #   other graphs, n > 1       fused SGD, then push + fused weighted neighbour sum (eager)
+        #   other graphs, n > 1       fused SGD + push of x, then wait + weighted neighbour sum (2 kernels)
         self.engine = None
         self.fused_allreduce = False
         want = getattr(conf, "gossip_impl", "auto")
         multi = self.n_nodes > 1 and self._mailbox_ok() and self.n_nodes - 1 <= 16
-        if self.device.type == "cuda" and want != "nccl" and (self.n_nodes == 1 or multi):
+        self.fused_gossip = False
+        if self.device.type == "cuda" and want != "nccl" and multi and not self.is_centralized:
+            # D-PSGD: local step + raw push in one kernel, wait + weighted neighbour sum in a second
+            self.engine = self.build_algo_engine("dpsgd", "raw")
+            self.fused_gossip = True
+        elif self.device.type == "cuda" and want != "nccl" and (self.n_nodes == 1 or multi):
             from ..ops.gossip import ALLREDUCE, ChocoEngine, RankBuffers
             from ..parallel.symm import DistributedMailbox, LoopbackMailbox
 
@@ -47,7 +52,7 @@ class SGD(DistributedOptimizer):
 
     @property
     def capturable(self) -> bool:
-        return self.engine is not None and (self.n_nodes == 1 or self.fused_allreduce)
+        return self.engine is not None and (self.n_nodes == 1 or self.fused_allreduce or self.fused_gossip)
 
     def prepare_step(self):
         self.local_index += 1
@@ -56,7 +61,9 @@ class SGD(DistributedOptimizer):
         return self.n_bits
 
     def launch(self, stream=None):
-        if self.fused_allreduce:
+        if self.fused_gossip:
+            self.engine.launch_step(stream)
+        elif self.fused_allreduce:
             self.engine.launch_allreduce_sgd(stream)
         else:
             self.engine.launch_sgd_only(True, stream)
@@ -74,7 +81,7 @@ class SGD(DistributedOptimizer):
             with timer("sync.apply_grad", epoch=ep):
                 bits = self.prepare_step()
                 self.launch()
-            if self.n_nodes > 1 and not self.fused_allreduce:
+            if self.n_nodes > 1 and not self.fused_allreduce and not self.fused_gossip:
                 with timer("sync.sync", epoch=ep):
                     self.neighbor_exchange().mix_(a.x)
             return bits
