@@ -20,3 +20,25 @@ def optimum(A, y, reg=None, seed=0, max_iter=2000):
                         random_state=seed, n_iter_no_change=20)
     clf.fit(A, y)
     return regularised_loss(clf, A, y, reg), clf
+
+
+def main(argv=None):
+    """``python -m chocosgd_b200.convex.baselines <data.pickle> <out dir>`` writes ``baselines.pickle``
+    (the optimal loss f*, as ``convex_code/baselines.py:24-36`` does for epsilon)."""
+    import pickle
+    import sys
+
+    from .data import pickle_it
+
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if len(argv) != 2:
+        raise SystemExit(main.__doc__)
+    with open(argv[0], "rb") as f:
+        A, y = pickle.load(f)
+    best, _ = optimum(A, y)
+    pickle_it(best, "baselines", argv[1])
+    print("optimal regularised loss:", best)
+
+
+if __name__ == "__main__":
+    main()

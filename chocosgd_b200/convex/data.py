@@ -41,3 +41,23 @@ def unpickle_dir(d):
             with open(os.path.join(d, fn), "rb") as f:
                 out[fn[:-7]] = pickle.load(f)
     return out
+
+
+def main(argv=None):
+    """``python -m chocosgd_b200.convex.data <libsvm file> <out.pickle>`` or
+    ``python -m chocosgd_b200.convex.data --synthetic <out.pickle> [N d]``."""
+    import sys
+
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "--synthetic":
+        n, d = (int(argv[2]), int(argv[3])) if len(argv) >= 4 else (40000, 2000)
+        with open(argv[1], "wb") as f:
+            pickle.dump(synthetic_logistic(n, d), f, protocol=pickle.HIGHEST_PROTOCOL)
+    elif len(argv) == 2:
+        pickle_libsvm(argv[0], argv[1])
+    else:
+        raise SystemExit(main.__doc__)
+
+
+if __name__ == "__main__":
+    main()

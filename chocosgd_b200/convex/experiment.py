@@ -65,3 +65,26 @@ def epsilon_final_params(n=400000, d=2000, n_cores=9, num_epoch=10, seeds=(1, 2,
                 out.append(Parameters(name=name, split_data_strategy=split, random_seed=seed,
                                       split_data_random_seed=seed, **common, **c))
     return out
+
+
+def main(argv=None):
+    """``python -m chocosgd_b200.convex.experiment final --dataset data.pickle --out dir [--nproc 10]``."""
+    import argparse
+
+    p = argparse.ArgumentParser()
+    p.add_argument("sweep", choices=("final",))
+    p.add_argument("--dataset", required=True)
+    p.add_argument("--out", required=True)
+    p.add_argument("--nproc", type=int, default=1)
+    p.add_argument("--num_epoch", type=int, default=10)
+    p.add_argument("--seeds", default="1,2,3,4,5")
+    a = p.parse_args(argv)
+    with open(a.dataset, "rb") as f:
+        A, y = pickle.load(f)
+    params = epsilon_final_params(n=A.shape[0], d=A.shape[1], num_epoch=a.num_epoch,
+                                  seeds=tuple(int(s) for s in a.seeds.split(",")))
+    run_experiment(a.out, (A, y), params, nproc=a.nproc)
+
+
+if __name__ == "__main__":
+    main()

@@ -34,6 +34,13 @@ def _cv_datasets(conf):
             SyntheticImages(shape, classes, n_train, seed=conf.manual_seed),
             SyntheticImages(shape, classes, n_val, seed=conf.manual_seed + 1),
         )
+    if name in ("epsilon", "rcv1"):
+        # feature-vector sets packed by `python -m chocosgd_b200.data.serialize --libsvm ...`
+        from .lmdb_dataset import define_epsilon_or_rcv1_folder
+
+        root = os.path.join(conf.data_dir, name)
+        return (define_epsilon_or_rcv1_folder(os.path.join(root, f"{name}_train.lmdb")),
+                define_epsilon_or_rcv1_folder(os.path.join(root, f"{name}_test.lmdb")))
     from .vision import get_vision_dataset
 
     return (
@@ -98,7 +105,15 @@ def define_nlp_dataset(conf, graph, run, device=None):
     else:
         corpus = Corpus(os.path.join(conf.data_dir, conf.data))
         n_tokens, train_ids, val_ids = len(corpus.dictionary), corpus.train, corpus.valid
+        if conf.rnn_use_pretrained_emb:
+            from .embeddings import find_vector_file, load_vectors
+
+            vec_file = find_vector_file(os.path.join(conf.data_dir, conf.data))
+            if vec_file is not None:
+                vectors, found = load_vectors(vec_file, corpus.dictionary.word2idx, seed=conf.manual_seed)
+                print(f"=> {found} / {n_tokens} words initialised from {vec_file}")
     gb = conf.batch_size * world
+    vectors = locals().get("vectors")
 
     def batchify(ids):
         n = ids.numel() // gb
@@ -111,8 +126,8 @@ def define_nlp_dataset(conf, graph, run, device=None):
     run.num_warmup_train_batches_per_worker = len(train_loader) * conf.lr_warmup_epochs
     run.num_iterations_per_worker = conf.num_iterations // world
     run.num_batches_val_per_device_per_epoch = len(val_loader)
-    return {"n_tokens": n_tokens, "train_loader": train_loader, "val_loader": val_loader, "emb_size": None,
-            "vectors": None}
+    return {"n_tokens": n_tokens, "train_loader": train_loader, "val_loader": val_loader,
+            "emb_size": None if vectors is None else vectors.size(1), "vectors": vectors}
 
 
 def define_dataset(conf, graph, run, force_shuffle=False, device=None):

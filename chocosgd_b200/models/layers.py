@@ -64,6 +64,8 @@ def num_classes_of(dataset: str) -> int:
         return 100
     if "imagenet" in dataset:
         return 1000
+    if dataset in ("epsilon", "rcv1"):
+        return 2
     if dataset.startswith("synthetic"):
         return 10
     raise ValueError(f"unknown dataset {dataset!r}")

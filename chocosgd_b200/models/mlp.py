@@ -7,6 +7,9 @@ import torch.nn as nn
 from . import layers as L
 
 
+FEATURE_SIZES = {"epsilon": 2000, "rcv1": 47236}   # LIBSVM feature sets (feature vectors, two classes)
+
+
 class MLP(nn.Module):
     def __init__(self, dataset, num_layers, hidden_size, drop_rate):
         super().__init__()
@@ -14,6 +17,8 @@ class MLP(nn.Module):
         self.num_classes = L.num_classes_of(dataset)
         if "mnist" in dataset:
             input_size = 28 * 28
+        elif dataset in FEATURE_SIZES:
+            input_size = FEATURE_SIZES[dataset]
         else:
             input_size = 32 * 32 * 3
         for i in range(1, num_layers + 1):
