@@ -1,7 +1,8 @@
 """Reference arm of the benchmark: the UNMODIFIED reference code installed under
 ``baseline/_ref`` (its ``pcode`` package), driven through its own public classes.
 
-What runs: ``pcode.models.resnet`` (ResNet-20), ``pcode.create_optimizer.define_optimizer``
+What runs: ``pcode.models.resnet`` (ResNet-20 / ResNet-50) or ``pcode.models.RNNLM``,
+``pcode.create_optimizer.define_optimizer``
 with ``--optimizer parallel_choco_v``, the reference compressors / aggregators / topology,
 and the body of its training iteration (``dl_code/pcode/distributed_running_cv.py:42-62``:
 host->device copy, zero_grad, forward, loss, metrics with their ``.item()`` reads, backward,
@@ -108,7 +109,10 @@ def available():
     return os.path.isdir(os.path.join(REF, "pcode"))
 
 
-def build(rank, world, comm_op, batch_size, device, consensus_stepsize=0.5):
+def build(rank, world, comm_op, batch_size, device, consensus_stepsize=0.5, model_name="resnet20"):
+    """Reference model + optimizer + metrics for one of the benchmark workloads:
+    ``resnet20`` (CIFAR shapes, fp32), ``resnet50`` (ImageNet shapes; the caller runs it under bf16
+    autocast) or ``lstm`` (2 x 650 tied-weight language model, vocabulary 33 278, clip 0.4)."""
     if REF not in sys.path:
         sys.path.insert(0, REF)
     install_bit2byte_shim()
@@ -123,22 +127,31 @@ def build(rank, world, comm_op, batch_size, device, consensus_stepsize=0.5):
         communication.dist = BatchedP2P(dist)
 
     topo = "ring" if world > 2 else "complete"
+    is_lm = model_name == "lstm"
     conf = argparse.Namespace(
-        arch="resnet20", data="cifar10", optimizer="parallel_choco_v", comm_op=comm_op,
+        arch={"resnet20": "resnet20", "resnet50": "resnet50", "lstm": "rnn_lm"}[model_name],
+        data="imagenet" if model_name == "resnet50" else "cifar10", optimizer="parallel_choco_v", comm_op=comm_op,
         compress_ratio=0.99, quantize_level=4, is_biased=True, backend="nccl", use_ipc=False,
-        consensus_stepsize=consensus_stepsize, comm_device="cuda", weight_decay=1e-4, lr=0.1, momentum_factor=0.9,
-        use_nesterov=True, epoch_=0.5, local_index=0, distributed=True, graph_topology=topo,
+        consensus_stepsize=consensus_stepsize, comm_device="cuda",
+        weight_decay=0.0 if is_lm else 1e-4, lr=2.5 if is_lm else 0.1, momentum_factor=0.0 if is_lm else 0.9,
+        use_nesterov=not is_lm, epoch_=0.5, local_index=0, distributed=True, graph_topology=topo,
         n_mpi_process=world, n_sub_process=1, on_cuda=True, batch_size=batch_size,
+        rnn_clip=0.4, n_tokens=33278,
     )
     conf.graph = topology.define_graph_topology(
         topo, world=",".join(["0"] * world), n_mpi_process=world, n_sub_process=1, comm_device="cuda",
         on_cuda=True, rank=rank,
     )
     torch.manual_seed(6)
-    model = models.resnet(conf).to(device)
+    if is_lm:
+        model = models.RNNLM(ntoken=conf.n_tokens, ninp=650, nhid=650, nlayers=2, tie_weights=True, dropout=0.4,
+                             weight_norm=False).to(device)
+    else:
+        model = models.resnet(conf).to(device)
     optimizer = create_optimizer.define_optimizer(conf, model)
-    metrics = create_metrics.Metrics(model, task="classification")
-    metrics.metrics_fn = _accuracy_with_reshape(metrics)
+    metrics = create_metrics.Metrics(model, task="language_modeling" if is_lm else "classification")
+    if not is_lm:
+        metrics.metrics_fn = _accuracy_with_reshape(metrics)
     timer = Timer(verbosity_level=0, on_cuda=True)
     criterion = torch.nn.CrossEntropyLoss(reduction="mean")
     return conf, model, optimizer, metrics, timer, criterion
@@ -170,17 +183,46 @@ def finish(state):
     torch.cuda.synchronize()
 
 
-def train_iteration(conf, model, optimizer, metrics, timer, criterion, inp_host, tgt_host, step):
-    """One iteration of the reference's CV loop."""
+def train_iteration(conf, model, optimizer, metrics, timer, criterion, inp_host, tgt_host, step, amp_dtype=None):
+    """One iteration of the reference's CV loop (``amp_dtype``: forward under autocast, which the
+    reference, written for PyTorch 1.3, does not have; used for the bf16 ResNet-50 workload so that
+    both arms compute in the same precision)."""
     model.train()
     conf.local_index = step + 1
     conf.epoch_ = (step + 1) / 391.0
     _input, _target = inp_host.cuda(non_blocking=True), tgt_host.cuda(non_blocking=True)
     optimizer.zero_grad()
-    output = model(_input)
+    if amp_dtype is not None:
+        with torch.autocast("cuda", dtype=amp_dtype):
+            output = model(_input)
+        output = output.float()
+    else:
+        output = model(_input)
     loss = criterion(output, _target)
     perf = metrics.evaluate(loss, output, _target)  # .item() per metric, as in the reference
     loss_v = loss.item()
     loss.backward()
     optimizer.step(timer=timer, scheduler=None)
     return loss_v, perf
+
+
+def train_iteration_lm(conf, model, optimizer, metrics, timer, criterion, inp_host, tgt_host, step, hidden):
+    """One iteration of the reference's language-model loop
+    (``dl_code/pcode/distributed_running_nlp.py:41-97,132-139``): detach the carried hidden state,
+    host->device copy, zero_grad, forward, loss over the flattened logits, perplexity metric and
+    ``loss.item()`` (host synchronisations, as there), backward, ``clip_grad_norm_``, ``optimizer.step``.
+    Returns ``(loss value, new hidden state)``."""
+    model.train()
+    conf.local_index = step + 1
+    conf.epoch_ = (step + 1) / 100.0
+    hidden = model.repackage_hidden(hidden)
+    _input, _target = inp_host.cuda(non_blocking=True), tgt_host.cuda(non_blocking=True)
+    optimizer.zero_grad()
+    output, hidden = model(_input, hidden)
+    loss = criterion(output.view(-1, conf.n_tokens), _target.contiguous().view(-1))
+    metrics.evaluate(loss, output, _target)   # exp(loss): reads the loss on the host
+    loss_v = loss.item()
+    loss.backward()
+    torch.nn.utils.clip_grad_norm_(model.parameters(), conf.rnn_clip)
+    optimizer.step(timer=timer)
+    return loss_v, hidden

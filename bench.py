@@ -3,6 +3,8 @@ CHOCO-SGD on a ring, images/s over all GPUs.
 
     python bench.py --gpus N --steps K --warmup W            # this framework
     python bench.py --impl reference --gpus N ...             # the unmodified reference
+    python bench.py --model lstm ...                          # 2 x 650 LSTM language model, CHOCO + QSGD, tokens/s
+    python bench.py --model resnet50 ...                      # ResNet-50 224 x 224, bf16 autocast, CHOCO + sign
 
 For N > 1 launch one rank per GPU with ``python -m torch.distributed.run``.  Rank 0 prints
 one JSON line.  Synthetic data (N(0,1) images, uniform labels), random-init weights.
@@ -23,14 +25,32 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-BATCH = 128
 # consensus step sizes inside the reference's tuning range [0.01, 0.5]; top-/random-1 % needs a small
 # one (chocosgd_b200.tools.tune_consensus_stepsize: 0.012 - 0.04 on rings of 2 - 8 nodes)
 GAMMA = {"compress_top_k": 0.02, "compress_random_k": 0.01, "sign": 0.45, "quantize_qsgd": 0.3}
-N_HOST_BATCHES = 16
 QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+# The workloads of the benchmark configurations: the headline (ResNet-20, default), the LSTM language
+# model and ResNet-50.  Each arm builds the same model family, optimizer and batch shapes.
+WORKLOADS = {
+    "resnet20": dict(
+        metric="ResNet-20 CHOCO-ring images/s", unit="images/s", batch=128, items_per_sample=1, comm_op="compress_top_k",
+        n_host_batches=16, dtype="fp32 (TF32 tensor-core convolutions, torch default)",
+        data="synthetic N(0,1) 32x32x3 images, uniform labels, random-init weights",
+        l2="per-step working set (activations + gradients, ~0.3 GB) exceeds the 126 MB L2"),
+    "lstm": dict(
+        metric="LSTM-2x650 CHOCO-ring tokens/s", unit="tokens/s", batch=32, items_per_sample=35, comm_op="quantize_qsgd",
+        n_host_batches=8, dtype="fp32 (strict fp32 linear layers, torch default; cuDNN LSTM GEMMs TF32 in both arms)",
+        data="synthetic uniform token ids over a 33278-word vocabulary, random-init weights",
+        l2="per-step working set (28 M parameters x 5 state vectors + 149 MB of logits) exceeds the 126 MB L2"),
+    "resnet50": dict(
+        metric="ResNet-50 CHOCO-ring images/s", unit="images/s", batch=128, items_per_sample=1, comm_op="sign",
+        n_host_batches=4, dtype="bf16 autocast (fp32 master weights and optimizer state)",
+        data="synthetic N(0,1) 224x224x3 images, uniform labels over 1000 classes, random-init weights",
+        l2="activations of one step (several GB) exceed the 126 MB L2"),
+}
 
 
 def parse():
@@ -39,11 +59,16 @@ def parse():
     p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=20)
     p.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    p.add_argument("--comm_op", default="compress_top_k",
+    p.add_argument("--model", default="resnet20", choices=tuple(WORKLOADS))
+    p.add_argument("--comm_op", default=None,
                    choices=("compress_top_k", "sign", "quantize_qsgd", "compress_random_k"))
     p.add_argument("--no_graph", action="store_true")
     p.add_argument("--native_layers", default="auto", choices=("auto", "all", "on", "off", "bn", "conv"))
-    return p.parse_args()
+    a = p.parse_args()
+    a.wl = WORKLOADS[a.model]
+    if a.comm_op is None:
+        a.comm_op = a.wl["comm_op"]
+    return a
 
 
 class ClockSampler:
@@ -133,10 +158,18 @@ def init_dist(n):
     return rank, world, local
 
 
-def host_batches(rank):
+def host_batches(rank, model):
+    """Pinned host batches of the workload's shape (the end-to-end region copies one per step)."""
+    wl = WORKLOADS[model]
     g = torch.Generator().manual_seed(1000 + rank)
-    xs = [torch.randn(BATCH, 3, 32, 32, generator=g).pin_memory() for _ in range(N_HOST_BATCHES)]
-    ys = [torch.randint(0, 10, (BATCH,), generator=g).pin_memory() for _ in range(N_HOST_BATCHES)]
+    n, b = wl["n_host_batches"], wl["batch"]
+    if model == "lstm":
+        xs = [torch.randint(0, 33278, (35, b), generator=g).pin_memory() for _ in range(n)]
+        ys = [torch.randint(0, 33278, (35, b), generator=g).pin_memory() for _ in range(n)]
+        return xs, ys
+    hw, classes = (224, 1000) if model == "resnet50" else (32, 10)
+    xs = [torch.randn(b, 3, hw, hw, generator=g).pin_memory() for _ in range(n)]
+    ys = [torch.randint(0, classes, (b,), generator=g).pin_memory() for _ in range(n)]
     return xs, ys
 
 
@@ -207,10 +240,16 @@ def run_ours(args, rank, world, local):
     from chocosgd_b200.ops import nn as native_nn
 
     device = torch.device("cuda", local)
-    argv = ["--arch", "resnet20", "--data", "cifar10", "--optimizer", "parallel_choco_v", "--comm_op", args.comm_op,
-            "--graph_topology", "ring", "--n_mpi_process", str(world), "--lr", "0.1", "--momentum_factor", "0.9",
-            "--use_nesterov", "True", "--weight_decay", "1e-4", "--consensus_stepsize", str(GAMMA[args.comm_op]),
-            "--batch_size", str(BATCH), "--gossip_impl", "fused"]
+    wl, batch = args.wl, args.wl["batch"]
+    argv = ["--optimizer", "parallel_choco_v", "--comm_op", args.comm_op, "--graph_topology", "ring",
+            "--n_mpi_process", str(world), "--consensus_stepsize", str(GAMMA[args.comm_op]),
+            "--batch_size", str(batch), "--gossip_impl", "fused"]
+    if args.model == "lstm":
+        argv += ["--arch", "rnn_lm", "--lr", "2.5", "--momentum_factor", "0.0", "--weight_decay", "0",
+                 "--rnn_n_hidden", "650", "--rnn_n_layers", "2", "--drop_rate", "0.4", "--rnn_clip", "0.4"]
+    else:
+        argv += ["--arch", args.model, "--data", "imagenet" if args.model == "resnet50" else "cifar10", "--lr", "0.1",
+                 "--momentum_factor", "0.9", "--use_nesterov", "True", "--weight_decay", "1e-4"]
     if "compress" in args.comm_op:
         argv += ["--compress_ratio", "0.99"]
     if args.comm_op == "quantize_qsgd":
@@ -220,21 +259,30 @@ def run_ours(args, rank, world, local):
     torch.manual_seed(6)
     torch.backends.cudnn.benchmark = True
     native_nn.configure_native("auto" if args.native_layers == "on" else args.native_layers)
-    model = define_model(conf, graph, device=device, verbose=False)
+    loader = {"n_tokens": 33278} if args.model == "lstm" else None
+    model = define_model(conf, graph, data_loader=loader, device=device, verbose=False)
     optimizer = define_optimizer(conf, model, graph)
-    metrics = Metrics(model)
     criterion = torch.nn.CrossEntropyLoss()
-    xs, ys = host_batches(rank)
-    step = TrainStep(model, criterion, optimizer, xs[0], ys[0], metrics=metrics, use_cuda_graph=not args.no_graph)
+    xs, ys = host_batches(rank, args.model)
+    nb = len(xs)
+    kw = {}
+    if args.model == "lstm":
+        kw = dict(metrics=Metrics(model, "language_modeling"), clip_grad_norm=conf.rnn_clip,
+                  hidden=tuple(h.to(device) for h in model.init_hidden(batch)))
+    elif args.model == "resnet50":
+        kw = dict(metrics=Metrics(model), amp_dtype=torch.bfloat16)
+    else:
+        kw = dict(metrics=Metrics(model))
+    step = TrainStep(model, criterion, optimizer, xs[0], ys[0], use_cuda_graph=not args.no_graph, **kw)
     model.train()
     loss_host = torch.zeros(args.steps + args.warmup + 8, dtype=torch.float32).pin_memory()
 
     # warm-up: graph capture + W untimed steps through the public call
     sampler = ClockSampler(rank == 0, local)
     for i in range(max(args.warmup, 3)):
-        step(xs[i % N_HOST_BATCHES], ys[i % N_HOST_BATCHES])
+        step(xs[i % nb], ys[i % nb])
     torch.cuda.synchronize()
-    optimizer.engine.check()
+    optimizer.check()
     sampler.mark()
 
     # (1) device-timed steps: the batch is already in the static device buffers
@@ -242,14 +290,14 @@ def run_ours(args, rank, world, local):
 
     # (2) end to end through the public API: pinned host batch -> device, step, loss -> host
     def e2e(i):
-        loss = step(xs[i % N_HOST_BATCHES], ys[i % N_HOST_BATCHES])
+        loss = step(xs[i % nb], ys[i % nb])
         loss_host[i:i + 1].copy_(loss.reshape(1), non_blocking=True)
 
     e2e_ms = timed(e2e, args.steps, world)
     keep_load_until_sampled(sampler, lambda i: step(), world)
     clocks = sampler.stop()
     optimizer.finalize()
-    optimizer.engine.check()
+    optimizer.check()
     losses = loss_host[:args.steps]
     assert torch.isfinite(losses).all(), "training diverged"
     # kernels of the native library per step: counted by the Python wrappers while the step was
@@ -273,12 +321,20 @@ def run_reference(args, rank, world, local):
         os.environ.setdefault("MASTER_PORT", "29511")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
     torch.backends.cudnn.benchmark = True
-    state = ref.build(rank, world, args.comm_op, BATCH, device, GAMMA[args.comm_op])
-    xs, ys = host_batches(rank)
+    batch = args.wl["batch"]
+    state = ref.build(rank, world, args.comm_op, batch, device, GAMMA[args.comm_op], model_name=args.model)
+    xs, ys = host_batches(rank, args.model)
+    nb = len(xs)
     out = {}
+    if args.model == "lstm":
+        out["hidden"] = state[1].init_hidden(batch)
 
     def it(i):
-        out["loss"], _ = ref.train_iteration(*state, xs[i % N_HOST_BATCHES], ys[i % N_HOST_BATCHES], it.n)
+        if args.model == "lstm":
+            out["loss"], out["hidden"] = ref.train_iteration_lm(*state, xs[i % nb], ys[i % nb], it.n, out["hidden"])
+        else:
+            out["loss"], _ = ref.train_iteration(*state, xs[i % nb], ys[i % nb], it.n,
+                                                 amp_dtype=torch.bfloat16 if args.model == "resnet50" else None)
         it.n += 1
 
     it.n = 0
@@ -291,7 +347,8 @@ def run_reference(args, rank, world, local):
     keep_load_until_sampled(sampler, it, world, quiesce=lambda: ref.finish(state))
     clocks = sampler.stop()
     ref.finish(state)
-    return ms, ms, clocks, 0, out["loss"], BATCH * 3 * 32 * 32 * 4 + BATCH * 8, {}
+    h2d = xs[0].numel() * xs[0].element_size() + ys[0].numel() * ys[0].element_size()
+    return ms, ms, clocks, 0, out["loss"], h2d, {}
 
 
 _JSON_OUT = None
@@ -331,21 +388,30 @@ def main():
         res = run_ours(args, rank, world, local)
     dev_ms, e2e_ms, clocks, launches, last_loss, h2d, extra = res
     if rank == 0:
-        imgs = BATCH * world * args.steps
+        wl = args.wl
+        items = wl["batch"] * wl["items_per_sample"] * world * args.steps
+        config = {"model": {"resnet20": "resnet20", "resnet50": "resnet50", "lstm": "lstm-2x650-tied"}[args.model],
+                  "global_batch": wl["batch"] * world, "seq_len": 35 if args.model == "lstm" else None,
+                  "parallelism": f"gossip-dp{world} ring", "optimizer": "CHOCO-SGD", "comm_op": args.comm_op,
+                  "consensus_stepsize": GAMMA[args.comm_op], "l2": wl["l2"]}
+        if "compress" in args.comm_op:
+            config["compress_ratio"] = 0.99
+        if args.comm_op == "quantize_qsgd":
+            config["quantize_level"] = 4
+        if args.model == "lstm":
+            config.update({"momentum": 0.0, "weight_decay": 0.0, "grad_clip": 0.4, "dropout": 0.4, "vocab": 33278})
+        else:
+            config.update({"nesterov": 0.9, "weight_decay": 1e-4})
         line = {
-            "metric": "ResNet-20 CHOCO-ring images/s", "value": imgs / (dev_ms * 1e-3), "unit": "images/s",
+            "metric": wl["metric"], "value": items / (dev_ms * 1e-3), "unit": wl["unit"],
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "fp32 (TF32 tensor-core convolutions, torch default)",
-            "data": "synthetic N(0,1) 32x32x3 images, uniform labels, random-init weights",
+            "vs_baseline": None, "dtype": wl["dtype"], "data": wl["data"],
             "impl": args.impl,
-            "config": {"model": "resnet20", "global_batch": BATCH * world, "seq_len": None,
-                       "parallelism": f"gossip-dp{world} ring", "optimizer": "CHOCO-SGD", "comm_op": args.comm_op,
-                       "compress_ratio": 0.99, "consensus_stepsize": GAMMA[args.comm_op], "nesterov": 0.9, "weight_decay": 1e-4,
-                       "l2": "per-step working set (activations + gradients, ~0.3 GB) exceeds the 126 MB L2"},
+            "config": config,
             "impl_detail": extra,
             "clocks": clocks,
-            "e2e": {"value": imgs / (e2e_ms * 1e-3), "unit": "images/s", "h2d_bytes_per_step": h2d,
+            "e2e": {"value": items / (e2e_ms * 1e-3), "unit": wl["unit"], "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches,
             "last_loss": last_loss,

@@ -95,6 +95,8 @@ class RunState:
     init_warmup_lr: Optional[float] = None
     is_centralized: bool = False
     distributed: bool = True
+    group: Any = None          # process group of the ranks currently in the run (None: the default group)
+    membership: Any = None     # parallel.elastic.Membership when --elastic
     extras: dict = field(default_factory=dict)
 
 
@@ -252,6 +254,14 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--steps", default=None, type=int, help="stop after this many local steps")
     p.add_argument("--wait_budget_ms", default=2000.0, type=float,
                    help="upper bound of every in-kernel wait on a peer flag")
+    p.add_argument("--elastic", default=False, type=str2bool,
+                   help="keep training on the survivors when a rank leaves or goes silent (heartbeat through the "
+                   "rendezvous store, survivor graph with Metropolis weights)")
+    p.add_argument("--heartbeat_every", default=50, type=int, help="steps between two membership checks")
+    p.add_argument("--heartbeat_stale_s", default=30.0, type=float,
+                   help="a rank whose heartbeat has not advanced for this long counts as lost")
+    p.add_argument("--leave_at_step", default=None, type=str,
+                   help="rank:step - that rank announces an orderly exit before that step (tests of --elastic)")
     p.add_argument("--synthetic_size", default=None, type=int,
                    help="number of samples of the synthetic dataset (data=synthetic_*)")
     p.add_argument("--use_cuda_graph", default=True, type=str2bool)

@@ -46,7 +46,7 @@ struct AlgoParams {
   float inv_world;                  // 1 / n (DGC, EF-signSGD)
   int mask_momentum;                // DGC: zero the momentum at the selected coordinates
   int use_memory;                   // DGC keeps no memory with a quantizer
-  int pad_;
+  int t_offset;                     // ECD-PSGD: its step index t is (pushes completed - t_offset)
 };
 
 extern "C" int algo_params_size() { return (int)sizeof(AlgoParams); }
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) algo_prep_kernel(const ChocoPar
   const float gscale = p.hyper[HYP_GSCALE];
   const bool mom_init = p.step[1] != 0;
   const float wd = tb.seg_wd[seg];
-  const float tt = (float)(t + 1);  // 1-based step index of ECD-PSGD
+  const float tt = (float)((int)t + 1 - a.t_offset);  // 1-based step index of ECD-PSGD
   const bool pushes = codec == CODEC_SIGN || codec == CODEC_RAW;
 
   if (codec == CODEC_TOPK) {
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) algo_apply_dense_kernel(const C
   if (!sh_flag) return;
 
   const float lr = p.hyper[HYP_LR], gamma = p.hyper[HYP_GAMMA];
-  const float tt = (float)T, ea = 1.f - 2.f / tt, eb = 2.f / tt;
+  const float tt = (float)((int)T - a.t_offset), ea = 1.f - 2.f / tt, eb = 2.f / tt;
   const uint32_t* own = p.outbox + par * PW;
   float unit_own = 0.f;
   if (codec == CODEC_SIGN) unit_own = __uint_as_float(__ldcg(own + seg)) / (float)seg_n;
@@ -396,7 +396,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) algo_apply_sparse_kernel(const 
   const int src_rank = src < 0 ? p.rank : p.peer_rank[src];
   const uint32_t seed = p.seed - 7919u * (uint32_t)p.rank + 7919u * (uint32_t)src_rank;
   const float lr = p.hyper[HYP_LR], gamma = p.hyper[HYP_GAMMA];
-  const float tt = (float)T, ea = 1.f - 2.f / tt, eb = 2.f / tt;
+  const float tt = (float)((int)T - a.t_offset), ea = 1.f - 2.f / tt, eb = 2.f / tt;
   for (int e = blockIdx.x * CHOCO_THREADS + threadIdx.x; e < sum_k; e += gridDim.x * CHOCO_THREADS) {
     const int seg = algo_segment_of_entry(tb, e);
     uint32_t idx;

@@ -9,7 +9,13 @@
 //     memory (so completion stays transitive along the stream);
 //   * nothing is written to global memory before pdl_wait().
 // Inside a captured CUDA graph the attribute becomes a programmatic dependency edge.  Without the
-// attribute (CHOCO_PDL=0, or a launch by plain <<<>>>) both calls are no-ops.
+// attribute (the default, or a launch by plain <<<>>>) both calls are no-ops.
+//
+// Off by default (CHOCO_PDL=1 switches it on): measured on B200 inside the captured ResNet-20 training
+// step (about 180 kernels of 3 - 10 us), programmatic edges made the step slower, 1.30 ms against
+// 1.25 ms with plain edges (1.34 ms when the trigger precedes the wait and several kernels of the
+// chain become resident at once); a graph's kernel-to-kernel hand-over is already cheaper than the
+// bookkeeping of the early launch at this kernel size.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdlib.h>
@@ -24,7 +30,7 @@ static inline bool pdl_enabled() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("CHOCO_PDL");
-    v = (e == nullptr || atoi(e) != 0) ? 1 : 0;
+    v = (e != nullptr && atoi(e) != 0) ? 1 : 0;
   }
   return v != 0;
 }

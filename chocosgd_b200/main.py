@@ -82,12 +82,20 @@ def main(conf):
         metrics = Metrics(model, task="classification")
         best = BestPerf(best_perf=run.best_perf, larger_is_better=True)
     scheduler.set_best_tracker(best)
+    if conf.elastic and world > 1:
+        import torch.distributed as dist
+
+        from .parallel.elastic import Membership
+
+        run.membership = Membership(dist.distributed_c10d._get_default_store(), rank, list(range(world)),
+                                    stale_after_s=conf.heartbeat_stale_s)
     ckpt.save_arguments(conf, graph, run)
     try:
         train_and_validate(conf, graph, run, model, criterion, scheduler, optimizer, metrics, data_loader, device)
     finally:
         run.logger.save_json()
-    bootstrap.shutdown()
+    # after a membership change the default group still counts the rank that left: no collective on it
+    bootstrap.shutdown(collective=run.extras.get("lost_ranks") is None)
     return run, scheduler
 
 

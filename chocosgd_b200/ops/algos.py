@@ -40,7 +40,7 @@ class AlgoParamsC(ctypes.Structure):
         ("inv_world", ctypes.c_float),
         ("mask_momentum", ctypes.c_int),
         ("use_memory", ctypes.c_int),
-        ("pad_", ctypes.c_int),
+        ("t_offset", ctypes.c_int),
     ]
 
 
@@ -113,6 +113,15 @@ class AlgoEngine(ChocoEngine):
         self._steps += 1
         self.launches_per_step = self._n_launch
 
+    def rebase_time(self):
+        """Make the current device step count the origin of the algorithm's own step index (ECD-PSGD
+        weights its updates by t): used after warm-up steps whose effects were rolled back."""
+        now = self.step_index()
+        for c in self._algo_structs:
+            c.t_offset = int(now)
+        raw = np.frombuffer(b"".join(bytes(c) for c in self._algo_structs), dtype=np.uint8).copy()
+        self.algo_params.copy_(torch.from_numpy(raw))
+
     def launch_decode(self, stream=None):
         return None  # the exchange of a step is applied inside the step
 
@@ -120,10 +129,15 @@ class AlgoEngine(ChocoEngine):
         self.check()
 
     def reset_step(self, step: int):
+        """After loading a checkpoint taken at algorithm step ``step``: the device counter keeps
+        counting pushes of this process (it pairs with the mailbox flags), the offset maps it back."""
+        now = self.step_index()
+        for c in self._algo_structs:
+            c.t_offset = int(now) - int(step)
+        raw = np.frombuffer(b"".join(bytes(c) for c in self._algo_structs), dtype=np.uint8).copy()
+        self.algo_params.copy_(torch.from_numpy(raw))
         for r in self.ranks:
-            st = self.per_rank[r]["step"]
-            st[0], st[2] = int(step), int(step)
-            st[1] = 1 if step > 0 else 0
+            self.per_rank[r]["step"][1] = 1 if step > 0 else 0
 
 
 class AlgoLoopbackWorld:

@@ -182,9 +182,16 @@ class ChocoEngine:
         T, nc, dev = seg.n_segments, self.tables.n_chunks, self.device
         z = lambda n, dt: torch.zeros(n, dtype=dt, device=dev)
         self.hyper = z(HYP_N, torch.float32)
-        self.hyper_host = torch.zeros(HYP_N, dtype=torch.float32)
+        # Staging for the hyper-parameter refresh: a ring of pinned slots, each guarded by an event
+        # recorded after its copy, so the host never rewrites a slot whose (asynchronous) copy has
+        # not run yet while it keeps enqueuing steps with a changing learning rate.
+        n_slots = 16 if dev.type == "cuda" else 1
+        self._hyper_ring = [torch.zeros(HYP_N, dtype=torch.float32) for _ in range(n_slots)]
         if dev.type == "cuda":
-            self.hyper_host = self.hyper_host.pin_memory()
+            self._hyper_ring = [t.pin_memory() for t in self._hyper_ring]
+        self._hyper_events = [None] * n_slots
+        self._hyper_slot = 0
+        self.hyper_host = self._hyper_ring[0]
         self.hyper_host[HYP_GSCALE] = 1.0
         self.hyper.copy_(self.hyper_host)
         self._hyper_sent = None
@@ -286,10 +293,17 @@ class ChocoEngine:
         key = (float(lr), float(momentum), float(gamma), bool(nesterov))
         if key == self._hyper_sent:
             return
-        h = self.hyper_host
+        i = self._hyper_slot = (self._hyper_slot + 1) % len(self._hyper_ring)
+        if self._hyper_events[i] is not None:
+            self._hyper_events[i].synchronize()  # the copy that last used this slot has completed
+        h = self.hyper_host = self._hyper_ring[i]
         h[HYP_LR], h[HYP_MOMENTUM], h[HYP_GAMMA], h[HYP_NESTEROV] = key[0], key[1], key[2], 1.0 if key[3] else 0.0
         # slots 0..3 only: slot 4 (gradient scale) is written by the clipping kernel
         self.hyper[:4].copy_(h[:4], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = self._hyper_events[i] or torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._hyper_events[i] = ev
         self._hyper_sent = key
 
     # ---- launches ---------------------------------------------------------------------------------
@@ -396,6 +410,16 @@ class ChocoEngine:
             st = self.per_rank[r]["step"]
             st[0], st[2] = int(step), int(step)
             st[1] = 1 if step > 0 else 0
+
+    def momentum_flags(self):
+        return [int(self.per_rank[r]["step"][1]) for r in self.ranks]
+
+    def set_momentum_flags(self, flags):
+        for r, f in zip(self.ranks, flags):
+            self.per_rank[r]["step"][1] = int(f)
+
+    def rebase_time(self):
+        """Hook for engines whose update rule depends on the step index (see ``AlgoEngine``)."""
 
     def check(self):
         """Read the status words (synchronises); raise on a timed-out wait."""

@@ -55,9 +55,20 @@ def init_distributed_world(conf, timeout_s: float = 120.0) -> tuple:
     return rank, n
 
 
-def shutdown():
+def shutdown(collective: bool = True):
+    """Tear the process group down.  ``collective=False``: the default group still counts a rank that
+    is gone (an elastic run after a membership change), so nothing that waits for all of its ranks may
+    run; the groups are dropped without a closing hand-shake."""
     if dist.is_available() and dist.is_initialized():
-        dist.destroy_process_group()
+        if collective:
+            dist.destroy_process_group()
+        else:
+            try:
+                if torch.cuda.is_available():
+                    torch.cuda.synchronize()
+                dist.destroy_process_group()
+            except Exception as e:  # a teardown that cannot complete must not fail a finished run
+                print(f"[bootstrap] teardown without all ranks: {e!r}")
 
 
 def heartbeat_check(store, rank: int, world_size: int, step: int, max_lag: int = 1_000_000, prefix: str = "hb"):

@@ -161,8 +161,10 @@ class DecentralizedAggregation(Aggregation):
         for r in self.neighbor_ranks:
             local[r] = torch.empty_like(data)
         for r in self.neighbor_ranks:
-            ops.append(dist.P2POp(dist.isend, data, r, group=self.group))
-            ops.append(dist.P2POp(dist.irecv, local[r], r, group=self.group))
+            # graph ranks index the members of ``group``; point-to-point calls address global ranks
+            peer = dist.get_global_rank(self.group, r) if self.group is not None else r
+            ops.append(dist.P2POp(dist.isend, data, peer, group=self.group))
+            ops.append(dist.P2POp(dist.irecv, local[r], peer, group=self.group))
         reqs = dist.batch_isend_irecv(ops)
         return _Pending(reqs, local)
 

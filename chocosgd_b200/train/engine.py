@@ -128,19 +128,65 @@ class TrainStep:
                     self.perf.copy_(torch.stack([p.float() for p in perf]))
         return loss
 
+    # ---- side-effect-free warm-up --------------------------------------------------------------
+    def _snapshot(self):
+        """Everything the warm-up steps change: parameters, momentum, the algorithm's state tensors,
+        module buffers (batch-norm statistics and counters), the recurrent state, host counters."""
+        opt = self.opt
+        algo = {k: v.clone() for k, v in opt.algo_state().items() if torch.is_tensor(v)}
+        return {
+            "x": opt.arena.x.clone(),
+            "m": None if opt.momentum_buf is None else opt.momentum_buf.clone(),
+            "algo": algo,
+            "buffers": [b.clone() for b in self.model.buffers()],
+            "hidden": None if self.hidden is None else [h.clone() for h in self.hidden],
+            "local_index": opt.local_index, "n_bits": opt.n_bits,
+            "mom_flags": opt.engine.momentum_flags(),
+        }
+
+    def _restore(self, snap):
+        opt = self.opt
+        opt.finalize()                       # apply the exchange still in flight, then roll back
+        live = opt.algo_state()
+        with torch.no_grad():
+            opt.arena.x.copy_(snap["x"])
+            if snap["m"] is not None:
+                opt.momentum_buf.copy_(snap["m"])
+            elif opt.momentum_buf is not None:
+                opt.momentum_buf.zero_()
+            for k, v in snap["algo"].items():
+                live[k].copy_(v)
+            for b, v in zip(self.model.buffers(), snap["buffers"]):
+                b.copy_(v)
+            if snap["hidden"] is not None:
+                for h, v in zip(self.hidden, snap["hidden"]):
+                    h.copy_(v)
+        opt.local_index, opt.n_bits = snap["local_index"], snap["n_bits"]
+        opt.engine.set_momentum_flags(snap["mom_flags"])
+        opt.engine.rebase_time()
+
     def prime(self):
-        """Build the CUDA graph (runs ``warmup_iters`` + 1 real training steps on the data
-        currently in the static buffers)."""
+        """Build the CUDA graph.  The warm-up iterations that capture needs run as real steps on
+        the data currently in the static buffers, then every effect of theirs is rolled back
+        (parameters, momentum, x_hat / s / memories, batch-norm statistics, recurrent state), so
+        that the captured step replayed next is the first update of this batch: the graph path
+        and the eager path follow the same trajectory.  Only the device-resident exchange
+        counter keeps counting (it pairs with the mailbox flags of the neighbours, which ran the
+        same warm-up).  Returns 1, the number of training steps the call amounts to."""
         if not self.use_graph or self.graph is not None:
             return 0
+        snap = self._snapshot()
         # the table must exist (with its final address) before capture: create it from
         # placeholder gradients, capture, then point it at the captured gradients
         eng = self.opt.engine
         eng.set_grad_pointers(self.opt.rank, [torch.zeros_like(p) for p in self.opt.arena.params])
         table = eng._grad_tables[self.opt.rank][0]
         self._grad_ptrs_dirty = True
-        n = self._capture_with_table(table)
-        return n
+        self._capture_with_table(table)
+        self._restore(snap)
+        self.opt.prepare_step()
+        self.graph.replay()              # the first real step on this batch
+        return 1
 
     def _capture_with_table(self, table):
         eng = self.opt.engine
@@ -161,7 +207,6 @@ class TrainStep:
         for p in self.opt.arena.params:
             p.grad = None
         self.graph = torch.cuda.CUDAGraph()
-        self.opt.prepare_step()
         from ..ops import _lib
 
         n0 = _lib.LAUNCHES[0]
@@ -175,8 +220,7 @@ class TrainStep:
         self._captured_grads = [p.grad for p in self.opt.arena.params]
         self._fill_table(table)
         torch.cuda.synchronize()
-        self.graph.replay()  # the captured step has not run yet: run it once (prepare_step was accounted above)
-        return self._warmup_iters + 1
+        return self._warmup_iters
 
     def _fill_table(self, table):
         grads = [p.grad for p in self.opt.arena.params]

@@ -15,6 +15,7 @@ from __future__ import annotations
 import copy
 import gc
 import math
+import time
 
 import torch
 import torch.distributed as dist
@@ -28,9 +29,72 @@ from ..utils.stat_tracker import RuntimeTracker
 from .engine import TrainStep
 
 
-def _barrier():
+def _barrier(group=None):
     if dist.is_available() and dist.is_initialized():
-        dist.barrier()
+        dist.barrier(group=group)
+
+
+class _Elastic:
+    """Membership checks between training steps and the recovery after a rank was lost.
+
+    Every ``heartbeat_every`` steps (and whenever a bounded device-side wait ran out) the ranks
+    compare heartbeats; survivors agree on who is gone, form a new process group and graph, and
+    rebuild the optimizer's transports.  Nothing of this runs while a kernel or a collective of
+    this rank is in flight: the stream is synchronised first."""
+
+    def __init__(self, conf, run):
+        self.conf, self.run, self.m = conf, run, run.membership
+        self.leave_rank, self.leave_step = None, None
+        if conf.leave_at_step:
+            r, s = conf.leave_at_step.split(":")
+            self.leave_rank, self.leave_step = int(r), int(s)
+
+    def wants_to_leave(self, global_rank, step) -> bool:
+        return self.leave_rank == global_rank and step >= self.leave_step
+
+    def leave(self, optimizer):
+        optimizer.finalize()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.m.leave()
+
+    def lost_now(self, optimizer, step, force=False):
+        """-> global ranks lost, or [] (cheap: one store write; reads only at check points)."""
+        from ..utils.error_handler import GossipTimeout
+
+        self.m.beat(step)
+        timed_out = None
+        if force or step % max(1, self.conf.heartbeat_every) == 0:
+            try:
+                optimizer.check()
+            except GossipTimeout as e:
+                timed_out = e
+            lost = self.m.lost()
+            if timed_out is not None and not lost:
+                # a peer stopped publishing payloads: give its heartbeat the chance to go stale
+                deadline = time.time() + (self.m.stale_after_s or 5.0) + 1.0
+                while not lost and time.time() < deadline:
+                    time.sleep(0.1)
+                    lost = self.m.lost()
+                if not lost:
+                    raise timed_out
+            return lost
+        return []
+
+    def recover(self, seen_lost, graph, model, optimizer, scheduler):
+        from ..parallel.elastic import rebuild_optimizer
+
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        lost, resume_step = self.m.agree(seen_lost, scheduler.local_index)
+        scheduler.local_index = resume_step      # survivors noticed the loss at different steps
+        backend = dist.get_backend() if dist.is_initialized() else None
+        new_graph, group = self.m.regroup(graph, lost, backend=backend)
+        self.run.group, self.run.graph = group, new_graph
+        self.run.extras["lost_ranks"] = sorted(set(self.run.extras.get("lost_ranks", [])) | set(lost))
+        new_opt = rebuild_optimizer(self.conf, model, optimizer, new_graph, group)
+        self.run.logger.log(f"lost ranks {lost}: continuing on {new_graph.n_nodes} nodes as rank {new_graph.rank}")
+        return new_graph, new_opt
 
 
 class _PendingRecords:
@@ -144,10 +208,27 @@ def train_and_validate(conf, graph, run, model, criterion, scheduler, optimizer,
     pending = _PendingRecords()
     rank_slice = slice(graph.rank * conf.batch_size, (graph.rank + 1) * conf.batch_size) if is_nlp else None
     step_fn, hidden = None, None
+    step_cache = {}   # one TrainStep (one captured graph) per batch shape, reused across epochs
+    elastic = _Elastic(conf, run) if run.membership is not None else None
+    global_rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
     print("=> enter the training.\n")
     while True:
-        _barrier()
+        _barrier(run.group)
         for _input, _target in data_loader["train_loader"]:
+            if elastic is not None:
+                if elastic.wants_to_leave(global_rank, scheduler.local_index + 1):
+                    elastic.leave(optimizer)
+                    logger.save_json()
+                    run.extras["lost_ranks"] = [global_rank]
+                    return scheduler
+                seen = elastic.lost_now(optimizer, scheduler.local_index + 1)
+                if seen:
+                    pending.flush(logger, graph, tracker_tr, metrics.metric_names, False)
+                    graph, optimizer = elastic.recover(seen, graph, model, optimizer, scheduler)
+                    tracker_tr = RuntimeTracker(metrics.metric_names, on_cuda=graph.on_cuda,
+                                                world_aggregator=optimizer.world_aggregator)
+                    step_fn, step_cache = None, {}
+                    break   # all survivors restart the pass over their loaders together
             model.train()
             scheduler.step(optimizer)
             with timer("load_data", epoch=scheduler.epoch_):
@@ -155,10 +236,13 @@ def train_and_validate(conf, graph, run, model, criterion, scheduler, optimizer,
                     _input, _target = _input[:, rank_slice], _target[:, rank_slice]
                     if _input.size(0) != conf.rnn_bptt_len or _input.size(1) != conf.batch_size:
                         continue  # ragged tail window
-                if step_fn is None or tuple(step_fn.static_input.shape) != tuple(_input.shape):
+                shape_key = tuple(_input.shape)
+                if step_fn is None or tuple(step_fn.static_input.shape) != shape_key:
+                    step_fn = step_cache.get(shape_key)
+                if step_fn is None:
                     if is_nlp:
                         hidden = tuple(h.to(optimizer.device) for h in model.init_hidden(conf.batch_size))
-                    step_fn = TrainStep(
+                    step_fn = step_cache[shape_key] = TrainStep(
                         model, criterion, optimizer, _input, _target, metrics=metrics,
                         use_cuda_graph=conf.use_cuda_graph and _input.size(0) == (conf.rnn_bptt_len if is_nlp else conf.batch_size),
                         clip_grad_norm=conf.rnn_clip if is_nlp else None, hidden=hidden,
@@ -171,8 +255,8 @@ def train_and_validate(conf, graph, run, model, criterion, scheduler, optimizer,
                         loss, step_fn.perf)
             if scheduler.local_index % conf.summary_freq == 0 or scheduler.epoch_ % 1 == 0 or scheduler.is_stop():
                 pending.flush(logger, graph, tracker_tr, metrics.metric_names, False)
-                if getattr(optimizer, "engine", None) is not None:
-                    optimizer.engine.check()
+                if elastic is None:
+                    optimizer.check()   # a bounded device-side wait that ran out ends the run here
             if scheduler.epoch_ % 1 == 0 or scheduler.is_stop():
                 avg = tracker_tr.stat["loss"].avg
                 if avg > 1e3 or math.isnan(avg):

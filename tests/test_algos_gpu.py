@@ -126,3 +126,34 @@ def test_bitwise_reproducible():
     _, a, _ = _run("dcd_psgd", "compress_top_k", "ring", 4, compress_ratio=0.9)
     _, b, _ = _run("dcd_psgd", "compress_top_k", "ring", 4, compress_ratio=0.9)
     assert torch.equal(a.x, b.x)
+
+
+@pytest.mark.parametrize("algo,comm_op", [("deep_squeeze", "sign"), ("dcd_psgd", "compress_top_k"), ("dpsgd", "raw")])
+def test_blocking_exchange_times_out_without_hanging(algo, comm_op):
+    """A neighbour that never publishes: the bounded wait of the apply kernel runs out, the kernels
+    return, the optimizer-level ``check()`` raises ``GossipTimeout`` and the context stays usable."""
+    from chocosgd_b200.ops.algos import AlgoEngine
+    from chocosgd_b200.ops.gossip import RankBuffers
+    from chocosgd_b200.parallel.symm import LoopbackMailbox
+    from chocosgd_b200.utils.error_handler import GossipTimeout
+
+    seg = Segments.from_sizes([100, 40])
+    dev = torch.device("cuda")
+    mk = lambda: torch.zeros(seg.total, device=dev)
+    x = torch.ones(seg.total, device=dev)
+    dummy = torch.zeros(32, device=dev)
+    bufs = {0: RankBuffers(x, mk(), mk(), dummy, dummy)}
+    nbh = {0: {0: 0.5, 1: 0.5}}
+    hats = {0: {0: x.clone(), 1: x.clone()}} if "psgd" in algo and algo != "dpsgd" else None
+    mems = {0: mk()} if algo == "deep_squeeze" else None
+    kw = {"compress_ratio": 0.9} if "compress" in comm_op else {}
+    eng = AlgoEngine(algo, [0], bufs, nbh, seg, [0.0, 0.0], comm_op,
+                     lambda pw: LoopbackMailbox({0: [1], 1: [0]}, pw, dev), dev, hats=hats, mems=mems, n_world=2,
+                     wait_budget_ms=20.0, **kw)
+    eng.set_hyper(0.1, 0.0, 0.5, False)
+    eng.launch_step()  # waits for rank 1's payload of this step, which never comes
+    torch.cuda.synchronize()
+    with pytest.raises(GossipTimeout) as ei:
+        eng.check()
+    assert ei.value.peer == 1 and ei.value.step == 0
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0  # context still alive

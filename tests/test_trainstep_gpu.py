@@ -38,7 +38,7 @@ def _run_cv(impl, use_graph, comm_op, steps=6):
                      warmup_iters=1)
     model.train()
     losses = []
-    n_calls = steps - 1 if use_graph else steps  # the first graph call runs warm-up (1) + captured (1) steps
+    n_calls = steps  # the warm-up steps of the graph capture are rolled back: every call is one step
     torch.backends.cudnn.benchmark = False
     torch.backends.cudnn.deterministic = True
     for _ in range(n_calls):
@@ -88,7 +88,7 @@ def test_lstm_step_with_clipping_in_a_graph():
         step = TrainStep(model, torch.nn.CrossEntropyLoss(), opt, x, y, metrics=Metrics(model, "language_modeling"),
                          use_cuda_graph=use_graph, clip_grad_norm=0.4, hidden=hidden, warmup_iters=1)
         model.train()
-        n_calls = 5 if use_graph else 6
+        n_calls = 6  # graph capture leaves no trace: every call is one step
         losses = [float(step(x, y)) for _ in range(n_calls)]
         opt.finalize()
         opt.engine.check()
@@ -115,7 +115,7 @@ def test_native_layers_in_a_step_count_batches_and_join_the_side_stream():
             y = torch.randint(0, 10, (32,), generator=g).pin_memory()
             step = TrainStep(model, torch.nn.CrossEntropyLoss(), opt, x, y, use_cuda_graph=use_graph, warmup_iters=1)
             model.train()
-            n_calls = steps - 1 if use_graph else steps  # the first graph call runs warm-up + captured step
+            n_calls = steps  # graph capture leaves no trace: every call is one step
             losses = [float(step(x, y)) for _ in range(n_calls)]
             opt.finalize()
             opt.engine.check()
@@ -131,5 +131,5 @@ def test_native_layers_in_a_step_count_batches_and_join_the_side_stream():
     l_n, c_n, n_n, _ = run(True, True, 6)
     l_r, c_r, n_r, _ = run(False, False, 6)
     assert n_n == n_r == 6 and c_n == c_r and set(c_n) == {6}
-    assert abs(l_n[0] - l_r[1]) < 0.1 * abs(l_r[1])  # graph call 1 reports the loss of step 2
+    assert abs(l_n[0] - l_r[0]) < 0.02 * abs(l_r[0])  # same first step: the capture's warm-up left no trace
     assert l_n[-1] < l_n[0] and l_r[-1] < l_r[0]
