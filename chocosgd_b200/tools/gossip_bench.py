@@ -7,7 +7,16 @@ For every (size, codec) it prints one JSON line: microseconds per step (CUDA eve
 ranks), achieved local memory bandwidth, and the fraction of the roofline
 ``max(local bytes / HBM bandwidth, neighbour payload bytes / NVLink bandwidth)``.
 ``--impl torch`` times this framework's torch.distributed path (the same algorithm with
-library send/recv and PyTorch ops), the baseline the fused kernels are compared with."""
+library send/recv and PyTorch ops).  ``--impl reference`` times the reference's own gossip step:
+its ``ParallelCHOCO_V`` optimizer (``dl_code/pcode/optim/parallel_choco_v.py:104-155``: its
+compressors, its ``DecentralizedAggregation`` send / recv, its helper thread) from the install
+under ``baseline/_ref``, on a "model" that is one flat parameter of the same size with a zero
+gradient, so a step is its local update plus one full gossip exchange.
+
+Byte model of the roofline (what an ideal implementation must move per element, momentum off):
+x, g, x_hat, s read and x, x_hat, s written and g cleared (32 B); sign adds its payload bits;
+QSGD, top-k and random-k add one write and one read of the difference (the norm / the selection
+threshold must be known before the payload can be produced), QSGD also its payload bits."""
 from __future__ import annotations
 
 import argparse
@@ -41,8 +50,72 @@ def local_bytes_per_elem(comm_op, deg, nbits):
     if comm_op == "quantize_qsgd":
         return base + 8 + (nbits + 1) * (deg + 2) / 8.0
     if comm_op == "compress_top_k":
-        return base + 4 + 4 * 4  # scratch write + four selection passes over the scratch
-    return base + 4
+        return base + 8      # one write + one re-read of the difference; 1 % payloads are negligible
+    return base + 8
+
+
+def reference_step(rank, world, topology, comm_op, n, dev):
+    """One gossip step of the reference's own ``ParallelCHOCO_V`` on a flat parameter of ``n``
+    elements.  Harness glue as in ``baseline/reference_arm.py`` (pure-PyTorch ``bit2byte``, batched
+    NCCL send / recv, its ``complete`` graph where its ring refuses n <= 2)."""
+    import argparse as _ap
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path.insert(0, os.path.join(root, "baseline"))
+    import reference_arm as ref
+
+    if not ref.available():
+        raise SystemExit(json.dumps({"bench": "gossip", "impl": "reference",
+                                     "unavailable": "reference not installed under baseline/_ref"}))
+    if ref.REF not in sys.path:
+        sys.path.insert(0, ref.REF)
+    ref.install_bit2byte_shim()
+    import pcode.create_optimizer as create_optimizer
+    import pcode.utils.communication as communication
+    import pcode.utils.topology as topo_mod
+    from pcode.optim.utils import join_thread
+    from pcode.utils.timer import Timer
+
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29517")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    if not isinstance(communication.dist, ref.BatchedP2P):
+        communication.dist = ref.BatchedP2P(dist)
+    topo = topology if (world > 2 or topology == "complete") else "complete"
+    conf = _ap.Namespace(
+        arch="flat", optimizer="parallel_choco_v", comm_op=comm_op, compress_ratio=0.99, quantize_level=4,
+        is_biased=True, backend="nccl", use_ipc=False, consensus_stepsize=0.5, comm_device="cuda", weight_decay=0.0,
+        lr=0.0, momentum_factor=0.0, use_nesterov=False, epoch_=0.5, local_index=0, distributed=True,
+        graph_topology=topo, n_mpi_process=world, n_sub_process=1, on_cuda=True)
+    conf.graph = topo_mod.define_graph_topology(topo, world=",".join(["0"] * world), n_mpi_process=world,
+                                                n_sub_process=1, comm_device="cuda", on_cuda=True, rank=rank)
+
+    class Flat(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(rank)
+            self.weight = torch.nn.Parameter(torch.randn(n, device=dev))
+
+    model = Flat()
+    opt = create_optimizer.define_optimizer(conf, model)
+    timer = Timer(verbosity_level=0, on_cuda=True)
+    model.weight.grad = torch.zeros_like(model.weight)
+
+    def step():
+        opt.step(timer=timer, scheduler=None)
+
+    def join():
+        th = getattr(opt, "helper_thread", None)
+        if th is not None:
+            join_thread(th)
+        torch.cuda.synchronize()
+
+    k = max(1, int(n * 0.01))
+    payload = {"sign": 4 * ((n + 31) // 32 + 1), "quantize_qsgd": 4 * n, "compress_top_k": 8 * k,
+               "compress_random_k": 8 * k}[comm_op]
+    return step, {"join": join, "opt": opt, "model": model}, 4, payload
 
 
 def run(args):
@@ -65,7 +138,13 @@ def run(args):
             torch.manual_seed(rank)
             x = torch.randn(seg.total, device=dev)
             mk = lambda: torch.zeros(seg.total, device=dev)
-            if args.impl == "fused":
+            ref_state = None
+            if args.impl == "reference":
+                step, ref_state, nbits, payload_bytes = reference_step(rank, world, args.topology, comm_op, n, dev)
+                launches = None
+                del x
+                x = None
+            elif args.impl == "fused":
                 from ..ops.gossip import ChocoEngine, RankBuffers
                 from ..parallel.symm import DistributedMailbox, LoopbackMailbox
 
@@ -114,12 +193,16 @@ def run(args):
                 step = cg.replay
                 step()
                 torch.cuda.synchronize()
+            if ref_state is not None:
+                ref_state["join"]()
             if world > 1:
                 dist.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for _ in range(args.steps):
                 step()
+            if ref_state is not None:
+                ref_state["join"]()   # the exchange of the last step completes inside the timed region
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1)
@@ -146,7 +229,7 @@ def run(args):
                 if world > 1:
                     dist.barrier()
                 eng.close()
-            del x
+            del x, step, ref_state
             torch.cuda.empty_cache()
     if world > 1:
         dist.destroy_process_group()
@@ -157,7 +240,7 @@ def main(argv=None):
     p.add_argument("--sizes", default="1048576,16777216,134217728")
     p.add_argument("--comm_ops", default="sign,compress_top_k,compress_random_k,quantize_qsgd")
     p.add_argument("--topology", default="ring")
-    p.add_argument("--impl", default="fused", choices=("fused", "torch"))
+    p.add_argument("--impl", default="fused", choices=("fused", "torch", "reference"))
     p.add_argument("--steps", type=int, default=20)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--graph", type=int, default=1)

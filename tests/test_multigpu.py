@@ -189,4 +189,102 @@ def test_mailbox_transport_equals_library_transport(world):
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     for r in range(world):
         for name, (d, ref) in out[r].items():
-            assert d <= 1e-10 * ref + 1e-12, (name, d, ref)
+            # stochastic rounding levels can flip where s|v|/norm sits on a rounding boundary
+            tol = 1e-4 if name.startswith("ecd_psgd") else 1e-10
+            assert d <= tol * ref + 1e-12, (name, d, ref)
+
+
+def _worker_leave(rank, world, port, out):
+    """CHOCO-SGD (fused kernels) for three steps; the last rank then leaves between steps (nothing of
+    its own in flight, NVLS off, plain peer stores); the others notice it on the host, agree, rebuild
+    group / graph / optimizer and take three more steps."""
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from chocosgd_b200.optim import define_optimizer
+    from chocosgd_b200.parallel.elastic import Membership, rebuild_optimizer
+    from chocosgd_b200.parallel.topology import Graph
+
+    conf = conf_for("sign", world)
+    graph = Graph("ring", world, rank)
+    model = make_model().cuda()
+    opt = define_optimizer(conf, model, graph)
+    member = Membership(dist.distributed_c10d._get_default_store(), rank, list(range(world)), settle_s=0.2)
+    dist.barrier()
+    for t in range(3):
+        opt.arena.g.copy_(grad_flat(rank, t, opt.seg))
+        opt.step()
+        member.beat(t + 1)
+    opt.finalize()
+    torch.cuda.synchronize()
+    dist.barrier()          # every rank has applied the exchange of step 3: nothing is in flight
+    if rank == world - 1:
+        member.leave()
+        out[rank] = {"left": True}
+        os._exit(0)
+    import time
+
+    t0, lost = time.time(), []
+    while not lost and time.time() - t0 < 20:
+        time.sleep(0.05)
+        lost = member.lost()
+    lost, _ = member.agree(lost, step=3)
+    x_before = opt.arena.x.clone()
+    new_graph, group = member.regroup(graph, lost, backend="nccl")
+    opt = rebuild_optimizer(conf, model, opt, new_graph, group)
+    for t in range(3, 6):
+        opt.arena.g.copy_(grad_flat(rank, t, opt.seg))
+        opt.step()
+    opt.finalize()
+    torch.cuda.synchronize()
+    out[rank] = {"lost": lost, "n": new_graph.n_nodes, "x_before": x_before.cpu().numpy(),
+                 "x": opt.arena.x.cpu().numpy(), "m": opt.momentum_buf.cpu().numpy()}
+    os._exit(0)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_rank_leaves_between_steps_and_the_rest_continue(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+
+    from chocosgd_b200.compress.reference import make_codec
+    from chocosgd_b200.optim.arena import FlatArena
+    from chocosgd_b200.parallel.topology import Graph
+    from chocosgd_b200.sim.matrix_form import Simulator
+
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    port = free_port()
+    procs = [ctx.Process(target=_worker_leave, args=(r, world, port, out)) for r in range(world)]
+    [p.start() for p in procs]
+    [p.join(600) for p in procs]
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    res = dict(out)
+    assert res[world - 1] == {"left": True}
+    survivors = list(range(world - 1))
+    for r in survivors:
+        assert res[r]["lost"] == [world - 1] and res[r]["n"] == world - 1
+    # the survivors' three steps after the loss follow the CHOCO recurrence on the survivor graph,
+    # started from their parameters at the time of the loss with x_hat = s = 0 (momentum carried over)
+    conf = conf_for("sign", world)
+    arena = FlatArena(make_model().named_parameters())
+    seg = arena.seg
+    wd = [0.0 if "bn" in n else conf.weight_decay for n in seg.names]
+    codec = make_codec(seg, "sign", None, None, None, False, conf.random_k_seed)
+    w = Graph("ring", world, 0).without([world - 1]).matrix
+    x0 = torch.stack([torch.from_numpy(res[r]["x_before"]) for r in survivors])
+    # momentum at the time of the loss = momentum after three steps of the full ring: re-simulate those
+    full = Simulator("choco", Graph("ring", world, 0).matrix, arena.x.clone(), seg, codec, lr=conf.lr,
+                     consensus_stepsize=conf.consensus_stepsize, weight_decay=wd, momentum=0.9, nesterov=True)
+    for t in range(3):
+        full.step(lambda i, tt, x: grad_flat(i, tt, seg))
+    sim = Simulator("choco", w, x0, seg, codec, lr=conf.lr, consensus_stepsize=conf.consensus_stepsize,
+                    weight_decay=wd, momentum=0.9, nesterov=True, identical_init=False)
+    sim.local.buf = [full.local.buf[r].clone() for r in survivors]
+    for t in range(3, 6):
+        sim.step(lambda i, tt, x: grad_flat(survivors[i], tt, seg))
+    for i, r in enumerate(survivors):
+        np.testing.assert_allclose(res[r]["x"], sim.x[i].numpy(), rtol=1e-4, atol=1e-5, err_msg=f"rank {r}")
