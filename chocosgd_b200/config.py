@@ -358,3 +358,10 @@ def validate(conf: Config) -> None:
         raise ValueError("quantize_qsgd needs --quantize_level (bits) or --qsgd_levels (s)")
     if conf.use_nesterov and conf.momentum_factor <= 0:
         raise ValueError("Nesterov momentum requires a momentum")
+    if conf.n_sub_process > 1:
+        # The reference gives a graph node several GPUs by wrapping its model in torch.nn.DataParallel
+        # (dl_code/main.py:79-81): one process scattering batches and gathering gradients every step.
+        # Here every GPU is a process with its own flat arena, captured step and peer mailboxes; use
+        # n_mpi_process = number of GPUs (for 8 nodes x 4 GPUs: 32 ranks, e.g. on the torus graph).
+        raise ValueError("--n_sub_process > 1 is not supported: run one rank per GPU (raise --n_mpi_process and, "
+                         "to keep the global batch, leave --batch_size per GPU as it is)")

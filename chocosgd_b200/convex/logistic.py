@@ -338,9 +338,31 @@ class LogisticDecentralizedSGD:
         every = max(1, int(per / LOSS_PER_EPOCH))
         all_losses = np.zeros(int(per * p.num_epoch / every) + 1)
         t_start = time.time()
+        # hand-written path: the whole iteration (every node's stochastic gradient, the gossip step in
+        # matrix form and the column compressor) is ONE kernel launch
+        fused = None
+        if A32 is not None and p.estimate == "final" and not getattr(self, "force_torch_ops", False):
+            from ..ops.logreg import LogregIterator, iter_supported
+
+            if iter_supported(n, d):
+                fused = LogregIterator(A32, y32, W, x.t().contiguous(), p.method, p.quantization,
+                                       k=p.coordinates_to_keep, levels=p.num_levels, lam=lam,
+                                       gamma=p.consensus_lr or 0.0, seed=int(p.random_seed or 0))
         for epoch in range(p.num_epoch):
             rows_epoch = torch.as_tensor(
                 np.stack([[rs.choice(indices[m]) for m in range(n)] for _ in range(per)]), device=dev)
+            if fused is not None:
+                for it in range(per):
+                    t = epoch * per + it
+                    if t % every == 0:
+                        all_losses[t // every] = loss_of(fused.state[0].t())
+                    fused.step(rows_epoch[it], self.lr(epoch, it, per, d), t)
+                x, x_hat = fused.state[0].t(), fused.state[1].t()
+                x_est = x
+                losses[epoch + 1] = loss_of(x_est)
+                if not np.isfinite(losses[epoch + 1]):
+                    break
+                continue
             for it in range(per):
                 t = epoch * per + it
                 if t % every == 0:

@@ -533,6 +533,21 @@ extern "C" int bn_forward_partials(const BnArgs* args, int n_partials, cudaStrea
   return (int)cudaGetLastError();
 }
 
+// Backward when the producer of dy already masked it with the ReLU and left per-CTA rows of
+// (sum dy, sum dy * xhat) in args->partial (the input-gradient convolution's epilogue): one
+// elementwise kernel, no reduction pass; dgamma / dbeta are published by its first CTA.
+extern "C" int bn_backward_partials(const BnArgs* args, int n_partials, cudaStream_t st) {
+  BnArgs a = *args;
+  if (a.C % 4 != 0 || BN_THREADS % (a.C / 4) != 0 || a.C / 4 > BN_THREADS || a.C > BN_MAX_C) return -1;
+  if (n_partials < 1 || (long long)n_partials * 2 * a.C > BN_FUSED_LIMIT || a.partial == nullptr) return -2;
+  a.n_partials = n_partials;
+  a.fused_finalize = 1;
+  a.relu = 0;
+  a.out2 = nullptr;
+  launch_k(bn_bwd_apply_kernel, dim3(grid_for((long long)a.P * a.C / 4, a.fused_finalize)), dim3(BN_THREADS), 0, st, a);
+  return (int)cudaGetLastError();
+}
+
 static unsigned* g_bn_barrier[64];
 
 static unsigned* bn_barrier_words() {

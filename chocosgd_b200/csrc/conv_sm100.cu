@@ -146,6 +146,13 @@ conv3x3_tf32_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 struct ConvPArgs {
   float* y;        // [N*H*W, C_out]
   float* stats;    // optional [gridDim.x][2 C_out]: sum, sum of squares per channel
+  // backward epilogue (BWD kernels): result = (acc + add) * [mask > 0]; with bnx the two statistics
+  // become sum(result) and sum(result * (bnx - bn_mean) * bn_invstd), the batch-norm backward sums
+  const float* add;        // optional [N*H*W, C_out]
+  const float* mask;       // optional [N*H*W, C_out]
+  const float* bnx;        // optional [N*H*W, C_out]
+  const float* bn_mean;    // [C_out]
+  const float* bn_invstd;  // [C_out]
   int* error;
   int H, W, Cin;
   int TH, TN;
@@ -158,11 +165,12 @@ struct ConvPArgs {
 // slot, so a slot holds GK k-blocks (all 9 filter taps for 16 channels, 3 otherwise): one wait,
 // 2 GK .. 4 GK tensor-core instructions, one commit.  GK lanes of the producer warp issue the
 // loads of a slot in parallel.  As many slots as fit beside the epilogue tile in ~200 KB.
-template <int COUT, int KC>
+template <int COUT, int KC, bool BWD = false>
 struct ConvPCfg {
   static constexpr int TSTRIDE = COUT + 4;  // floats per row of the epilogue tile (bank-conflict free)
   static constexpr int KB_BYTES = 128 * KC * 4 + COUT * KC * 4;
-  static constexpr int ROOM = 200 * 1024 - 128 * TSTRIDE * 4;
+  static constexpr int TILES = 1;            // one shared tile for the epilogue (forward and backward form)
+  static constexpr int ROOM = 200 * 1024 - TILES * 128 * TSTRIDE * 4;
 #ifndef CONV_GK_MAX
 #define CONV_GK_MAX 9
 #endif
@@ -184,12 +192,13 @@ __device__ __forceinline__ bool epi_bar_or(bool flag) {
   return r != 0;
 }
 
-template <int COUT, int KC>
+template <int COUT, int KC, bool BWD>
 __global__ void __launch_bounds__(CONV_THREADS, 1)
 conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ConvPArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int S = ConvPCfg<COUT, KC>::STAGES, TS = ConvPCfg<COUT, KC>::TSTRIDE, GK = ConvPCfg<COUT, KC>::GK;
+  using Cfg = ConvPCfg<COUT, KC, BWD>;
+  constexpr int S = Cfg::STAGES, TS = Cfg::TSTRIDE, GK = Cfg::GK;
   constexpr int ROW = KC * 4;
   constexpr int A_BYTES = 128 * ROW;
   constexpr int B_BYTES = COUT * ROW;
@@ -198,7 +207,7 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   uint8_t* sA = smem;                          // [S][GK][A_BYTES]
   uint8_t* sB = smem + S * GK * A_BYTES;        // [S][GK][B_BYTES]
   float* sT = reinterpret_cast<float*>(sB + S * GK * B_BYTES);     // [128][TS] epilogue tile
-  uint64_t* full = reinterpret_cast<uint64_t*>(sT + 128 * TS);
+  uint64_t* full = reinterpret_cast<uint64_t*>(sT + Cfg::TILES * 128 * TS);
   uint64_t* empty = full + S;
   uint64_t* acc_full = empty + S;    // [2]
   uint64_t* acc_empty = acc_full + 2;  // [2]
@@ -287,66 +296,116 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     }
   } else if (warp < 4) {
     const int t128 = threadIdx.x;                 // 0..127
-    constexpr int NSEG = 128 / COUT > 0 ? 128 / COUT : 1;
-    const int sc = t128 % COUT, sseg = t128 / COUT;   // statistics: this thread's channel and pixel segment
-    float s0 = 0.f, s1 = 0.f;
+    // Epilogue in two steps.  (1) The accumulator goes TMEM -> registers -> shared tile, one pixel row
+    // per thread (padded rows: conflict-free).  (2) The 128 threads walk the tile linearly: a tile's 128
+    // pixels are consecutive rows of the [N H W, C_out] tensors, i.e. ONE contiguous block of memory, so
+    // every global load (skip gradient, ReLU mask, batch-norm input) and the store of the result is
+    // fully coalesced.  In that pass a thread always meets the same four channels, so the two
+    // per-channel statistics accumulate in registers across rows and tiles.
+    constexpr int C4 = COUT / 4;           // float4 columns of a row
+    constexpr int RSTEP = 128 / C4;        // rows covered by one sweep of the 128 threads
+    const int c4 = t128 % C4, r0 = t128 / C4;
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    float mu[4] = {0.f, 0.f, 0.f, 0.f}, is[4] = {0.f, 0.f, 0.f, 0.f};
+    if (BWD && g.bnx != nullptr) {
+      const float4 m4 = *reinterpret_cast<const float4*>(g.bn_mean + c4 * 4);
+      const float4 i4 = *reinterpret_cast<const float4*>(g.bn_invstd + c4 * 4);
+      mu[0] = m4.x; mu[1] = m4.y; mu[2] = m4.z; mu[3] = m4.w;
+      is[0] = i4.x; is[1] = i4.y; is[2] = i4.z; is[3] = i4.w;
+    }
     uint32_t lt = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < g.n_tiles; tile += gridDim.x, ++lt) {
       const uint32_t buf = lt & 1;
       const bool bad = !mbar_wait(acc_full + buf, (lt >> 1) & 1) || *abort_flag != 0;
       if (epi_bar_or(bad)) {                       // the same decision in all 128 epilogue threads
-        *abort_flag = 1;
+        *abort_flag = 1;                           // (also orders the previous tile's linear pass before this write)
         ok = false;
         break;
       }
       tc_fence_after();
       const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
-      const size_t pix = ((size_t)n0 * g.H + h0) * g.W + t128;
-      float* out = g.y + pix * COUT;
+      const size_t tile_off = (((size_t)n0 * g.H + h0) * g.W) * COUT;   // first float of the tile
       float* trow = sT + t128 * TS;
 #pragma unroll 1
       for (int c = 0; c < COUT; c += 16) {
         uint32_t v[16];
         tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * COUT + (uint32_t)c, v);
 #pragma unroll
-        for (int j = 0; j < 16; j += 4) {
-          float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
-                                 __uint_as_float(v[j + 3]));
-          if (g.relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
-          *reinterpret_cast<float4*>(out + c + j) = o;
-          if (g.stats != nullptr) *reinterpret_cast<float4*>(trow + c + j) = o;
-        }
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(trow + c + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                 __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
       }
       // the accumulator buffer may be overwritten by the tile after next
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + buf);
-      if (g.stats != nullptr) {
-        epi_bar();
-        if (sseg < NSEG) {
-          const float* col = sT + (size_t)(sseg * COUT) * TS + sc;
-#pragma unroll 8
-          for (int i = 0; i < COUT; ++i) {
-            const float x = col[(size_t)i * TS];
-            s0 += x;
-            s1 = fmaf(x, x, s1);
+      epi_bar();
+      const bool want_stats = g.stats != nullptr;
+      // four rows per trip: all their global loads are issued before the first use (the 128 epilogue
+      // threads of an SM are few, so the pass lives on memory-level parallelism)
+      constexpr int UN = (128 / RSTEP) >= 4 ? 4 : (128 / RSTEP);
+#pragma unroll 1
+      for (int rb = r0; rb < 128; rb += UN * RSTEP) {
+        float4 o[UN], ra[UN], rm[UN], rx[UN];
+        size_t off[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          const int row = rb + u * RSTEP;
+          off[u] = tile_off + (size_t)row * COUT + c4 * 4;
+          if (BWD) {
+            if (g.add != nullptr) ra[u] = __ldg(reinterpret_cast<const float4*>(g.add + off[u]));
+            if (g.mask != nullptr) rm[u] = __ldg(reinterpret_cast<const float4*>(g.mask + off[u]));
+            if (want_stats) rx[u] = __ldg(reinterpret_cast<const float4*>(g.bnx + off[u]));
           }
+          o[u] = *reinterpret_cast<const float4*>(sT + row * TS + c4 * 4);
         }
-        epi_bar();
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          float4 v = o[u];
+          if (BWD) {
+            if (g.add != nullptr) { v.x += ra[u].x; v.y += ra[u].y; v.z += ra[u].z; v.w += ra[u].w; }
+            if (g.mask != nullptr) {
+              v.x = rm[u].x > 0.f ? v.x : 0.f; v.y = rm[u].y > 0.f ? v.y : 0.f;
+              v.z = rm[u].z > 0.f ? v.z : 0.f; v.w = rm[u].w > 0.f ? v.w : 0.f;
+            }
+            if (want_stats) {
+              s0[0] += v.x; s0[1] += v.y; s0[2] += v.z; s0[3] += v.w;
+              s1[0] = fmaf(v.x, (rx[u].x - mu[0]) * is[0], s1[0]);
+              s1[1] = fmaf(v.y, (rx[u].y - mu[1]) * is[1], s1[1]);
+              s1[2] = fmaf(v.z, (rx[u].z - mu[2]) * is[2], s1[2]);
+              s1[3] = fmaf(v.w, (rx[u].w - mu[3]) * is[3], s1[3]);
+            }
+          } else {
+            if (g.relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+            if (want_stats) {
+              s0[0] += v.x; s0[1] += v.y; s0[2] += v.z; s0[3] += v.w;
+              s1[0] = fmaf(v.x, v.x, s1[0]); s1[1] = fmaf(v.y, v.y, s1[1]);
+              s1[2] = fmaf(v.z, v.z, s1[2]); s1[3] = fmaf(v.w, v.w, s1[3]);
+            }
+          }
+          *reinterpret_cast<float4*>(g.y + off[u]) = v;
+        }
       }
+      // (the barrier at the top of the next iteration keeps the next tile's writes to the shared tile
+      // behind this pass)
     }
     if (g.stats != nullptr && ok) {
-      if (sseg < NSEG) {
-        sT[(sseg * COUT + sc) * 2] = s0;
-        sT[(sseg * COUT + sc) * 2 + 1] = s1;
+      // threads r0 = 0 .. RSTEP-1 hold partial sums of the same four channels: add them in a fixed order
+      epi_bar();
+      float* red = sT;                               // [RSTEP][C4][8]
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        red[(r0 * C4 + c4) * 8 + e] = s0[e];
+        red[(r0 * C4 + c4) * 8 + 4 + e] = s1[e];
       }
       epi_bar();
       if (t128 < COUT) {
+        const int cc4 = t128 / 4, e = t128 % 4;
         float a0 = 0.f, a1 = 0.f;
-        for (int sg = 0; sg < NSEG; ++sg) {
-          a0 += sT[(sg * COUT + t128) * 2];
-          a1 += sT[(sg * COUT + t128) * 2 + 1];
+        for (int r = 0; r < RSTEP; ++r) {
+          a0 += red[(r * C4 + cc4) * 8 + e];
+          a1 += red[(r * C4 + cc4) * 8 + 4 + e];
         }
         g.stats[(size_t)blockIdx.x * 2 * COUT + t128] = a0;
         g.stats[(size_t)blockIdx.x * 2 * COUT + COUT + t128] = a1;
@@ -438,18 +497,25 @@ static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, const ConvA
   return (int)cudaGetLastError();
 }
 
-template <int COUT, int KC>
-static int launch_conv_persist(const CUtensorMap& mx, const CUtensorMap& mw, const ConvPArgs& g, int grid, cudaStream_t st) {
-  using Cfg = ConvPCfg<COUT, KC>;
-  constexpr int smem = Cfg::STAGES * Cfg::GK * Cfg::KB_BYTES + 128 * Cfg::TSTRIDE * 4 + 1024 + 512;
+template <int COUT, int KC, bool BWD>
+static int launch_conv_persist_t(const CUtensorMap& mx, const CUtensorMap& mw, const ConvPArgs& g, int grid, cudaStream_t st) {
+  using Cfg = ConvPCfg<COUT, KC, BWD>;
+  constexpr int smem = Cfg::STAGES * Cfg::GK * Cfg::KB_BYTES + Cfg::TILES * 128 * Cfg::TSTRIDE * 4 + 1024 + 512;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(conv3x3_persist_kernel<COUT, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(conv3x3_persist_kernel<COUT, KC, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  launch_k(conv3x3_persist_kernel<COUT, KC>, dim3(grid), dim3(CONV_THREADS), smem, st, mx, mw, g);
+  launch_k(conv3x3_persist_kernel<COUT, KC, BWD>, dim3(grid), dim3(CONV_THREADS), smem, st, mx, mw, g);
   return (int)cudaGetLastError();
+}
+
+template <int COUT, int KC>
+static int launch_conv_persist(const CUtensorMap& mx, const CUtensorMap& mw, const ConvPArgs& g, int grid, cudaStream_t st) {
+  const bool bwd = g.add != nullptr || g.mask != nullptr || g.bnx != nullptr;
+  return bwd ? launch_conv_persist_t<COUT, KC, true>(mx, mw, g, grid, st)
+             : launch_conv_persist_t<COUT, KC, false>(mx, mw, g, grid, st);
 }
 
 // 1 when conv3x3_tf32 handles this shape
@@ -499,8 +565,16 @@ extern "C" int conv3x3_grid(int N, int H, int W, int Cout) {
   return g;
 }
 
+struct ConvBwdEpilogue {
+  const void* add;
+  const void* mask;
+  const void* bnx;
+  const void* bn_mean;
+  const void* bn_invstd;
+};
+
 static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N, int H, int W, int Cin, int Cout,
-                       int relu, cudaStream_t st);
+                       int relu, cudaStream_t st, const ConvBwdEpilogue* bwd = nullptr);
 
 // x [N,H,W,Cin], w [Cout,3,3,Cin], y [N,H,W,Cout], all fp32 NHWC / KRSC
 extern "C" int conv3x3_tf32(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout, int relu,
@@ -515,8 +589,23 @@ extern "C" int conv3x3_tf32_stats(const void* x, const void* w, void* y, void* s
   return conv3x3_run(x, w, y, stats, N, H, W, Cin, Cout, 0, st);
 }
 
+// Input gradient with the work that follows it folded into the epilogue:
+//   result = (conv(dy, flipped filter) + add) * [mask > 0]
+// and, when bnx / bn_mean / bn_invstd / stats are given, per-CTA rows [conv3x3_grid()][2 Cout] of
+// (sum result, sum result * xhat): the two reductions of the batch-norm backward of the layer whose
+// output fed this convolution.  add = gradient arriving over the skip connection, mask = that
+// layer's ReLU output.  Any of add / mask / (bnx ...) may be null.
+extern "C" int conv3x3_dgrad_fused(const void* dy, const void* w_flipped, void* out, const void* add, const void* mask,
+                                   const void* bnx, const void* bn_mean, const void* bn_invstd, void* stats, int N,
+                                   int H, int W, int Cin, int Cout, cudaStream_t st) {
+  if ((bnx != nullptr) != (stats != nullptr)) return -1;
+  if (bnx != nullptr && (bn_mean == nullptr || bn_invstd == nullptr)) return -1;
+  ConvBwdEpilogue e = {add, mask, bnx, bn_mean, bn_invstd};
+  return conv3x3_run(dy, w_flipped, out, stats, N, H, W, Cin, Cout, 0, st, &e);
+}
+
 static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N, int H, int W, int Cin, int Cout,
-                       int relu, cudaStream_t st) {
+                       int relu, cudaStream_t st, const ConvBwdEpilogue* bwd) {
   if (!conv3x3_supported(N, H, W, Cin, Cout)) return -1;
   int th = 128 / W;
   if (th > H) th = H;
@@ -544,9 +633,17 @@ static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N
   if (g.error == nullptr) return -13;
   g.H = H; g.W = W; g.Cin = Cin; g.TH = th; g.TN = tn; g.tiles_h = H / th; g.relu = relu;
   const int tiles = (N / tn) * (H / th);
-  if (stats != nullptr || conv_use_persistent()) {
+  if (stats != nullptr || bwd != nullptr || conv_use_persistent()) {
     ConvPArgs pg;
     pg.y = g.y; pg.stats = reinterpret_cast<float*>(stats); pg.error = g.error;
+    pg.add = pg.mask = pg.bnx = pg.bn_mean = pg.bn_invstd = nullptr;
+    if (bwd != nullptr) {
+      pg.add = reinterpret_cast<const float*>(bwd->add);
+      pg.mask = reinterpret_cast<const float*>(bwd->mask);
+      pg.bnx = reinterpret_cast<const float*>(bwd->bnx);
+      pg.bn_mean = reinterpret_cast<const float*>(bwd->bn_mean);
+      pg.bn_invstd = reinterpret_cast<const float*>(bwd->bn_invstd);
+    }
     pg.H = H; pg.W = W; pg.Cin = Cin; pg.TH = th; pg.TN = tn; pg.tiles_h = H / th; pg.n_tiles = tiles; pg.relu = relu;
     const int grid = conv3x3_grid(N, H, W, Cout);
 #define CONVP_CASE(CO)                                                             \

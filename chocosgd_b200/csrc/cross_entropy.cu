@@ -31,15 +31,16 @@ __device__ __forceinline__ float ce_warp_sum(float v) {
 // out[0] = loss, out[1] = top-1 %, out[2] = top-5 %, out[3] = number of counted rows
 __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const float* __restrict__ z, const long long* __restrict__ tgt,
                                                                   float* __restrict__ dz, float* row_loss, int* row_rank,
-                                                                  unsigned* counter, float* out, float* loss_out, int B, int C) {
+                                                                  unsigned* counter, float* out, float* loss_out, int B, int C,
+                                                                  long long ld) {
   pdl_wait();
   pdl_trigger();
   __shared__ float red[CE_THREADS / 32];
   __shared__ int redi[CE_THREADS / 32];
   __shared__ int last;
   const int row = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const float* zr = z + (size_t)row * C;
-  float* dr = dz + (size_t)row * C;
+  const float* zr = z + (size_t)row * ld;    // ld >= C floats per row (padded rows of a GEMM output)
+  float* dr = dz + (size_t)row * ld;
   const long long t = tgt[row];
   const bool valid = t >= 0 && t < C;
   // pass 1: row maximum
@@ -132,18 +133,27 @@ __global__ void ce_rescale_kernel(float* dz, const float* out, long long n, int 
 
 // scratch: B floats + B ints + 1 unsigned (counter: zero before the first call, self-resetting);
 // out: 4 floats; loss_out: 1 float
+extern "C" int cross_entropy_fused_ld(const void* logits, const void* target, void* dlogits, void* scratch, void* out,
+                                      void* loss_out, int B, int C, long long ld, int may_ignore, cudaStream_t st);
+
 extern "C" int cross_entropy_fused(const void* logits, const void* target, void* dlogits, void* scratch, void* out,
                                    void* loss_out, int B, int C, int may_ignore, cudaStream_t st) {
-  if (B < 1 || C < 1) return -1;
+  return cross_entropy_fused_ld(logits, target, dlogits, scratch, out, loss_out, B, C, C, may_ignore, st);
+}
+
+// same with `ld` floats between consecutive rows of logits and of dlogits (ld >= C)
+extern "C" int cross_entropy_fused_ld(const void* logits, const void* target, void* dlogits, void* scratch, void* out,
+                                      void* loss_out, int B, int C, long long ld, int may_ignore, cudaStream_t st) {
+  if (B < 1 || C < 1 || ld < C) return -1;
   float* row_loss = reinterpret_cast<float*>(scratch);
   int* row_rank = reinterpret_cast<int*>(row_loss + B);
   unsigned* counter = reinterpret_cast<unsigned*>(row_rank + B);
   launch_k(cross_entropy_kernel, dim3(B), dim3(CE_THREADS), 0, st, reinterpret_cast<const float*>(logits),
                                                  reinterpret_cast<const long long*>(target),
                                                  reinterpret_cast<float*>(dlogits), row_loss, row_rank, counter,
-                                                 reinterpret_cast<float*>(out), reinterpret_cast<float*>(loss_out), B, C);
+                                                 reinterpret_cast<float*>(out), reinterpret_cast<float*>(loss_out), B, C, ld);
   if (may_ignore) {
-    const long long n = (long long)B * C;
+    const long long n = (long long)B * ld;   // padding columns included: scaling them is harmless
     long long blocks = (n + 255) / 256;
     if (blocks > 1184) blocks = 1184;
     launch_k(ce_rescale_kernel, dim3((int)blocks), dim3(256), 0, st, reinterpret_cast<float*>(dlogits), reinterpret_cast<const float*>(out), n, B);

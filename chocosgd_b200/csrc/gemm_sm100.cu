@@ -31,11 +31,13 @@ struct GemmArgs {
   int M, N, K, ldd;
   int k_blocks_per_split;
   int relu;
+  int passes;          // 1: plain TF32;  3: split-operand passes (hi.hi + hi.lo + lo.hi), see gemm_tf32x3
 };
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo, GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -55,7 +57,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int kb_begin = blockIdx.z * g.k_blocks_per_split;
   int kb_end = kb_begin + g.k_blocks_per_split;
   if (kb_end > total_kb) kb_end = total_kb;
-  const int n_kb = kb_end - kb_begin;
+  const int n_kb1 = kb_end - kb_begin;
+  const int n_kb = n_kb1 * g.passes;      // pipeline iterations: every pass walks the same k-blocks
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GEMM_STAGES; ++s) {
@@ -84,19 +87,22 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int s = i % GEMM_STAGES;
         if (i >= GEMM_STAGES && !mbar_wait(empty + s, ((i / GEMM_STAGES) - 1) & 1)) { *abort_flag = 1; break; }
         if (*abort_flag) break;
-        const int k0 = (kb_begin + i) * GEMM_BK;
+        const int pass = i / n_kb1;
+        const int k0 = (kb_begin + i % n_kb1) * GEMM_BK;
+        const CUtensorMap* pa = pass == 2 ? &map_a_lo : &map_a;   // passes: (A, B), (A, B_lo), (A_lo, B)
+        const CUtensorMap* pb = pass == 1 ? &map_b_lo : &map_b;
         mbar_expect_tx(full + s, A_BYTES + B_BYTES);
         if (!A_MN) {
-          tma_load_2d(sA + s * A_BYTES, &map_a, full + s, k0, m0);
+          tma_load_2d(sA + s * A_BYTES, pa, full + s, k0, m0);
         } else {
           for (int j = 0; j < GEMM_BM / 32; ++j)
-            tma_load_2d(sA + s * A_BYTES + j * 4096, &map_a, full + s, m0 + 32 * j, k0);
+            tma_load_2d(sA + s * A_BYTES + j * 4096, pa, full + s, m0 + 32 * j, k0);
         }
         if (!B_MN) {
-          tma_load_2d(sB + s * B_BYTES, &map_b, full + s, k0, n0);
+          tma_load_2d(sB + s * B_BYTES, pb, full + s, k0, n0);
         } else {
           for (int j = 0; j < BN / 32; ++j)
-            tma_load_2d(sB + s * B_BYTES + j * 4096, &map_b, full + s, n0 + 32 * j, k0);
+            tma_load_2d(sB + s * B_BYTES + j * 4096, pb, full + s, n0 + 32 * j, k0);
         }
       }
     } else if (warp == 5 && lane == 0) {
@@ -179,7 +185,9 @@ __device__ __forceinline__ bool gemm_epi_bar_or(bool flag) {
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
+                         GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int A_BYTES = GEMM_BM * GEMM_BK * 4;
@@ -196,7 +204,8 @@ gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (g.M + GEMM_BM - 1) / GEMM_BM, tiles_n = (g.N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
-  const int n_kb = (g.K + GEMM_BK - 1) / GEMM_BK;
+  const int n_kb1 = (g.K + GEMM_BK - 1) / GEMM_BK;
+  const int n_kb = n_kb1 * g.passes;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GEMM_STAGES; ++s) {
@@ -238,14 +247,17 @@ gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        const int k0 = i * GEMM_BK;
+        const int pass = i / n_kb1;
+        const int k0 = (i % n_kb1) * GEMM_BK;
+        const CUtensorMap* pa = pass == 2 ? &map_a_lo : &map_a;   // passes: (A, B), (A, B_lo), (A_lo, B)
+        const CUtensorMap* pb = pass == 1 ? &map_b_lo : &map_b;
         if (lane < PA) {
-          if (!A_MN) tma_load_2d(sA + s * A_BYTES, &map_a, full + s, k0, m0);
-          else tma_load_2d(sA + s * A_BYTES + lane * 4096, &map_a, full + s, m0 + 32 * lane, k0);
+          if (!A_MN) tma_load_2d(sA + s * A_BYTES, pa, full + s, k0, m0);
+          else tma_load_2d(sA + s * A_BYTES + lane * 4096, pa, full + s, m0 + 32 * lane, k0);
         } else if (lane < PA + PB) {
           const int j = lane - PA;
-          if (!B_MN) tma_load_2d(sB + s * B_BYTES, &map_b, full + s, k0, n0);
-          else tma_load_2d(sB + s * B_BYTES + j * 4096, &map_b, full + s, n0 + 32 * j, k0);
+          if (!B_MN) tma_load_2d(sB + s * B_BYTES, pb, full + s, k0, n0);
+          else tma_load_2d(sB + s * B_BYTES + j * 4096, pb, full + s, n0 + 32 * j, k0);
         }
         __syncwarp();
       }
@@ -394,7 +406,8 @@ extern "C" int gemm_tf32_last_error() {
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int splits, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mal, const CUtensorMap& mbl,
+                       const GemmArgs& g, int splits, cudaStream_t st) {
   constexpr int smem = GEMM_STAGES * (GEMM_BM * GEMM_BK * 4 + BN * GEMM_BK * 4) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
@@ -404,12 +417,13 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     configured = true;
   }
   dim3 grid((g.M + GEMM_BM - 1) / GEMM_BM, (g.N + BN - 1) / BN, splits);
-  gemm_tf32_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, g);
+  gemm_tf32_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, mal, mbl, g);
   return (int)cudaGetLastError();
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm_persist(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int grid, cudaStream_t st) {
+static int launch_gemm_persist(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mal,
+                               const CUtensorMap& mbl, const GemmArgs& g, int grid, cudaStream_t st) {
   constexpr int smem = GEMM_STAGES * (GEMM_BM * GEMM_BK * 4 + BN * GEMM_BK * 4) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
@@ -418,49 +432,61 @@ static int launch_gemm_persist(const CUtensorMap& ma, const CUtensorMap& mb, con
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gemm_tf32_persist_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, g);
+  gemm_tf32_persist_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, mal, mbl, g);
   return (int)cudaGetLastError();
 }
 
 template <int BN>
-static int dispatch_persist(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
-                            int grid, cudaStream_t st) {
-  if (!a_mn && !b_mn) return launch_gemm_persist<BN, false, false>(ma, mb, g, grid, st);
-  if (!a_mn && b_mn) return launch_gemm_persist<BN, false, true>(ma, mb, g, grid, st);
-  if (a_mn && !b_mn) return launch_gemm_persist<BN, true, false>(ma, mb, g, grid, st);
-  return launch_gemm_persist<BN, true, true>(ma, mb, g, grid, st);
+static int dispatch_persist(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mal,
+                            const CUtensorMap& mbl, const GemmArgs& g, int grid, cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_gemm_persist<BN, false, false>(ma, mb, mal, mbl, g, grid, st);
+  if (!a_mn && b_mn) return launch_gemm_persist<BN, false, true>(ma, mb, mal, mbl, g, grid, st);
+  if (a_mn && !b_mn) return launch_gemm_persist<BN, true, false>(ma, mb, mal, mbl, g, grid, st);
+  return launch_gemm_persist<BN, true, true>(ma, mb, mal, mbl, g, grid, st);
 }
 
 template <int BN>
-static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g,
-                          int splits, cudaStream_t st) {
-  if (!a_mn && !b_mn) return launch_gemm<BN, false, false>(ma, mb, g, splits, st);
-  if (!a_mn && b_mn) return launch_gemm<BN, false, true>(ma, mb, g, splits, st);
-  if (a_mn && !b_mn) return launch_gemm<BN, true, false>(ma, mb, g, splits, st);
-  return launch_gemm<BN, true, true>(ma, mb, g, splits, st);
+static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mal,
+                          const CUtensorMap& mbl, const GemmArgs& g, int splits, cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_gemm<BN, false, false>(ma, mb, mal, mbl, g, splits, st);
+  if (!a_mn && b_mn) return launch_gemm<BN, false, true>(ma, mb, mal, mbl, g, splits, st);
+  if (a_mn && !b_mn) return launch_gemm<BN, true, false>(ma, mb, mal, mbl, g, splits, st);
+  return launch_gemm<BN, true, true>(ma, mb, mal, mbl, g, splits, st);
 }
 
 // D[M,N] = A . B^T (+ bias).  a_mn = 0: A is [M, K] (K contiguous, lda);  a_mn = 1: A is [K, M].
 // Same for B with N rows.  split_k > 1 accumulates with atomics into D, which the caller zeroed.
-extern "C" int gemm_tf32(const void* a, const void* b, void* d, const void* bias, int M, int N, int K, int lda, int ldb,
-                         int ldd, int a_mn, int b_mn, int split_k, int relu, cudaStream_t stream) {
+// a_lo / b_lo non-null: three passes over K accumulate  A.B + A.B_lo + A_lo.B  into the same TMEM
+// accumulator (operands given as exact TF32 values plus their fp32 remainders, see tf32_split_pad):
+// products carry 2^-21 relative error instead of TF32's 2^-10, at three times the tensor-core work.
+static int gemm_run(const void* a, const void* a_lo, const void* b, const void* b_lo, void* d, const void* bias, int M,
+                    int N, int K, int lda, int ldb, int ldd, int a_mn, int b_mn, int split_k, int relu,
+                    cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((a_lo == nullptr) != (b_lo == nullptr)) return -1;
   // 256-wide tiles when the grid still fills the machine: with 4-byte operands a 128 x 128 tile reads
   // shared memory as fast as the tensor core consumes it; 128 x 256 needs 25 % less per FLOP
   const long long tiles256 = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + 255) / 256);
   const int BN = N <= 32 ? 32 : (N <= 64 ? 64 : ((N >= 256 && tiles256 >= 120 && split_k <= 1) ? 256 : 128));
-  CUtensorMap ma, mb;
-  int rc = a_mn ? make_map_2d(&ma, a, M, K, lda, 32, GEMM_BK, true)
-                : make_map_2d(&ma, a, K, M, lda, GEMM_BK, GEMM_BM, false);
-  if (rc) return rc;
-  rc = b_mn ? make_map_2d(&mb, b, N, K, ldb, 32, GEMM_BK, true) : make_map_2d(&mb, b, K, N, ldb, GEMM_BK, BN, false);
-  if (rc) return rc;
+  CUtensorMap ma, mb, mal, mbl;
+  for (int which = 0; which < 2; ++which) {
+    const void* pa = which ? a_lo : a;
+    const void* pb = which ? b_lo : b;
+    if (pa == nullptr) { mal = ma; mbl = mb; break; }
+    int rc = a_mn ? make_map_2d(which ? &mal : &ma, pa, M, K, lda, 32, GEMM_BK, true)
+                  : make_map_2d(which ? &mal : &ma, pa, K, M, lda, GEMM_BK, GEMM_BM, false);
+    if (rc) return rc;
+    rc = b_mn ? make_map_2d(which ? &mbl : &mb, pb, N, K, ldb, 32, GEMM_BK, true)
+              : make_map_2d(which ? &mbl : &mb, pb, K, N, ldb, GEMM_BK, BN, false);
+    if (rc) return rc;
+  }
   GemmArgs g;
   g.d = reinterpret_cast<float*>(d);
   g.bias = reinterpret_cast<const float*>(bias);
   g.error = gemm_error_word();
   if (g.error == nullptr) return -13;
   g.M = M; g.N = N; g.K = K; g.ldd = ldd; g.relu = relu;
+  g.passes = a_lo != nullptr ? 3 : 1;
   const int total_kb = (K + GEMM_BK - 1) / GEMM_BK;
   int splits = split_k < 1 ? 1 : split_k;
   if (splits > total_kb) splits = total_kb;
@@ -479,12 +505,58 @@ extern "C" int gemm_tf32(const void* a, const void* b, void* d, const void* bias
     const long long tiles = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
     if (enabled && tiles >= 2LL * sms) {
       const int grid = sms;
-      return BN == 256 ? dispatch_persist<256>(a_mn, b_mn, ma, mb, g, grid, stream)
-                       : dispatch_persist<128>(a_mn, b_mn, ma, mb, g, grid, stream);
+      return BN == 256 ? dispatch_persist<256>(a_mn, b_mn, ma, mb, mal, mbl, g, grid, stream)
+                       : dispatch_persist<128>(a_mn, b_mn, ma, mb, mal, mbl, g, grid, stream);
     }
   }
-  if (BN == 32) return dispatch_major<32>(a_mn, b_mn, ma, mb, g, splits, stream);
-  if (BN == 64) return dispatch_major<64>(a_mn, b_mn, ma, mb, g, splits, stream);
-  if (BN == 256) return dispatch_major<256>(a_mn, b_mn, ma, mb, g, splits, stream);
-  return dispatch_major<128>(a_mn, b_mn, ma, mb, g, splits, stream);
+  if (BN == 32) return dispatch_major<32>(a_mn, b_mn, ma, mb, mal, mbl, g, splits, stream);
+  if (BN == 64) return dispatch_major<64>(a_mn, b_mn, ma, mb, mal, mbl, g, splits, stream);
+  if (BN == 256) return dispatch_major<256>(a_mn, b_mn, ma, mb, mal, mbl, g, splits, stream);
+  return dispatch_major<128>(a_mn, b_mn, ma, mb, mal, mbl, g, splits, stream);
+}
+
+extern "C" int gemm_tf32(const void* a, const void* b, void* d, const void* bias, int M, int N, int K, int lda, int ldb,
+                         int ldd, int a_mn, int b_mn, int split_k, int relu, cudaStream_t stream) {
+  return gemm_run(a, nullptr, b, nullptr, d, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, split_k, relu, stream);
+}
+
+// fp32-grade product on the TF32 tensor cores (the "3xTF32" scheme): operands come as (hi, lo) pairs
+// from tf32_split_pad with the same leading dimension.
+extern "C" int gemm_tf32x3(const void* a_hi, const void* a_lo, const void* b_hi, const void* b_lo, void* d,
+                           const void* bias, int M, int N, int K, int lda, int ldb, int ldd, int a_mn, int b_mn,
+                           int split_k, int relu, cudaStream_t stream) {
+  if (a_lo == nullptr || b_lo == nullptr) return -1;
+  return gemm_run(a_hi, a_lo, b_hi, b_lo, d, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, split_k, relu, stream);
+}
+
+// hi = x with the 13 low mantissa bits cleared (an exact TF32 value), lo = x - hi (exact in fp32), both
+// written with `ldd` floats per row (ldd >= cols, a multiple of 4 so that rows are 16-byte aligned for
+// TMA; the tail columns are zero).  One pass: 4 bytes read, 8 written per element.
+__global__ void tf32_split_pad_kernel(const float* __restrict__ src, long long rows, int cols, long long lds,
+                                      float* __restrict__ hi, float* __restrict__ lo, int ldd) {
+  const long long total = rows * (long long)(ldd / 4);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (ldd / 4);
+    const int c = (int)(i % (ldd / 4)) * 4;
+    float v[4], h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      v[e] = (c + e < cols) ? src[r * lds + c + e] : 0.f;
+      h[e] = __uint_as_float(__float_as_uint(v[e]) & 0xFFFFE000u);
+      l[e] = v[e] - h[e];
+    }
+    *reinterpret_cast<float4*>(hi + r * ldd + c) = make_float4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<float4*>(lo + r * ldd + c) = make_float4(l[0], l[1], l[2], l[3]);
+  }
+}
+
+extern "C" int tf32_split_pad(const void* src, long long rows, int cols, long long lds, void* hi, void* lo, int ldd,
+                              cudaStream_t st) {
+  if (rows <= 0 || cols <= 0 || ldd < cols || ldd % 4 != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(hi) & 15) != 0 || (reinterpret_cast<uintptr_t>(lo) & 15) != 0) return -1;
+  long long blocks = (rows * (ldd / 4) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  tf32_split_pad_kernel<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const float*>(src), rows, cols, lds,
+                                                    reinterpret_cast<float*>(hi), reinterpret_cast<float*>(lo), ldd);
+  return (int)cudaGetLastError();
 }

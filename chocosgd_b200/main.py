@@ -69,10 +69,6 @@ def main(conf):
     model = define_model(conf, graph, data_loader=data_loader, device=device)
     optimizer = define_optimizer(conf, model, graph)
     scheduler = Scheduler(conf, graph, run)
-    if conf.n_sub_process > 1 and "rnn_lm" not in conf.arch and graph.on_cuda:
-        from .parallel.data_parallel import LocalDataParallel
-
-        model = LocalDataParallel(model, device_ids=graph.device)
     ckpt.maybe_resume_from_checkpoint(conf, graph, run, model, optimizer, scheduler)
     criterion = torch.nn.CrossEntropyLoss(reduction="mean")
     if "rnn_lm" in conf.arch:

@@ -31,12 +31,22 @@ def bn_act(bn, x, residual=None, relu=True):
     return _f(bn, x, residual, relu)
 
 
-def conv_bn_act(conv, bn, x, residual=None, relu=True):
+def conv_bn_act(conv, bn, x, residual=None, relu=True, fold_res=False):
     """relu(bn(conv(x)) + residual); on the native path the convolution epilogue also yields the
     batch statistics, so no reduction pass runs over the activation."""
     from ..ops.bn import conv_bn_act as _f
 
-    return _f(conv, bn, x, residual, relu)
+    return _f(conv, bn, x, residual, relu, fold_res)
+
+
+def fold_residual_ok(conv, x) -> bool:
+    """Whether a residual block whose skip connection is ``x`` can hand the skip gradient to ``conv``'s
+    input-gradient kernel (native kernels on, shape covered)."""
+    if not x.is_cuda:
+        return False
+    from ..ops.bn import fold_residual_ok as _f
+
+    return _f(conv, x)
 
 
 def conv3x3(in_planes, out_planes, stride=1):

@@ -26,8 +26,12 @@ class BasicBlock(nn.Module):
 
     def forward(self, x):
         residual = x if self.downsample is None else self.downsample(x)
-        out = L.conv_bn_act(self.conv1, self.bn1, x)
-        return L.conv_bn_act(self.conv2, self.bn2, out, residual=residual)
+        # identity blocks on the native kernels: the skip gradient is added inside conv1's
+        # input-gradient kernel instead of by a separate add
+        fold = self.downsample is None and self.training and L.fold_residual_ok(self.conv1, x) \
+            and L.fold_residual_ok(self.conv2, x)
+        out = L.conv_bn_act(self.conv1, self.bn1, x, fold_res=fold)
+        return L.conv_bn_act(self.conv2, self.bn2, out, residual=residual, fold_res=fold)
 
 
 class Bottleneck(nn.Module):
@@ -86,11 +90,27 @@ class ResNetCifar(_ResNetBase):
         self.fc = L.Linear(64 * block_fn.expansion, self.num_classes)
         L.he_init(self)
 
-    def forward(self, x):
+    def forward_features(self, x):
+        """The last feature map (before pooling); ``forward`` = ``classify(forward_features(x))``."""
         x = L.conv_bn_act(self.conv1, self.bn1, x)
-        x = self.layer3(self.layer2(self.layer1(x)))
-        x = self.avgpool(x)
+        return self.layer3(self.layer2(self.layer1(x)))
+
+    def classify(self, feat):
+        x = self.avgpool(feat)
         return self.fc(x.reshape(x.size(0), -1))
+
+    def forward(self, x):
+        return self.classify(self.forward_features(x))
+
+    def head_loss(self, feat, target):
+        """Pooling + classifier + mean cross-entropy (+ top-1 / top-5) of a feature map in one kernel:
+        ``(loss, stats)``, or None when the fused kernel does not cover the shapes / device."""
+        from ..ops import head
+
+        pool_all = feat.shape[-1] == feat.shape[-2] == self.avgpool.kernel_size
+        if pool_all and head.supported(feat, self.fc.weight, target):
+            return head.head_loss(feat, self.fc.weight, self.fc.bias, target)
+        return None
 
 
 class ResNetImagenet(_ResNetBase):

@@ -32,6 +32,8 @@ def _lib_bn():
             fn.restype = ctypes.c_int
         lib.bn_forward_partials.argtypes = [ctypes.POINTER(BnArgsC), ctypes.c_int, ctypes.c_void_p]
         lib.bn_forward_partials.restype = ctypes.c_int
+        lib.bn_backward_partials.argtypes = [ctypes.POINTER(BnArgsC), ctypes.c_int, ctypes.c_void_p]
+        lib.bn_backward_partials.restype = ctypes.c_int
         lib.bn_reduce_grid.argtypes = [ctypes.c_int, ctypes.c_int]
         lib.bn_reduce_grid.restype = ctypes.c_int
         lib.bn_last_error.restype = ctypes.c_int
@@ -66,7 +68,8 @@ def supported(x, C) -> bool:
 
 class _BnActFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gamma, beta, residual, running_mean, running_var, relu, momentum, eps, stats=None):
+    def forward(ctx, x, gamma, beta, residual, running_mean, running_var, relu, momentum, eps, stats=None,
+                fold_res=False):
         lib = _lib_bn()
         N, C, H, W = x.shape
         P = N * H * W
@@ -94,6 +97,15 @@ class _BnActFn(torch.autograd.Function):
             raise RuntimeError(f"bn_forward failed ({rc})")
         ctx.save_for_backward(x, y, gamma, mean, invstd)
         ctx.relu, ctx.has_res = bool(relu), residual is not None
+        # the skip gradient is handed to the block's first convolution (added in its epilogue)
+        ctx.fold_res = bool(fold_res) and residual is not None
+        ctx.res_key = residual.data_ptr() if ctx.fold_res else None
+        if relu:
+            # the consumer of y may fold this layer's backward sums into its input-gradient epilogue
+            from .conv import FUSION
+
+            if FUSION.enabled:
+                FUSION.bn_of_output[y.data_ptr()] = (y, x, mean, invstd)
         return y
 
     @staticmethod
@@ -102,27 +114,44 @@ class _BnActFn(torch.autograd.Function):
         x, y, gamma, mean, invstd = ctx.saved_tensors
         N, C, H, W = x.shape
         P = N * H * W
+        from .conv import FUSION
+
         dy = dy.contiguous(memory_format=torch.channels_last)
+        hint = FUSION.masked.pop(dy.data_ptr(), None) if ctx.relu else None
+        if hint is not None and hint[0].shape != dy.shape:
+            hint = None
         dx = torch.empty_like(x)
-        dres = torch.empty_like(x) if ctx.has_res else None
         dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
         dbeta = torch.empty_like(dgamma)
         partial, counter = _get_scratch(x.device, P, C, lib)
         a = BnArgsC()
         a.x, a.dy, a.y, a.gamma = x.data_ptr(), dy.data_ptr(), y.data_ptr(), gamma.data_ptr()
         a.out = dx.data_ptr()
-        a.out2 = dres.data_ptr() if dres is not None else 0
         a.mean, a.invstd, a.dgamma, a.dbeta = mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr()
         a.partial, a.counter = partial.data_ptr(), counter.data_ptr()
         a.P, a.C, a.relu = P, C, int(ctx.relu)
-        rc = lib.bn_backward(ctypes.byref(a), _lib.stream_ptr())
-        _lib.count(2)
+        if hint is not None:
+            # dy comes from an input-gradient epilogue that applied this layer's ReLU mask and left the
+            # two backward sums as per-CTA rows: one elementwise kernel; the skip gradient is dy itself
+            dres = dy if ctx.has_res else None
+            a.partial = hint[1].data_ptr()
+            rc = lib.bn_backward_partials(ctypes.byref(a), hint[1].shape[0], _lib.stream_ptr())
+            _lib.count(1)
+        else:
+            dres = torch.empty_like(x) if ctx.has_res else None
+            a.out2 = dres.data_ptr() if dres is not None else 0
+            rc = lib.bn_backward(ctypes.byref(a), _lib.stream_ptr())
+            _lib.count(2)
         if rc != 0:
             raise RuntimeError(f"bn_backward failed ({rc})")
-        return dx, dgamma, dbeta, dres, None, None, None, None, None, None
+        if ctx.fold_res:
+            FUSION.pending_res[ctx.res_key] = (dy, dres)
+            FUSION.clear_after_backward()
+            dres = None
+        return dx, dgamma, dbeta, dres, None, None, None, None, None, None, None
 
 
-def bn_act(bn, x, residual=None, relu=True, stats=None):
+def bn_act(bn, x, residual=None, relu=True, stats=None, fold_res=False):
     """``relu(bn(x) + residual)`` with one fused kernel pair when possible.  ``stats``: rows of
     per-channel (sum, sum of squares) partials of ``x`` from its producer (``conv_bn_act``)."""
     from . import nn as native_nn
@@ -135,16 +164,34 @@ def bn_act(bn, x, residual=None, relu=True, stats=None):
         mom = bn.momentum if bn.momentum is not None else 0.1
         rm = bn.running_mean if bn.track_running_stats else None
         rv = bn.running_var if bn.track_running_stats else None
-        return _BnActFn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps, stats)
+        return _BnActFn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps, stats, fold_res)
     out = stock_forward(bn, x)
     if residual is not None:
         out = out + residual
     return F.relu(out, inplace=True) if relu else out
 
 
-def conv_bn_act(conv, bn, x, residual=None, relu=True):
+def fold_residual_ok(conv, x) -> bool:
+    """True when ``conv`` (the first convolution of a residual block whose skip connection is ``x``
+    itself) will run the native kernels and can add the skip gradient in its input-gradient epilogue."""
+    from . import nn as native_nn
+
+    if not (native_nn.native_enabled("conv") and native_nn.native_enabled("bn") and x.is_cuda and x.requires_grad
+            and torch.is_grad_enabled()):
+        return False
+    from .conv import FUSION, conv_supported
+
+    if not FUSION.enabled:
+        return False
+
+    return conv.in_channels != 3 and conv_supported(conv, x)
+
+
+def conv_bn_act(conv, bn, x, residual=None, relu=True, fold_res=False):
     """``relu(bn(conv(x)) + residual)``.  When both layers run their native kernels the convolution
-    epilogue also produces the batch statistics, so the batch-norm needs no reduction pass."""
+    epilogue also produces the batch statistics, so the batch-norm needs no reduction pass.
+    ``fold_res`` (decided by the block with ``fold_residual_ok``): the gradient of the skip connection
+    travels from this block's last batch-norm to its first convolution outside autograd."""
     from . import nn as native_nn
 
     if (native_nn.native_enabled("conv") and native_nn.native_enabled("bn") and bn.training and x.is_cuda
@@ -153,8 +200,10 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True):
 
         if ((conv_supported(conv, x) or first_conv_supported(conv, x)) and (conv.out_channels // 4) <= 256
                 and 256 % (conv.out_channels // 4) == 0):
-            y, stats = conv2d_native(conv, x, want_stats=True)
-            return bn_act(bn, y, residual, relu, stats=stats)
+            y, stats = conv2d_native(conv, x, want_stats=True, fold_res=fold_res and residual is None)
+            return bn_act(bn, y, residual, relu, stats=stats, fold_res=fold_res)
+    if fold_res:
+        raise RuntimeError("fold_res was requested for a layer pair that does not run the native kernels")
     return bn_act(bn, conv(x), residual, relu)
 
 

@@ -24,6 +24,8 @@ def _declare():
         vp, i = ctypes.c_void_p, ctypes.c_int
         lib.cross_entropy_fused.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, vp]
         lib.cross_entropy_fused.restype = i
+        lib.cross_entropy_fused_ld.argtypes = [vp, vp, vp, vp, vp, vp, i, i, ctypes.c_longlong, i, vp]
+        lib.cross_entropy_fused_ld.restype = i
         lib._ce_declared = True
     return lib
 
@@ -37,18 +39,21 @@ class _CrossEntropyFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, target, may_ignore):
         lib = _declare()
-        z = logits.contiguous()
+        # rows may be padded (the output of the native GEMM has 16-byte aligned rows): no copy then,
+        # and the gradient gets the same row pitch so that it can go back into the GEMMs as it is
+        z = logits if (logits.stride(1) == 1 and logits.stride(0) >= logits.shape[1]) else logits.contiguous()
         B, C = z.shape
-        dz = torch.empty_like(z)
+        ld = z.stride(0)
+        dz = torch.empty_strided((B, C), (ld, 1), dtype=z.dtype, device=z.device) if ld != C else torch.empty_like(z)
         key = (z.device, B)
         scratch = _SCRATCH.get(key)
         if scratch is None:  # zeroed once: the arrival counter resets itself
             scratch = _SCRATCH[key] = torch.zeros(2 * B + 4, dtype=torch.int32, device=z.device)
         stats = torch.empty(4, dtype=torch.float32, device=z.device)
         loss = torch.empty((), dtype=torch.float32, device=z.device)
-        _lib.check(lib.cross_entropy_fused(_lib.ptr(z), _lib.ptr(target.contiguous()), _lib.ptr(dz), _lib.ptr(scratch),
-                                           _lib.ptr(stats), _lib.ptr(loss), B, C, int(bool(may_ignore)),
-                                           _lib.stream_ptr()), "cross_entropy_fused")
+        _lib.check(lib.cross_entropy_fused_ld(_lib.ptr(z), _lib.ptr(target.contiguous()), _lib.ptr(dz),
+                                              _lib.ptr(scratch), _lib.ptr(stats), _lib.ptr(loss), B, C, ld,
+                                              int(bool(may_ignore)), _lib.stream_ptr()), "cross_entropy_fused")
         _lib.count(2 if may_ignore else 1)
         ctx.save_for_backward(dz)
         ctx.set_materialize_grads(False)  # no zero tensor for the statistics output

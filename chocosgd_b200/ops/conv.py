@@ -44,6 +44,8 @@ def _declare():
         lib.conv3x3_wgrad16_parts.restype = i
         lib.conv3x3_wgrad16_supported.argtypes = [i, i, i]
         lib.conv3x3_wgrad16_supported.restype = i
+        lib.conv3x3_dgrad_fused.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, vp]
+        lib.conv3x3_dgrad_fused.restype = i
         lib._conv_declared = True
     return lib
 
@@ -129,6 +131,61 @@ def conv3x3_wgrad(x, dy, weight):
     return dw
 
 
+class _Fusion:
+    """Hand-over between neighbouring layers of one training step, so that work of the batch-norm
+    backward and of the skip connection can ride in the epilogue of the input-gradient convolution:
+
+    * ``bn_of_output``: a batch-norm + ReLU output -> (its pre-normalisation input, mean, invstd);
+      looked up by the convolution that consumes that output;
+    * ``pending_res``: a tensor used as a block's skip connection -> the gradient that arrived
+      over the skip; the block's first convolution adds it in its input-gradient epilogue (no add
+      kernel, and its batch-norm sums then cover the whole gradient);
+    * ``masked``: a gradient the epilogue already multiplied with the ReLU mask -> the per-CTA rows
+      of batch-norm backward sums it produced; the batch-norm backward then skips its reduction.
+
+    Keys are data pointers; every entry keeps its tensors alive so that the address cannot be reused
+    while the entry exists.  ``clear()`` runs at the start of a step and when a backward pass ends."""
+
+    def __init__(self):
+        self.bn_of_output, self.pending_res, self.masked = {}, {}, {}
+        self._callback_queued = False
+        #: CHOCO_BWD_FUSION=0 keeps every layer's backward self-contained (A/B switch, tests)
+        self.enabled = os.environ.get("CHOCO_BWD_FUSION", "1") != "0"
+
+    def clear(self):
+        self.bn_of_output.clear()
+        self.pending_res.clear()
+        self.masked.clear()
+        self._callback_queued = False
+
+    def clear_after_backward(self):
+        if not self._callback_queued:
+            torch.autograd.Variable._execution_engine.queue_callback(self.clear)
+            self._callback_queued = True
+
+
+FUSION = _Fusion()
+
+
+def conv3x3_dgrad_fused(dy, flipped, cin, add=None, mask=None, bn=None):
+    """``(dx, stats)``: input gradient with the skip gradient added, the ReLU mask applied and the
+    batch-norm backward sums of the producing layer accumulated, all in the epilogue."""
+    lib = _declare()
+    n, cout, h, w = dy.shape
+    dx = torch.empty((n, cin, h, w), dtype=torch.float32, device=dy.device, memory_format=torch.channels_last)
+    stats = bnx = mean = invstd = None
+    if bn is not None:
+        bnx, mean, invstd = bn
+        stats = torch.empty((lib.conv3x3_grid(n, h, w, cin), 2 * cin), dtype=torch.float32, device=dy.device)
+    rc = lib.conv3x3_dgrad_fused(_lib.ptr(dy), _lib.ptr(flipped), _lib.ptr(dx), _lib.ptr(add), _lib.ptr(mask),
+                                 _lib.ptr(bnx), _lib.ptr(mean), _lib.ptr(invstd), _lib.ptr(stats), n, h, w, cout, cin,
+                                 _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"conv3x3_dgrad_fused failed ({rc})")
+    _lib.count(1)
+    return dx, stats
+
+
 class FlippedWeights:
     """Flipped filters of all native convolutions of a model, refreshed by ONE kernel per step.
 
@@ -181,8 +238,16 @@ def set_active_flips(f):
 
 class _Conv3x3Fn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, want_stats=False):
-        ctx.save_for_backward(x, weight)
+    def forward(ctx, x, weight, want_stats=False, fold_res=False):
+        # x is the output of a batch-norm + ReLU of this step: its backward sums can be produced by
+        # this convolution's input-gradient epilogue
+        ent = FUSION.bn_of_output.get(x.data_ptr()) if FUSION.enabled else None
+        ctx.bn_in = ent is not None and ent[0].shape == x.shape
+        ctx.fold_res = bool(fold_res)
+        if ctx.bn_in:
+            ctx.save_for_backward(x, weight, ent[1], ent[2], ent[3])
+        else:
+            ctx.save_for_backward(x, weight)
         ctx.set_materialize_grads(False)  # no zero-filled gradient tensor for the statistics output
         if want_stats:
             y, stats = conv3x3_with_stats(x, weight, weight.shape[0])
@@ -193,13 +258,13 @@ class _Conv3x3Fn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, _dstats=None):
         if dy is None:
-            return None, None, None
+            return None, None, None, None
         dx, dw = _Conv3x3Fn._backward(ctx, dy)
-        return dx, dw, None
+        return dx, dw, None, None
 
     @staticmethod
     def _backward(ctx, dy):
-        x, weight = ctx.saved_tensors
+        x, weight = ctx.saved_tensors[:2]
         lib = _declare()
         dy = dy.contiguous(memory_format=torch.channels_last)
         cout, cin = weight.shape[0], weight.shape[1]
@@ -225,7 +290,16 @@ class _Conv3x3Fn(torch.autograd.Function):
                 rc = lib.conv_flip_weights(_lib.ptr(weight), _lib.ptr(flipped), cout, cin, _lib.stream_ptr())
                 if rc != 0:
                     raise RuntimeError(f"conv_flip_weights failed ({rc})")
-            dx = conv3x3(dy, flipped, cin)
+            add = FUSION.pending_res.pop(x.data_ptr(), None) if ctx.fold_res else None
+            if ctx.bn_in or add is not None:
+                bn = ctx.saved_tensors[2:5] if ctx.bn_in else None
+                dx, stats = conv3x3_dgrad_fused(dy, flipped, cin, add=add[1] if add is not None else None,
+                                                mask=x if ctx.bn_in else None, bn=bn)
+                if stats is not None:
+                    FUSION.masked[dx.data_ptr()] = (dx, stats)
+                    FUSION.clear_after_backward()
+            else:
+                dx = conv3x3(dy, flipped, cin)
         return dx, dw
 
 
@@ -372,7 +446,7 @@ class _ConvFirstFn(torch.autograd.Function):
         return None, dw, None
 
 
-def conv2d_native(m, x, want_stats=False):
+def conv2d_native(m, x, want_stats=False, fold_res=False):
     if m.in_channels == 3:
         return _ConvFirstFn.apply(x, m.weight, want_stats)
-    return _Conv3x3Fn.apply(x, m.weight, want_stats)
+    return _Conv3x3Fn.apply(x, m.weight, want_stats, fold_res)

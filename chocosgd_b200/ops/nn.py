@@ -31,10 +31,10 @@ def available_kinds():
 
 
 #: kinds switched on by ``auto``: the ones measured faster than the library op inside a training
-#: step.  ``linear`` (tcgen05 GEMM at about half of the library's TF32 throughput on large
-#: shapes) and ``lstm`` (per-timestep cell kernels against the library's persistent kernel) are
-#: opt-in through ``set_native`` / ``--native_layers all``.
-AUTO_KINDS = ("bn", "conv", "wgrad", "ce")
+#: step.  ``linear`` takes only layers large enough to fill the machine (the language model's
+#: decoder: fp32-grade products on the TF32 tensor cores against the library's fp32 FMA GEMM);
+#: ``lstm`` (persistent recurrence kernels) is opt-in through ``set_native`` / ``--native_layers all``.
+AUTO_KINDS = ("bn", "conv", "wgrad", "ce", "linear")
 
 
 def configure_native(mode: str = "auto"):
@@ -60,7 +60,7 @@ def native_enabled(kind: str) -> bool:
 
 class Linear(nn.Linear):
     def forward(self, x):
-        if _NATIVE["linear"] and x.is_cuda and x.dtype == torch.float32:
+        if _NATIVE["linear"] and x.is_cuda and x.dtype == torch.float32 and not torch.is_autocast_enabled():
             from .gemm import linear_native, linear_supported
 
             if linear_supported(x, self.weight):

@@ -93,6 +93,10 @@ class TrainStep:
 
             self.flips.refresh()  # one kernel: flipped filters of every native convolution
             set_active_flips(self.flips)
+        if self.flips is not None:
+            from ..ops.conv import FUSION
+
+            FUSION.clear()   # hand-over tables between layers are per step
         if self.bn_counters is not None and self.model.training:
             self.bn_counters.tick()  # one add for all batch-norm step counters
         if self.fused:
@@ -106,9 +110,17 @@ class TrainStep:
                 out, new_h = self.model(self.static_input, h)
                 logits, tgt = out.reshape(-1, out.size(-1)), self.static_target.reshape(-1)
             else:
-                out = self.model(self.static_input)
+                fused_head = None
+                if self._fused_ce and self.amp_dtype is None and hasattr(self.model, "head_loss"):
+                    feat = self.model.forward_features(self.static_input)
+                    fused_head = self.model.head_loss(feat, self.static_target)
+                    out = None if fused_head is not None else self.model.classify(feat)
+                else:
+                    out = self.model(self.static_input)
                 logits, tgt = out, self.static_target
-            if self._fused_ce and logits.dim() == 2 and ce_supported(logits, tgt):
+            if self.hidden is None and fused_head is not None:
+                loss, stats = fused_head          # pooling + classifier + loss + accuracies: one kernel
+            elif self._fused_ce and logits.dim() == 2 and ce_supported(logits, tgt):
                 loss, stats = fused_cross_entropy(logits, tgt, True)  # loss, gradient, accuracies: one kernel
             else:
                 loss = self.criterion(logits, tgt)

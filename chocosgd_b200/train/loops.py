@@ -161,12 +161,30 @@ def validate(conf, graph, run, model, optimizer, criterion, scheduler, metrics, 
 
     if (conf.graph_topology != "complete" and not conf.train_fast and conf.evaluate_consensus
             and force_evaluate_on_averaged_model):
-        copied = copy.deepcopy(model)
-        optimizer.world_aggregator.agg_model(copied, op="avg")
-        _evaluate(copied, label="averaged_model")
+        arena = getattr(optimizer, "arena", None)
+        if arena is not None and arena.x.is_cuda:
+            # flat arena: ONE all-reduce gives the world-averaged parameters, the distance kernel the
+            # consensus error ||x_i - x_bar||_2, and the averaged model is evaluated in place (the
+            # local parameters are put back afterwards) - no model copy, no per-tensor collectives
+            from ..parallel.exchange import sq_distance
+
+            optimizer.finalize()
+            x_local = arena.x.clone()
+            x_bar = optimizer.world_aggregator._agg(arena.x.clone(), op="avg")
+            distance = float(sq_distance(x_local, x_bar).sqrt())
+            arena.x.copy_(x_bar)
+            try:
+                _evaluate(model, label="averaged_model")
+            finally:
+                arena.x.copy_(x_local)
+        else:
+            copied = copy.deepcopy(model)
+            optimizer.world_aggregator.agg_model(copied, op="avg")
+            _evaluate(copied, label="averaged_model")
+            distance = get_model_difference(model, copied)
         run.logger.log_metric(
             name="stat",
-            values={"rank": graph.rank, "epoch": scheduler.epoch_, "distance": get_model_difference(model, copied)},
+            values={"rank": graph.rank, "epoch": scheduler.epoch_, "distance": distance},
             tags={"split": "test", "type": "averaged_model"},
         )
     return _evaluate(model, label=label)

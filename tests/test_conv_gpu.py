@@ -163,3 +163,57 @@ def test_first_layer_convolution(n, h, w, cout):
     torch.testing.assert_close(tot[:cout], y.double().sum(dim=(0, 2, 3)), rtol=1e-4, atol=1e-2)
     torch.testing.assert_close(tot[cout:], (y.double() ** 2).sum(dim=(0, 2, 3)), rtol=1e-4, atol=1e-2)
     assert stats.shape[0] * 2 * cout <= 8192
+
+
+def test_residual_blocks_with_fused_backward_epilogues():
+    """Two identity blocks behind a stem: with the hand-over between layers (skip gradient added,
+    ReLU mask applied and batch-norm backward sums taken in the input-gradient epilogue) every
+    gradient equals the one of the same native kernels with self-contained layer backwards."""
+    from chocosgd_b200.models.resnet import BasicBlock
+    from chocosgd_b200.models import layers as L
+    from chocosgd_b200.ops import _lib
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.conv import FUSION, last_error
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv1 = L.Conv2d(16, 32, 3, padding=1, bias=False)
+            self.bn1 = L.BatchNorm2d(32)
+            self.b1, self.b2 = BasicBlock(32, 32), BasicBlock(32, 32)
+
+        def forward(self, x):
+            return self.b2(self.b1(L.conv_bn_act(self.conv1, self.bn1, x)))
+
+    torch.manual_seed(5)
+    net = Net().cuda().to(memory_format=torch.channels_last)
+    for m in net.modules():
+        if isinstance(m, torch.nn.BatchNorm2d):
+            m.weight.data.uniform_(0.5, 1.5)
+            m.bias.data.uniform_(-0.3, 0.3)
+    x = torch.randn(32, 16, 16, 16, device="cuda").contiguous(memory_format=torch.channels_last).requires_grad_()
+    g = torch.randn(32, 32, 16, 16, device="cuda").contiguous(memory_format=torch.channels_last)
+    params = [p for p in net.parameters()]
+    nnn.set_native(True, which=("conv", "wgrad", "bn"))
+    results = {}
+    try:
+        for fused in (True, False):
+            FUSION.enabled = fused
+            FUSION.clear()
+            net.train()
+            n0 = _lib.LAUNCHES[0]
+            out = net(x)
+            grads = torch.autograd.grad(out, [x] + params, g)
+            torch.cuda.synchronize()
+            results[fused] = (out, grads, _lib.LAUNCHES[0] - n0)
+    finally:
+        FUSION.enabled = True
+        FUSION.clear()
+        nnn.set_native(False)
+    assert last_error() == 0
+    (out_f, gf, n_f), (out_u, gu, n_u) = results[True], results[False]
+    assert torch.equal(out_f, out_u)
+    for a, b in zip(gf, gu):
+        assert (a - b).abs().max().item() <= 2e-4 * b.abs().max().item() + 1e-6
+    # 5 batch-norm reductions (stem, b1.bn1, b1.bn2, b2.bn1; b2.bn2 has no native consumer: 4) fold away
+    assert n_u - n_f == 4, (n_u, n_f)

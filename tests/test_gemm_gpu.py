@@ -52,23 +52,56 @@ def test_gemm_split_k():
     _check(128, 128, 4096, False, False, split_k=4)
 
 
-def test_linear_native_matches_torch():
+def test_linear_native_matches_torch(monkeypatch):
+    """Native Linear (forward, input gradient, weight gradient on the tcgen05 GEMM with split operands):
+    row lengths that are not multiples of four, ragged tiles, fp32-grade accuracy against float64."""
+    from chocosgd_b200.ops import gemm as G
     from chocosgd_b200.ops import nn as nnn
 
+    monkeypatch.setattr(G, "MIN_NATIVE_WORK", 0)
     torch.manual_seed(0)
-    lin = nnn.Linear(512, 256).cuda()
-    x = torch.randn(96, 512, device="cuda", requires_grad=True)
-    y_ref = torch.nn.functional.linear(x, lin.weight, lin.bias)
-    g = torch.randn_like(y_ref)
-    gx_ref, gw_ref, gb_ref = torch.autograd.grad(y_ref, (x, lin.weight, lin.bias), g)
-    nnn.set_native(True, which=("linear",))
-    try:
-        y = lin(x)
-        gx, gw, gb = torch.autograd.grad(y, (x, lin.weight, lin.bias), g)
-    finally:
-        nnn.set_native(False)
-    for a, b in ((y, y_ref), (gx, gx_ref), (gw, gw_ref), (gb, gb_ref)):
-        assert (a - b).abs().max() <= 5e-3 * b.abs().max() + 1e-3
+    for (m, k, n) in ((96, 512, 256), (1120, 650, 1330), (35, 70, 333)):
+        lin = nnn.Linear(k, n).cuda()
+        x = torch.randn(m, k, device="cuda", requires_grad=True)
+        g = torch.randn(m, n, device="cuda")
+        xd, wd, bd = x.detach().double().requires_grad_(), lin.weight.detach().double().requires_grad_(), \
+            lin.bias.detach().double().requires_grad_()
+        y_ref = torch.nn.functional.linear(xd, wd, bd)
+        gx_ref, gw_ref, gb_ref = torch.autograd.grad(y_ref, (xd, wd, bd), g.double())
+        nnn.set_native(True, which=("linear",))
+        try:
+            y = lin(x)
+            assert y.shape == (m, n)
+            gx, gw, gb = torch.autograd.grad(y, (x, lin.weight, lin.bias), g)
+        finally:
+            nnn.set_native(False)
+        assert gw.is_contiguous() and gx.is_contiguous()
+        for a, b in ((y, y_ref), (gx, gx_ref), (gw, gw_ref), (gb, gb_ref)):
+            assert (a.double() - b).abs().max() <= 2e-5 * b.abs().max() + 1e-6, (m, k, n)
+    assert G.last_error() == 0
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_split_operands_reach_fp32_accuracy(a_mn, b_mn):
+    from chocosgd_b200.ops.gemm import gemm, gemm_x3, last_error, split_pad
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for (M, N, K, split_k) in ((300, 270, 650, 1), (2048, 2304, 332, 1), (130, 70, 4099, 4)):
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda", generator=g)
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda", generator=g)
+        ah, al = split_pad(a)
+        assert torch.equal(ah + al, a) and ah.stride(0) % 4 == 0
+        out = gemm_x3((ah, al), split_pad(b), a_mn=a_mn, b_mn=b_mn, split_k=split_k)
+        ref = _ref(a, b, a_mn, b_mn)
+        err = (out.double() - ref).abs().max().item()
+        # products carry 2^-21; the tensor core adds them in fp32 without rounding to nearest, so the
+        # error grows with K (1.4e-5 of the largest entry at K = 4099)
+        assert err <= 5e-5 * ref.abs().max().item(), (M, N, K, err)
+        if M % 4 == 0 and N % 4 == 0 and K % 4 == 0:     # one TF32 pass is three orders less accurate
+            err1 = (gemm(a, b, a_mn=a_mn, b_mn=b_mn).double() - ref).abs().max().item()
+            assert err1 > 20 * err
+    torch.cuda.synchronize()
+    assert last_error() == 0
 
 
 def test_gemm_persistent_variant():

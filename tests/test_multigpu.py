@@ -202,7 +202,9 @@ def _worker_leave(rank, world, port, out):
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    # no device_id: with one, torch creates the survivors' communicator by splitting the default one,
+    # which needs the rank that left; without it the new group makes its own rendez-vous (as main.py does)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
     from chocosgd_b200.optim import define_optimizer
     from chocosgd_b200.parallel.elastic import Membership, rebuild_optimizer
     from chocosgd_b200.parallel.topology import Graph
