@@ -154,11 +154,13 @@ struct ConvPArgs {
   const float* bn_mean;    // [C_out]
   const float* bn_invstd;  // [C_out]
   int* error;
-  int H, W, Cin;
+  int H, W, Cin;    // H, W: OUTPUT height and width (the tiles are tiles of the output)
   int TH, TN;
   int tiles_h;
   int n_tiles;
   int relu;
+  int taps;         // 9 (3x3, pad 1) or 1 (1x1, pad 0)
+  int stride;       // 1 or 2: the input tensor map then loads every second pixel of a twice as large box
 };
 
 // One CTA per SM has a single MMA-issuing thread and a single barrier round trip per pipeline
@@ -216,8 +218,10 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cblocks = g.Cin / KC;
-  const int n_kb = 9 * cblocks;
-  const int n_grp = n_kb / GK;                  // slots per tile (9 cblocks is a multiple of GK)
+  const int n_kb = g.taps * cblocks;
+  const int gk = n_kb < GK ? n_kb : GK;         // k-blocks per slot (a 1x1 filter has fewer than GK in all)
+  const int n_grp = n_kb / gk;                  // slots per tile (9 cblocks is a multiple of GK)
+  const int pad = g.taps == 9 ? 1 : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -253,18 +257,20 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       if (lane == 0) {
         if (gi >= (uint32_t)S && !mbar_wait(empty + s, ((gi / S) - 1) & 1)) ok = 0;
         if (*abort_flag) ok = 0;
-        if (ok) mbar_expect_tx(full + s, GK * (A_BYTES + B_BYTES));
+        if (ok) mbar_expect_tx(full + s, gk * (A_BYTES + B_BYTES));
         else *abort_flag = 1;
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      if (lane < GK) {
+      if (lane < gk) {
         const int tile = (int)blockIdx.x + (int)(gi / n_grp) * (int)gridDim.x;
-        const int i = (int)(gi % n_grp) * GK + lane;
+        const int i = (int)(gi % n_grp) * gk + lane;
         const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
         const int tap = i / cblocks, c0 = (i % cblocks) * KC;
-        const int r = tap / 3, t = tap % 3;
-        tma_load_4d(sA + (s * GK + lane) * A_BYTES, &map_x, full + s, c0, t - 1, h0 + r - 1, n0);
+        const int r = g.taps == 9 ? tap / 3 : 0, t = g.taps == 9 ? tap % 3 : 0;
+        // input coordinates of the tile's first output pixel under filter tap (r, t); with stride 2
+        // the box covers 2 W x 2 TH input pixels of which the map's element strides keep every second
+        tma_load_4d(sA + (s * GK + lane) * A_BYTES, &map_x, full + s, c0, t - pad, g.stride * h0 + r - pad, n0);
         tma_load_2d(sB + (s * GK + lane) * B_BYTES, &map_w, full + s, tap * g.Cin + c0, 0);
       }
       __syncwarp();
@@ -284,6 +290,7 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < GK; ++j) {
+          if (j >= gk) break;
           const uint32_t a_addr = smem_u32(sA + (s * GK + j) * A_BYTES), b_addr = smem_u32(sB + (s * GK + j) * B_BYTES);
 #pragma unroll
           for (int k = 0; k < KC / 8; ++k)
@@ -574,7 +581,25 @@ struct ConvBwdEpilogue {
 };
 
 static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N, int H, int W, int Cin, int Cout,
-                       int relu, cudaStream_t st, const ConvBwdEpilogue* bwd = nullptr);
+                       int relu, cudaStream_t st, const ConvBwdEpilogue* bwd = nullptr, int ks = 3, int stride = 1);
+
+// 1 when conv_fwd_tf32 handles a ks x ks convolution (3x3 pad 1 or 1x1 pad 0) of the given stride
+// whose OUTPUT is [N, HO, WO, Cout]
+extern "C" int conv_fwd_supported(int N, int HO, int WO, int Cin, int Cout, int ks, int stride) {
+  if (!(ks == 3 || ks == 1) || !(stride == 1 || stride == 2)) return 0;
+  if (stride * WO > 256) return 0;   // a TMA box is at most 256 elements wide before the element stride
+  return conv3x3_supported(N, HO, WO, Cin, Cout);
+}
+
+// General forward: x [N, stride HO, stride WO, Cin], w [Cout, ks, ks, Cin], y [N, HO, WO, Cout]; stats
+// (optional) as in conv3x3_tf32_stats.  A strided convolution is the same implicit GEMM: the tensor map
+// of x gets element strides (1, stride, stride, 1), so the box of a filter tap delivers exactly the
+// input pixels of the tile's 128 output pixels, and nothing else changes in the kernel.
+extern "C" int conv_fwd_tf32(const void* x, const void* w, void* y, void* stats, int N, int HO, int WO, int Cin, int Cout,
+                             int ks, int stride, cudaStream_t st) {
+  if (!conv_fwd_supported(N, HO, WO, Cin, Cout, ks, stride)) return -1;
+  return conv3x3_run(x, w, y, stats, N, HO, WO, Cin, Cout, 0, st, nullptr, ks, stride);
+}
 
 // x [N,H,W,Cin], w [Cout,3,3,Cin], y [N,H,W,Cout], all fp32 NHWC / KRSC
 extern "C" int conv3x3_tf32(const void* x, const void* w, void* y, int N, int H, int W, int Cin, int Cout, int relu,
@@ -605,8 +630,10 @@ extern "C" int conv3x3_dgrad_fused(const void* dy, const void* w_flipped, void* 
 }
 
 static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N, int H, int W, int Cin, int Cout,
-                       int relu, cudaStream_t st, const ConvBwdEpilogue* bwd) {
+                       int relu, cudaStream_t st, const ConvBwdEpilogue* bwd, int ks, int stride) {
   if (!conv3x3_supported(N, H, W, Cin, Cout)) return -1;
+  const int taps = ks * ks;
+  const bool general = ks != 3 || stride != 1;
   int th = 128 / W;
   if (th > H) th = H;
   const int tn = 128 / (W * th);
@@ -614,15 +641,17 @@ static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N
   const CUtensorMapSwizzle sw = kc == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap mx, mw;
   {
-    cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
-    cuuint64_t str[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
-    cuuint32_t box[4] = {(cuuint32_t)kc, (cuuint32_t)W, (cuuint32_t)th, (cuuint32_t)tn};
-    int rc = tc_make_map(&mx, x, 4, dims, str, box, sw);
+    const cuuint64_t WI = (cuuint64_t)W * stride, HI = (cuuint64_t)H * stride;   // input extent
+    cuuint64_t dims[4] = {(cuuint64_t)Cin, WI, HI, (cuuint64_t)N};
+    cuuint64_t str[3] = {(cuuint64_t)Cin * 4, WI * Cin * 4, HI * WI * Cin * 4};
+    cuuint32_t box[4] = {(cuuint32_t)kc, (cuuint32_t)(W * stride), (cuuint32_t)(th * stride), (cuuint32_t)tn};
+    cuuint32_t est[4] = {1, (cuuint32_t)stride, (cuuint32_t)stride, 1};
+    int rc = tc_make_map(&mx, x, 4, dims, str, box, sw, est);
     if (rc) return rc;
   }
   {
-    cuuint64_t dims[2] = {(cuuint64_t)9 * Cin, (cuuint64_t)Cout};
-    cuuint64_t str[1] = {(cuuint64_t)9 * Cin * 4};
+    cuuint64_t dims[2] = {(cuuint64_t)taps * Cin, (cuuint64_t)Cout};
+    cuuint64_t str[1] = {(cuuint64_t)taps * Cin * 4};
     cuuint32_t box[2] = {(cuuint32_t)kc, (cuuint32_t)Cout};
     int rc = tc_make_map(&mw, w, 2, dims, str, box, sw);
     if (rc) return rc;
@@ -633,8 +662,9 @@ static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N
   if (g.error == nullptr) return -13;
   g.H = H; g.W = W; g.Cin = Cin; g.TH = th; g.TN = tn; g.tiles_h = H / th; g.relu = relu;
   const int tiles = (N / tn) * (H / th);
-  if (stats != nullptr || bwd != nullptr || conv_use_persistent()) {
+  if (stats != nullptr || bwd != nullptr || general || conv_use_persistent()) {
     ConvPArgs pg;
+    pg.taps = taps; pg.stride = stride;
     pg.y = g.y; pg.stats = reinterpret_cast<float*>(stats); pg.error = g.error;
     pg.add = pg.mask = pg.bnx = pg.bn_mean = pg.bn_invstd = nullptr;
     if (bwd != nullptr) {

@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(LRI_THREADS) logreg_iter_kernel(LogregIterArgs
   __shared__ double red[LRI_THREADS / 32];
   __shared__ unsigned hist[256];
   __shared__ unsigned long long sel_prefix;
-  __shared__ unsigned sel_need;
+  __shared__ unsigned sel_need, sel_equal;
   const int m = blockIdx.x, d = a.d, n = a.n;
   const double* xm = a.x_in + (size_t)m * d;
   const double* xhm = a.xh_in + (size_t)m * d;
@@ -205,15 +205,33 @@ __global__ void __launch_bounds__(LRI_THREADS) logreg_iter_kernel(LogregIterArgs
         if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
       }
       __syncthreads();
-      if (threadIdx.x == 0) {
-        unsigned above = 0;
-        int b = 255;
-        for (; b > 0; --b) {
-          if (above + hist[b] >= need) break;
-          above += hist[b];
+      if (threadIdx.x < 32) {
+        // lane l owns the bins 255 - 8 l ... 248 - 8 l (descending); the digit is the first bin, from
+        // the top, at which the running count reaches `need`
+        const int top = 255 - 8 * (int)threadIdx.x;
+        unsigned mine = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) mine += hist[top - q];
+        unsigned incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const unsigned v = __shfl_up_sync(0xffffffffu, incl, o);
+          if ((int)threadIdx.x >= o) incl += v;
         }
-        sel_prefix = prefix | ((unsigned long long)b << shift);
-        sel_need = need - above;
+        const unsigned excl = incl - mine;
+        const unsigned hit = __ballot_sync(0xffffffffu, incl >= need);
+        const int owner = hit ? __ffs(hit) - 1 : 31;
+        if ((int)threadIdx.x == owner) {
+          unsigned above = excl;
+          int b = top;
+          for (int q = 0; q < 7; ++q, --b) {
+            if (above + hist[b] >= need) break;
+            above += hist[b];
+          }
+          sel_prefix = prefix | ((unsigned long long)b << shift);
+          sel_need = need - above;
+          sel_equal = hist[b];
+        }
       }
       __syncthreads();
       prefix = sel_prefix;
@@ -222,14 +240,20 @@ __global__ void __launch_bounds__(LRI_THREADS) logreg_iter_kernel(LogregIterArgs
       __syncthreads();
     }
     // prefix = k-th largest key; `need` of the keys equal to it are kept (lowest indices first)
-    if (threadIdx.x == 0) {
-      unsigned taken = 0;
-      for (int j = 0; j < d; ++j) {
-        const unsigned long long key = (unsigned long long)__double_as_longlong(fabs(lri_v[j]));
-        if (key < prefix) lri_v[j] = 0.0;
-        else if (key == prefix) {
-          if (taken < need) ++taken;
-          else lri_v[j] = 0.0;
+    for (int j = threadIdx.x; j < d; j += LRI_THREADS) {
+      const unsigned long long key = (unsigned long long)__double_as_longlong(fabs(lri_v[j]));
+      if (key < prefix) lri_v[j] = 0.0;
+    }
+    if (need < sel_equal) {   // more entries tie with the threshold than may be kept (uniform over the CTA)
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        unsigned taken = 0;
+        for (int j = 0; j < d; ++j) {
+          const unsigned long long key = (unsigned long long)__double_as_longlong(fabs(lri_v[j]));
+          if (key == prefix && lri_v[j] != 0.0) {
+            if (taken < need) ++taken;
+            else lri_v[j] = 0.0;
+          }
         }
       }
     }

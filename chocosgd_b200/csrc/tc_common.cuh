@@ -100,13 +100,17 @@ static inline TcEncodeTiledFn tc_get_encode() {
 
 // fp32 tensor map of `rank` dims (dims[0] contiguous); strides_bytes has rank-1 entries
 static inline int tc_make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims,
-                              const cuuint64_t* strides_bytes, const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+                              const cuuint64_t* strides_bytes, const cuuint32_t* box, CUtensorMapSwizzle swizzle,
+                              const cuuint32_t* elem_strides = nullptr) {
   TcEncodeTiledFn enc = tc_get_encode();
   if (enc == nullptr) return -10;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return -11;
   for (int i = 0; i < rank - 1; ++i)
     if (strides_bytes[i] % 16 != 0) return -11;
+  // element strides e > 1: every e-th element of the box's extent is loaded (ceil(box / e) elements)
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  if (elem_strides != nullptr)
+    for (int i = 0; i < rank; ++i) estr[i] = elem_strides[i];
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), dims, strides_bytes,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

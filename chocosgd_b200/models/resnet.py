@@ -11,6 +11,16 @@ import torch.nn as nn
 from . import layers as L
 
 
+def _shortcut(downsample, x):
+    """The skip connection: identity, or the (1x1 convolution, batch-norm) pair run as one fused pair
+    (the convolution's epilogue yields the batch statistics)."""
+    if downsample is None:
+        return x
+    if isinstance(downsample, nn.Sequential) and len(downsample) == 2 and isinstance(downsample[1], nn.BatchNorm2d):
+        return L.conv_bn_act(downsample[0], downsample[1], x, relu=False)
+    return downsample(x)
+
+
 class BasicBlock(nn.Module):
     expansion = 1
 
@@ -25,7 +35,7 @@ class BasicBlock(nn.Module):
         self.stride = stride
 
     def forward(self, x):
-        residual = x if self.downsample is None else self.downsample(x)
+        residual = _shortcut(self.downsample, x)
         # identity blocks on the native kernels: the skip gradient is added inside conv1's
         # input-gradient kernel instead of by a separate add
         fold = self.downsample is None and self.training and L.fold_residual_ok(self.conv1, x) \
@@ -50,7 +60,7 @@ class Bottleneck(nn.Module):
         self.stride = stride
 
     def forward(self, x):
-        residual = x if self.downsample is None else self.downsample(x)
+        residual = _shortcut(self.downsample, x)
         out = L.conv_bn_act(self.conv1, self.bn1, x)
         out = L.conv_bn_act(self.conv2, self.bn2, out)
         return L.conv_bn_act(self.conv3, self.bn3, out, residual=residual)

@@ -196,9 +196,9 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True, fold_res=False):
 
     if (native_nn.native_enabled("conv") and native_nn.native_enabled("bn") and bn.training and x.is_cuda
             and bn.affine and bn.track_running_stats is not None and torch.is_grad_enabled()):
-        from .conv import conv2d_native, conv_supported, first_conv_supported
+        from .conv import any_conv_supported, conv2d_native
 
-        if ((conv_supported(conv, x) or first_conv_supported(conv, x)) and (conv.out_channels // 4) <= 256
+        if (any_conv_supported(conv, x) and (conv.out_channels // 4) <= 256
                 and 256 % (conv.out_channels // 4) == 0):
             y, stats = conv2d_native(conv, x, want_stats=True, fold_res=fold_res and residual is None)
             return bn_act(bn, y, residual, relu, stats=stats, fold_res=fold_res)

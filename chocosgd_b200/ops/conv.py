@@ -1,9 +1,11 @@
 """Native convolution path: 3x3 / stride 1 / pad 1 NHWC fp32 convolutions run the persistent
 tcgen05 implicit-GEMM kernel (``csrc/conv_sm100.cu``) for the forward pass (optionally with the
 batch-norm statistics of its output) and for the input gradient (same kernel on dy with the flipped
-filter).  Weight gradients: ``csrc/conv_wgrad16.cu`` for 16 channels, ``csrc/conv_wgrad_sm100.cu``
-(tcgen05, opt-in) or the library for 32 / 64 channels, forked onto a second stream.  The 3-channel
-first layer runs ``csrc/conv_first.cu``.  Strided and 1x1 convolutions use the library."""
+filter).  Weight gradients: ``csrc/conv_wgrad16.cu`` for 16 channels, ``csrc/conv_wgrad_gen.cu`` for 32 / 64
+channels and for the strided layers (``csrc/conv_wgrad_sm100.cu``, tcgen05, is opt-in), forked onto a
+second stream.  The 3-channel first layer runs ``csrc/conv_first.cu``.  Strided 3x3 and 1x1
+convolutions (first convolution of a stage, down-sampling shortcut) run the same persistent kernel
+through a tensor map with element strides."""
 from __future__ import annotations
 
 import ctypes
@@ -46,6 +48,14 @@ def _declare():
         lib.conv3x3_wgrad16_supported.restype = i
         lib.conv3x3_dgrad_fused.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, vp]
         lib.conv3x3_dgrad_fused.restype = i
+        lib.conv_fwd_supported.argtypes = [i, i, i, i, i, i, i]
+        lib.conv_fwd_supported.restype = i
+        lib.conv_fwd_tf32.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, vp]
+        lib.conv_fwd_tf32.restype = i
+        lib.conv_wgrad_gen_parts.argtypes = [i, i, i, i, i, i, i]
+        lib.conv_wgrad_gen_parts.restype = i
+        lib.conv_wgrad_gen.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, vp]
+        lib.conv_wgrad_gen.restype = i
         lib._conv_declared = True
     return lib
 
@@ -97,17 +107,40 @@ def last_error() -> int:
     return lib.conv3x3_last_error() | lib.conv3x3_wgrad_last_error()
 
 
+def _wgrad_tcgen05() -> bool:
+    # 32 / 64 channels: the tcgen05 weight-gradient kernel is opt-in (CHOCO_WGRAD_TCGEN05=1); it
+    # measures 34 / 27 us against 26 / 23 us of the library kernels on the ResNet-20 shapes
+    return os.environ.get("CHOCO_WGRAD_TCGEN05", "0") == "1"
+
+
 def wgrad_supported(n, h, w, cin, cout) -> bool:
-    """True when a native weight-gradient kernel covers the shape: tcgen05 for 32 / 64 channels,
-    the warp-level tensor-core kernel for 16 channels."""
+    """True when a native weight-gradient kernel covers a 3x3 / stride 1 shape: the warp-level
+    tensor-core kernels (``conv_wgrad16.cu`` for 16 channels, ``conv_wgrad_gen.cu`` for 32 / 64) or,
+    opt-in, the tcgen05 kernel."""
     lib = _declare()
     if cin == cout == 16:
         return bool(lib.conv3x3_wgrad16_supported(n, h, w))
-    # 32 / 64 channels: the tcgen05 weight-gradient kernel is opt-in (CHOCO_WGRAD_TCGEN05=1); it
-    # measures 34 / 27 us against 26 / 23 us of the library kernels on the ResNet-20 shapes
-    if os.environ.get("CHOCO_WGRAD_TCGEN05", "0") != "1":
-        return False
-    return bool(lib.conv3x3_wgrad_supported(n, h, w, cin, cout))
+    if _wgrad_tcgen05():
+        return bool(lib.conv3x3_wgrad_supported(n, h, w, cin, cout))
+    return lib.conv_wgrad_gen_parts(n, h, w, cin, cout, 3, 1) > 0
+
+
+def conv_wgrad_gen(x, dy, weight, ks, stride):
+    """dW of a 3x3 (pad 1) or 1x1 (pad 0) convolution of stride 1 or 2 (``csrc/conv_wgrad_gen.cu``)."""
+    lib = _declare()
+    n, cin = x.shape[0], x.shape[1]
+    cout, ho, wo = dy.shape[1], dy.shape[2], dy.shape[3]
+    parts = lib.conv_wgrad_gen_parts(n, ho, wo, cin, cout, ks, stride)
+    if parts <= 0:
+        raise RuntimeError("conv_wgrad_gen: shape not covered")
+    dw = torch.empty_like(weight)
+    scratch = torch.empty(parts * weight.numel(), dtype=torch.float32, device=x.device)
+    rc = lib.conv_wgrad_gen(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, ho, wo, cin, cout, ks, stride,
+                            _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"conv_wgrad_gen failed ({rc})")
+    _lib.count(2)
+    return dw
 
 
 def conv3x3_wgrad(x, dy, weight):
@@ -122,6 +155,8 @@ def conv3x3_wgrad(x, dy, weight):
             raise RuntimeError(f"conv3x3_wgrad16 failed ({rc})")
         _lib.count(2)
         return dw
+    if not _wgrad_tcgen05():
+        return conv_wgrad_gen(x, dy, weight, 3, 1)
     scratch = torch.empty(lib.conv3x3_wgrad_parts(n, h, w) * 9 * c * c, dtype=torch.float32, device=x.device)
     rc = lib.conv3x3_wgrad_tf32(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, h, w, c,
                                 _lib.stream_ptr())
@@ -303,6 +338,79 @@ class _Conv3x3Fn(torch.autograd.Function):
         return dx, dw
 
 
+def gen_conv_supported(m, x) -> bool:
+    """Strided 3x3 (pad 1) and 1x1 (pad 0) convolutions between 16 / 32 / 64 / 128 channels: the first
+    convolution of a ResNet stage and its down-sampling shortcut."""
+    if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 4 and m.weight.dtype == torch.float32):
+        return False
+    ks, st = m.kernel_size[0], m.stride[0]
+    if m.kernel_size != (ks, ks) or m.stride != (st, st) or ks not in (1, 3) or st not in (1, 2) or (ks == 3 and st == 1):
+        return False
+    if m.padding != (ks // 2, ks // 2) or m.dilation != (1, 1) or m.groups != 1 or m.bias is not None:
+        return False
+    if m.padding_mode != "zeros":
+        return False
+    if not (x.is_contiguous(memory_format=torch.channels_last) and m.weight.is_contiguous(memory_format=torch.channels_last)):
+        return False
+    n, c, h, w = x.shape
+    if h % st or w % st:
+        return False
+    return bool(_declare().conv_fwd_supported(n, h // st, w // st, c, m.out_channels, ks, st))
+
+
+class _ConvGenFn(torch.autograd.Function):
+    """Strided 3x3 / 1x1 convolution: forward on the persistent tcgen05 kernel (strided tensor map),
+    weight gradient on ``conv_wgrad_gen.cu``."""
+
+    @staticmethod
+    def forward(ctx, x, weight, ks, stride, want_stats=False):
+        lib = _declare()
+        n, cin, h, w = x.shape
+        cout, ho, wo = weight.shape[0], h // stride, w // stride
+        ctx.save_for_backward(x, weight)
+        ctx.geom = (ks, stride)
+        ctx.set_materialize_grads(False)
+        y = torch.empty((n, cout, ho, wo), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+        stats = None
+        if want_stats:
+            stats = torch.empty((lib.conv3x3_grid(n, ho, wo, cout), 2 * cout), dtype=torch.float32, device=x.device)
+        rc = lib.conv_fwd_tf32(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), _lib.ptr(stats), n, ho, wo, cin, cout, ks,
+                               stride, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"conv_fwd_tf32 failed ({rc})")
+        _lib.count(1)
+        if want_stats:
+            ctx.mark_non_differentiable(stats)
+            return y, stats
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, _dstats=None):
+        if dy is None:
+            return None, None, None, None, None
+        x, weight = ctx.saved_tensors
+        ks, stride = ctx.geom
+        lib = _declare()
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        n, cin, h, w = x.shape
+        cout = weight.shape[0]
+        geom = ((stride, stride), (ks // 2, ks // 2), (1, 1), False, (0, 0), 1)
+        dx = dw = None
+        from . import nn as native_nn
+
+        if ctx.needs_input_grad[1]:
+            if native_nn.native_enabled("wgrad") and lib.conv_wgrad_gen_parts(n, h // stride, w // stride, cin, cout, ks,
+                                                                            stride) > 0:
+                fn = lambda: conv_wgrad_gen(x, dy, weight, ks, stride)
+            else:
+                fn = lambda: torch.ops.aten.convolution_backward(dy, x, weight, None, *geom, (False, True, False))[1]
+            fork = _WGRAD_STREAM.enabled and weight.grad is None and not torch.is_grad_enabled()
+            dw = _WGRAD_STREAM.run(fn, (x, dy), x.device) if fork else fn()
+        if ctx.needs_input_grad[0]:
+            dx = torch.ops.aten.convolution_backward(dy, x, weight, None, *geom, (True, False, False))[0]
+        return dx, dw, None, None, None
+
+
 class _WgradStream:
     """Weight gradients on a second stream.
 
@@ -449,4 +557,11 @@ class _ConvFirstFn(torch.autograd.Function):
 def conv2d_native(m, x, want_stats=False, fold_res=False):
     if m.in_channels == 3:
         return _ConvFirstFn.apply(x, m.weight, want_stats)
+    if m.stride != (1, 1) or m.kernel_size != (3, 3):
+        return _ConvGenFn.apply(x, m.weight, m.kernel_size[0], m.stride[0], want_stats)
     return _Conv3x3Fn.apply(x, m.weight, want_stats, fold_res)
+
+
+def any_conv_supported(m, x) -> bool:
+    """True when one of the native convolution kernels covers the layer for this input."""
+    return conv_supported(m, x) or first_conv_supported(m, x) or gen_conv_supported(m, x)

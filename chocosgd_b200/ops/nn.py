@@ -71,9 +71,9 @@ class Linear(nn.Linear):
 class Conv2d(nn.Conv2d):
     def forward(self, x):
         if _NATIVE["conv"] and x.is_cuda:
-            from .conv import conv2d_native, conv_supported, first_conv_supported
+            from .conv import any_conv_supported, conv2d_native
 
-            if conv_supported(self, x) or first_conv_supported(self, x):
+            if any_conv_supported(self, x):
                 return conv2d_native(self, x)
         return super().forward(x)
 

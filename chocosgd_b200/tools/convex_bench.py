@@ -1,4 +1,4 @@
-"""Convex plumbing run on the CPU: L2-regularised logistic regression (lambda = 1/N) with CHOCO-SGD
+"""Convex plumbing run on the CPU (``--device cuda``: the same recurrences with one kernel per iteration): L2-regularised logistic regression (lambda = 1/N) with CHOCO-SGD
 (top-k, k = 1 % of d) against exact decentralized SGD, 9 simulated nodes on a ring, synthetic data
 (``convex_code/logistic.py``, ``convex_code/experiment_epsilon_final.py:24-60``).
 
@@ -17,6 +17,7 @@ def main(argv=None):
     p.add_argument("--features", type=int, default=2000)
     p.add_argument("--nodes", type=int, default=9)
     p.add_argument("--epochs", type=int, default=2)
+    p.add_argument("--device", default="cpu", help="cpu (numpy) or cuda (one kernel per simulator iteration)")
     a = p.parse_args(argv)
     from ..convex import LogisticDecentralizedSGD, Parameters
     from ..convex.data import synthetic_logistic
@@ -29,12 +30,12 @@ def main(argv=None):
                          estimate="final", n_cores=a.nodes, topology="ring", distribute_data=True,
                          split_data_strategy="random", method=method, quantization=quant, random_seed=1,
                          split_data_random_seed=1, **extra)
-        m = LogisticDecentralizedSGD(prm)
+        m = LogisticDecentralizedSGD(prm, device=a.device)
         t0 = time.time()
         m.fit(A, y)
         dt = time.time() - t0
         iters = a.epochs * n // a.nodes
-        print(json.dumps({"bench": "convex", "samples": n, "features": d, "nodes": a.nodes, "topology": "ring",
+        print(json.dumps({"bench": "convex", "device": a.device, "samples": n, "features": d, "nodes": a.nodes, "topology": "ring",
                           "epochs": a.epochs, "method": method, "quantization": quant, "k": k if quant == "top" else None,
                           "seconds": round(dt, 2), "iterations": iters,
                           "us_per_iteration_all_nodes": round(1e6 * dt / iters, 1),

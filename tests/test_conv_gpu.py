@@ -48,6 +48,10 @@ def test_unsupported_shapes_fall_back():
     assert not conv_supported(conv, x)
     s2 = nnn.Conv2d(16, 32, 3, stride=2, padding=1, bias=False).cuda().to(memory_format=torch.channels_last)
     assert not conv_supported(s2, torch.randn(2, 16, 32, 32, device="cuda").contiguous(memory_format=torch.channels_last))
+    from chocosgd_b200.ops.conv import any_conv_supported
+
+    odd = nnn.Conv2d(24, 32, 3, padding=1, bias=False).cuda().to(memory_format=torch.channels_last)
+    assert not any_conv_supported(odd, torch.randn(2, 24, 32, 32, device="cuda").contiguous(memory_format=torch.channels_last))
 
 
 @pytest.mark.parametrize("n,cin,h,w,cout", SHAPES + [(128, 32, 16, 16, 32), (128, 64, 8, 8, 64)])
@@ -217,3 +221,62 @@ def test_residual_blocks_with_fused_backward_epilogues():
         assert (a - b).abs().max().item() <= 2e-4 * b.abs().max().item() + 1e-6
     # 5 batch-norm reductions (stem, b1.bn1, b1.bn2, b2.bn1; b2.bn2 has no native consumer: 4) fold away
     assert n_u - n_f == 4, (n_u, n_f)
+
+
+GEN_SHAPES = [  # n, cin, h, w (input), cout, ks, stride
+    (8, 16, 32, 32, 32, 3, 2), (128, 16, 32, 32, 32, 3, 2), (8, 32, 16, 16, 64, 3, 2), (128, 32, 16, 16, 64, 3, 2),
+    (8, 16, 32, 32, 32, 1, 2), (128, 16, 32, 32, 32, 1, 2), (6, 32, 16, 16, 64, 1, 2), (128, 32, 16, 16, 64, 1, 2),
+]
+
+
+@pytest.mark.parametrize("n,cin,h,w,cout,ks,stride", GEN_SHAPES)
+def test_strided_and_1x1_convolutions(n, cin, h, w, cout, ks, stride):
+    """First convolution of a stage (3x3 / 2) and the down-sampling shortcut (1x1 / 2): forward with the
+    batch statistics, weight gradient and input gradient against PyTorch fp32."""
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.conv import _ConvGenFn, gen_conv_supported, last_error
+
+    torch.manual_seed(3)
+    torch.backends.cudnn.allow_tf32 = False
+    conv = nnn.Conv2d(cin, cout, ks, stride=stride, padding=ks // 2, bias=False).cuda().to(memory_format=torch.channels_last)
+    x = torch.randn(n, cin, h, w, device="cuda").contiguous(memory_format=torch.channels_last).requires_grad_()
+    assert gen_conv_supported(conv, x)
+    ref = F.conv2d(x, conv.weight, stride=stride, padding=ks // 2)
+    g = torch.randn_like(ref)
+    gx_ref, gw_ref = torch.autograd.grad(ref, (x, conv.weight), g)
+    nnn.set_native(True, which=("conv", "wgrad"))
+    try:
+        out, stats = _ConvGenFn.apply(x, conv.weight, ks, stride, True)
+        gx, gw = torch.autograd.grad(out, (x, conv.weight), g)
+    finally:
+        nnn.set_native(False)
+        torch.backends.cudnn.allow_tf32 = True
+    torch.cuda.synchronize()
+    assert last_error() == 0
+    for a, b in ((out, ref), (gx, gx_ref), (gw, gw_ref)):
+        err = (a - b).abs().max().item()
+        assert err <= 5e-3 * b.abs().max().item() + 1e-3, (err, b.abs().max().item())
+    tot = stats.sum(0)
+    torch.testing.assert_close(tot[:cout], out.sum((0, 2, 3)), rtol=1e-3, atol=1e-2)
+    torch.testing.assert_close(tot[cout:], (out * out).sum((0, 2, 3)), rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("n,c,hw", [(8, 32, 16), (128, 32, 16), (8, 64, 8), (128, 64, 8), (3, 64, 8)])
+def test_wgrad_warp_kernel_32_64_channels(n, c, hw):
+    from chocosgd_b200.ops.conv import conv_wgrad_gen
+
+    torch.manual_seed(4)
+    x = torch.randn(n, c, hw, hw, device="cuda").contiguous(memory_format=torch.channels_last)
+    dy = torch.randn(n, c, hw, hw, device="cuda").contiguous(memory_format=torch.channels_last)
+    w = torch.zeros(c, c, 3, 3, device="cuda").contiguous(memory_format=torch.channels_last)
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        ref = torch.ops.aten.convolution_backward(dy, x, w, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1,
+                                                  (False, True, False))[1]
+    finally:
+        torch.backends.cudnn.allow_tf32 = True
+    a = conv_wgrad_gen(x, dy, w, 3, 1)
+    b = conv_wgrad_gen(x, dy, w, 3, 1)
+    assert torch.equal(a, b)                      # fixed-order reduction: bitwise reproducible
+    err = (a - ref).abs().max().item()
+    assert err <= 5e-3 * ref.abs().max().item() + 1e-3, (err, ref.abs().max().item())

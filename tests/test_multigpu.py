@@ -287,6 +287,6 @@ def test_rank_leaves_between_steps_and_the_rest_continue(world):
                     weight_decay=wd, momentum=0.9, nesterov=True, identical_init=False)
     sim.local.buf = [full.local.buf[r].clone() for r in survivors]
     for t in range(3, 6):
-        sim.step(lambda i, tt, x: grad_flat(survivors[i], tt, seg))
+        sim.step(lambda i, tt, x, t=t: grad_flat(survivors[i], t, seg))   # (the simulator's own clock restarts at 0)
     for i, r in enumerate(survivors):
         np.testing.assert_allclose(res[r]["x"], sim.x[i].numpy(), rtol=1e-4, atol=1e-5, err_msg=f"rank {r}")
