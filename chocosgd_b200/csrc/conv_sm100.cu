@@ -161,7 +161,22 @@ struct ConvPArgs {
   int relu;
   int taps;         // 9 (3x3, pad 1) or 1 (1x1, pad 0)
   int stride;       // 1 or 2: the input tensor map then loads every second pixel of a twice as large box
+  // mode 1: input gradient of a 3x3 / stride 2 / pad 1 convolution (plus, optionally, of the 1x1 / stride 2
+  // shortcut that reads the same tensor).  The result [N, 2H, 2W, C_out] is produced as four parity
+  // classes (row parity, column parity) of H x W pixels each; H, W, TH, TN, tiles_h describe ONE class,
+  // which has the geometry of dy.  A result pixel (2a + ph, 2b + pw) receives the filter taps (r, s) with
+  // r = 1 for ph = 0 and r in {0, 2} for ph = 1 (same for s / pw), each reading dy at (a + (ph + 1 - r) / 2,
+  // b + (pw + 1 - s) / 2): unit-stride boxes of dy, 1 / 2 / 2 / 4 taps for the four classes.
+  int mode;
+  int cb2;              // k-blocks of the shortcut's dy (class 0 only); 0 = no shortcut
+  int tiles_per_class;
 };
+
+// k-blocks (filter tap x KC-channel block) of a tile of parity class cls in mode 1
+__device__ __forceinline__ int s2_n_kb(int cls, int cblocks, int cb2) {
+  const int nt = ((cls >> 1) ? 2 : 1) * ((cls & 1) ? 2 : 1);
+  return nt * cblocks + (cls == 0 ? cb2 : 0);
+}
 
 // One CTA per SM has a single MMA-issuing thread and a single barrier round trip per pipeline
 // slot, so a slot holds GK k-blocks (all 9 filter taps for 16 channels, 3 otherwise): one wait,
@@ -196,7 +211,8 @@ __device__ __forceinline__ bool epi_bar_or(bool flag) {
 
 template <int COUT, int KC, bool BWD>
 __global__ void __launch_bounds__(CONV_THREADS, 1)
-conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ConvPArgs g) {
+conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                       const __grid_constant__ CUtensorMap map_x2, const __grid_constant__ CUtensorMap map_w2, ConvPArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using Cfg = ConvPCfg<COUT, KC, BWD>;
@@ -218,9 +234,7 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cblocks = g.Cin / KC;
-  const int n_kb = g.taps * cblocks;
-  const int gk = n_kb < GK ? n_kb : GK;         // k-blocks per slot (a 1x1 filter has fewer than GK in all)
-  const int n_grp = n_kb / gk;                  // slots per tile (9 cblocks is a multiple of GK)
+  const int n_kb0 = g.taps * cblocks;           // k-blocks per tile (mode 0); a pipeline slot holds up to GK of them
   const int pad = g.taps == 9 ? 1 : 0;
 
   if (threadIdx.x == 0) {
@@ -249,31 +263,53 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   pdl_trigger();
 
   if (warp == 4) {
-    const int my_tiles = (g.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const uint32_t total = (uint32_t)my_tiles * (uint32_t)n_grp;
-    for (uint32_t gi = 0; gi < total; ++gi) {
-      const uint32_t s = gi % S;
-      int ok = 1;
-      if (lane == 0) {
-        if (gi >= (uint32_t)S && !mbar_wait(empty + s, ((gi / S) - 1) & 1)) ok = 0;
-        if (*abort_flag) ok = 0;
-        if (ok) mbar_expect_tx(full + s, gk * (A_BYTES + B_BYTES));
-        else *abort_flag = 1;
+    uint32_t it = 0;
+    int ok = 1;
+    for (int tile = blockIdx.x; tile < g.n_tiles && ok; tile += gridDim.x) {
+      const int cls = g.mode ? tile / g.tiles_per_class : 0;
+      const int sub = g.mode ? tile % g.tiles_per_class : tile;
+      const int n0 = (sub / g.tiles_h) * g.TN, h0 = (sub % g.tiles_h) * g.TH;
+      const int n_kb = g.mode ? s2_n_kb(cls, cblocks, g.cb2) : n_kb0;
+      for (int g0 = 0; g0 < n_kb; g0 += GK, ++it) {
+        const uint32_t s = it % S;
+        const int cnt = n_kb - g0 < GK ? n_kb - g0 : GK;
+        if (lane == 0) {
+          if (it >= (uint32_t)S && !mbar_wait(empty + s, ((it / S) - 1) & 1)) ok = 0;
+          if (*abort_flag) ok = 0;
+          if (ok) mbar_expect_tx(full + s, cnt * (A_BYTES + B_BYTES));
+          else *abort_flag = 1;
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (lane < cnt) {
+          const int i = g0 + lane;
+          uint8_t* dA = sA + (s * GK + lane) * A_BYTES;
+          uint8_t* dB = sB + (s * GK + lane) * B_BYTES;
+          if (!g.mode) {
+            const int tap = i / cblocks, c0 = (i % cblocks) * KC;
+            const int r = g.taps == 9 ? tap / 3 : 0, t = g.taps == 9 ? tap % 3 : 0;
+            // input coordinates of the tile's first output pixel under filter tap (r, t); with stride 2
+            // the box covers 2 W x 2 TH input pixels of which the map's element strides keep every second
+            tma_load_4d(dA, &map_x, full + s, c0, t - pad, g.stride * h0 + r - pad, n0);
+            tma_load_2d(dB, &map_w, full + s, tap * g.Cin + c0, 0);
+          } else {
+            const int ph = cls >> 1, pw = cls & 1;
+            const int nts = pw ? 2 : 1, n_main = (ph ? 2 : 1) * nts * cblocks;
+            if (i < n_main) {
+              const int ti = i / cblocks, c0 = (i % cblocks) * KC;
+              const int r = ph ? ((ti / nts) ? 2 : 0) : 1, t = pw ? ((ti % nts) ? 2 : 0) : 1;
+              tma_load_4d(dA, &map_x, full + s, c0, (pw + 1 - t) >> 1, h0 + ((ph + 1 - r) >> 1), n0);
+              // the flipped filter holds forward tap (r, t) at index 8 - (3 r + t)
+              tma_load_2d(dB, &map_w, full + s, (8 - (3 * r + t)) * g.Cin + c0, 0);
+            } else {
+              const int c0 = (i - n_main) * KC;      // the shortcut: a 1x1 filter, class (0, 0) only
+              tma_load_4d(dA, &map_x2, full + s, c0, 0, h0, n0);
+              tma_load_2d(dB, &map_w2, full + s, c0, 0);
+            }
+          }
+        }
+        __syncwarp();
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      if (lane < gk) {
-        const int tile = (int)blockIdx.x + (int)(gi / n_grp) * (int)gridDim.x;
-        const int i = (int)(gi % n_grp) * gk + lane;
-        const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
-        const int tap = i / cblocks, c0 = (i % cblocks) * KC;
-        const int r = g.taps == 9 ? tap / 3 : 0, t = g.taps == 9 ? tap % 3 : 0;
-        // input coordinates of the tile's first output pixel under filter tap (r, t); with stride 2
-        // the box covers 2 W x 2 TH input pixels of which the map's element strides keep every second
-        tma_load_4d(sA + (s * GK + lane) * A_BYTES, &map_x, full + s, c0, t - pad, g.stride * h0 + r - pad, n0);
-        tma_load_2d(sB + (s * GK + lane) * B_BYTES, &map_w, full + s, tap * g.Cin + c0, 0);
-      }
-      __syncwarp();
     }
   } else if (warp == 5 && lane == 0) {
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(COUT >> 3) << 17) | ((128u >> 4) << 24);
@@ -284,18 +320,20 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       if (lt >= 2 && !mbar_wait(acc_empty + buf, ((lt >> 1) - 1) & 1)) { *abort_flag = 1; ok = false; break; }
       tc_fence_after();
       const uint32_t d = tmem_base + buf * COUT;
-      for (int gq = 0; gq < n_grp; ++gq, ++it) {
+      const int n_kb = g.mode ? s2_n_kb(tile / g.tiles_per_class, cblocks, g.cb2) : n_kb0;
+      for (int g0 = 0; g0 < n_kb; g0 += GK, ++it) {
         const uint32_t s = it % S;
+        const int cnt = n_kb - g0 < GK ? n_kb - g0 : GK;
         if (!mbar_wait(full + s, (it / S) & 1)) { *abort_flag = 1; ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int j = 0; j < GK; ++j) {
-          if (j >= gk) break;
+          if (j >= cnt) break;
           const uint32_t a_addr = smem_u32(sA + (s * GK + j) * A_BYTES), b_addr = smem_u32(sB + (s * GK + j) * B_BYTES);
 #pragma unroll
           for (int k = 0; k < KC / 8; ++k)
             umma_tf32(d, make_desc(a_addr + k * 32, 16, SBO, LAYOUT), make_desc(b_addr + k * 32, 16, SBO, LAYOUT), idesc,
-                      (gq > 0 || j > 0 || k > 0) ? 1u : 0u);
+                      (g0 > 0 || j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(empty + s);
       }
@@ -331,8 +369,10 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         break;
       }
       tc_fence_after();
-      const int n0 = (tile / g.tiles_h) * g.TN, h0 = (tile % g.tiles_h) * g.TH;
-      const size_t tile_off = (((size_t)n0 * g.H + h0) * g.W) * COUT;   // first float of the tile
+      const int cls = g.mode ? tile / g.tiles_per_class : 0;
+      const int sub = g.mode ? tile % g.tiles_per_class : tile;
+      const int n0 = (sub / g.tiles_h) * g.TN, h0 = (sub % g.tiles_h) * g.TH;
+      const size_t tile_off = (((size_t)n0 * g.H + h0) * g.W) * COUT;   // first float of the tile (mode 0)
       float* trow = sT + t128 * TS;
 #pragma unroll 1
       for (int c = 0; c < COUT; c += 16) {
@@ -359,7 +399,14 @@ conv3x3_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
           const int row = rb + u * RSTEP;
-          off[u] = tile_off + (size_t)row * COUT + c4 * 4;
+          if (!g.mode) {
+            off[u] = tile_off + (size_t)row * COUT + c4 * 4;
+          } else {
+            // row -> pixel (n, a, b) of the class image -> pixel (2a + ph, 2b + pw) of the result
+            const int b = row % g.W, a = (row / g.W) % g.TH, nn = row / (g.W * g.TH);
+            off[u] = ((((size_t)(n0 + nn) * (2 * g.H) + 2 * (h0 + a) + (cls >> 1)) * (2 * g.W)) + 2 * b + (cls & 1)) * COUT +
+                     c4 * 4;
+          }
           if (BWD) {
             if (g.add != nullptr) ra[u] = __ldg(reinterpret_cast<const float4*>(g.add + off[u]));
             if (g.mask != nullptr) rm[u] = __ldg(reinterpret_cast<const float4*>(g.mask + off[u]));
@@ -439,23 +486,26 @@ __global__ void conv_flip_weights_kernel(const float* __restrict__ w, float* __r
   }
 }
 
-// all registered layers in one launch: table[l] = {w, out, cout, cin}; gridDim.y = layer
+// all registered layers in one launch: table[l] = {w, out, cout, cin, taps}; gridDim.y = layer
+// (taps = 9: 3x3 filters; taps = 1: a 1x1 filter, i.e. a plain transpose)
 struct FlipEntry {
   const float* w;
   float* out;
-  int cout, cin;
+  int cout, cin, taps, pad_;
 };
 
 __global__ void conv_flip_weights_multi_kernel(const FlipEntry* __restrict__ table) {
   pdl_wait();
   pdl_trigger();
   const FlipEntry e = table[blockIdx.y];
-  const int total = e.cout * 9 * e.cin;
+  const int total = e.cout * e.taps * e.cin;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const int co = i % e.cout, tap = (i / e.cout) % 9, ci = i / (9 * e.cout);
-    e.out[i] = e.w[(co * 9 + (8 - tap)) * e.cin + ci];
+    const int co = i % e.cout, tap = (i / e.cout) % e.taps, ci = i / (e.taps * e.cout);
+    e.out[i] = e.w[(co * e.taps + (e.taps - 1 - tap)) * e.cin + ci];
   }
 }
+
+extern "C" int conv_flip_entry_size() { return (int)sizeof(FlipEntry); }
 
 extern "C" int conv_flip_weights_multi(const void* table, int n_layers, int max_elems, cudaStream_t st) {
   dim3 grid((max_elems + 255) / 256 > 64 ? 64 : (max_elems + 255) / 256, n_layers);
@@ -505,7 +555,8 @@ static int launch_conv(const CUtensorMap& mx, const CUtensorMap& mw, const ConvA
 }
 
 template <int COUT, int KC, bool BWD>
-static int launch_conv_persist_t(const CUtensorMap& mx, const CUtensorMap& mw, const ConvPArgs& g, int grid, cudaStream_t st) {
+static int launch_conv_persist_t(const CUtensorMap& mx, const CUtensorMap& mw, const ConvPArgs& g, int grid, cudaStream_t st,
+                                 const CUtensorMap* mx2 = nullptr, const CUtensorMap* mw2 = nullptr) {
   using Cfg = ConvPCfg<COUT, KC, BWD>;
   constexpr int smem = Cfg::STAGES * Cfg::GK * Cfg::KB_BYTES + Cfg::TILES * 128 * Cfg::TSTRIDE * 4 + 1024 + 512;
   static bool configured = false;
@@ -514,7 +565,9 @@ static int launch_conv_persist_t(const CUtensorMap& mx, const CUtensorMap& mw, c
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  launch_k(conv3x3_persist_kernel<COUT, KC, BWD>, dim3(grid), dim3(CONV_THREADS), smem, st, mx, mw, g);
+  // (the second pair of maps is read in mode 1 only: any valid map fills the slots otherwise)
+  launch_k(conv3x3_persist_kernel<COUT, KC, BWD>, dim3(grid), dim3(CONV_THREADS), smem, st, mx, mw,
+           mx2 != nullptr ? *mx2 : mx, mw2 != nullptr ? *mw2 : mw, g);
   return (int)cudaGetLastError();
 }
 
@@ -664,7 +717,7 @@ static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N
   const int tiles = (N / tn) * (H / th);
   if (stats != nullptr || bwd != nullptr || general || conv_use_persistent()) {
     ConvPArgs pg;
-    pg.taps = taps; pg.stride = stride;
+    pg.taps = taps; pg.stride = stride; pg.mode = 0; pg.cb2 = 0; pg.tiles_per_class = 0;
     pg.y = g.y; pg.stats = reinterpret_cast<float*>(stats); pg.error = g.error;
     pg.add = pg.mask = pg.bnx = pg.bn_mean = pg.bn_invstd = nullptr;
     if (bwd != nullptr) {
@@ -686,5 +739,102 @@ static int conv3x3_run(const void* x, const void* w, void* y, void* stats, int N
   if (Cout == CO) return kc == 32 ? launch_conv<CO, 32>(mx, mw, g, tiles, st) : launch_conv<CO, 16>(mx, mw, g, tiles, st);
   CONV_CASE(16) CONV_CASE(32) CONV_CASE(64) CONV_CASE(128)
 #undef CONV_CASE
+  return -1;
+}
+
+// ---- input gradient of the strided layers ---------------------------------------------------------
+static int conv_sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+  }
+  return sms;
+}
+
+// dy: [N, HO, WO, Cdy].  1 when conv3x3s2_dgrad_fused covers the shape.
+extern "C" int conv3x3s2_dgrad_supported(int N, int HO, int WO, int Cdy, int Cx, int Cdy2) {
+  if (!(Cx == 16 || Cx == 32 || Cx == 64) || Cdy % 32 != 0 || Cdy < 32 || Cdy > 128) return 0;
+  if (Cdy2 != 0 && (Cdy2 % 32 != 0 || Cdy2 > 128)) return 0;
+  return conv3x3_supported(N, HO, WO, Cdy, Cx);
+}
+
+// CTAs (= rows of statistics partials) of conv3x3s2_dgrad_fused
+extern "C" int conv3x3s2_dgrad_grid(int N, int HO, int WO, int Cx) {
+  int th = 128 / WO;
+  if (th > HO) th = HO;
+  const int tn = 128 / (WO * th);
+  if (tn < 1 || th < 1) return 0;
+  const int tiles = 4 * (N / tn) * (HO / th);
+  int g = tiles < conv_sm_count() ? tiles : conv_sm_count();
+  const int cap = 8192 / (2 * Cx);
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  const int per = (tiles + g - 1) / g;
+  return (tiles + per - 1) / per;
+}
+
+// Input gradient of y = conv3x3(x, w, stride 2, pad 1) and, when dy2 is given, of the shortcut
+// y2 = conv1x1(x, w2, stride 2) that reads the same x, in ONE launch:
+//   out[N, 2 HO, 2 WO, Cx] = dgrad(dy, w) + dgrad(dy2, w2)   then the same epilogue as conv3x3_dgrad_fused
+// w_flipped: [Cx, 9, Cdy] (conv_flip_weights of w); w2_t: [Cx, Cdy2] (w2 transposed).
+extern "C" int conv3x3s2_dgrad_fused(const void* dy, const void* w_flipped, const void* dy2, const void* w2_t, void* out,
+                                     const void* add, const void* mask, const void* bnx, const void* bn_mean,
+                                     const void* bn_invstd, void* stats, int N, int HO, int WO, int Cdy, int Cx, int Cdy2,
+                                     cudaStream_t st) {
+  if (dy2 == nullptr) Cdy2 = 0;
+  if (!conv3x3s2_dgrad_supported(N, HO, WO, Cdy, Cx, Cdy2)) return -1;
+  if ((bnx != nullptr) != (stats != nullptr)) return -1;
+  if (bnx != nullptr && (bn_mean == nullptr || bn_invstd == nullptr)) return -1;
+  if (Cdy2 != 0 && w2_t == nullptr) return -1;
+  int th = 128 / WO;
+  if (th > HO) th = HO;
+  const int tn = 128 / (WO * th);
+  constexpr int kc = 32;
+  const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  CUtensorMap mx, mw, mx2, mw2;
+  auto act_map = [&](CUtensorMap* m, const void* p, int C) {
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)WO, (cuuint64_t)HO, (cuuint64_t)N};
+    cuuint64_t str[3] = {(cuuint64_t)C * 4, (cuuint64_t)WO * C * 4, (cuuint64_t)HO * WO * C * 4};
+    cuuint32_t box[4] = {(cuuint32_t)kc, (cuuint32_t)WO, (cuuint32_t)th, (cuuint32_t)tn};
+    return tc_make_map(m, p, 4, dims, str, box, sw);
+  };
+  auto w_map = [&](CUtensorMap* m, const void* p, int K) {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Cx};
+    cuuint64_t str[1] = {(cuuint64_t)K * 4};
+    cuuint32_t box[2] = {(cuuint32_t)kc, (cuuint32_t)Cx};
+    return tc_make_map(m, p, 2, dims, str, box, sw);
+  };
+  int rc = act_map(&mx, dy, Cdy);
+  if (rc) return rc;
+  rc = w_map(&mw, w_flipped, 9 * Cdy);
+  if (rc) return rc;
+  if (Cdy2 != 0) {
+    rc = act_map(&mx2, dy2, Cdy2);
+    if (rc) return rc;
+    rc = w_map(&mw2, w2_t, Cdy2);
+    if (rc) return rc;
+  }
+  ConvPArgs pg;
+  pg.y = reinterpret_cast<float*>(out);
+  pg.stats = reinterpret_cast<float*>(stats);
+  pg.add = reinterpret_cast<const float*>(add);
+  pg.mask = reinterpret_cast<const float*>(mask);
+  pg.bnx = reinterpret_cast<const float*>(bnx);
+  pg.bn_mean = reinterpret_cast<const float*>(bn_mean);
+  pg.bn_invstd = reinterpret_cast<const float*>(bn_invstd);
+  pg.error = conv_error_word();
+  if (pg.error == nullptr) return -13;
+  pg.H = HO; pg.W = WO; pg.Cin = Cdy; pg.TH = th; pg.TN = tn; pg.tiles_h = HO / th;
+  pg.tiles_per_class = (N / tn) * (HO / th);
+  pg.n_tiles = 4 * pg.tiles_per_class;
+  pg.relu = 0; pg.taps = 9; pg.stride = 1; pg.mode = 1; pg.cb2 = Cdy2 / kc;
+  const int grid = conv3x3s2_dgrad_grid(N, HO, WO, Cx);
+  const CUtensorMap* p2 = Cdy2 != 0 ? &mx2 : nullptr;
+  const CUtensorMap* q2 = Cdy2 != 0 ? &mw2 : nullptr;
+  if (Cx == 16) return launch_conv_persist_t<16, 32, true>(mx, mw, pg, grid, st, p2, q2);
+  if (Cx == 32) return launch_conv_persist_t<32, 32, true>(mx, mw, pg, grid, st, p2, q2);
+  if (Cx == 64) return launch_conv_persist_t<64, 32, true>(mx, mw, pg, grid, st, p2, q2);
   return -1;
 }

@@ -31,12 +31,25 @@ def bn_act(bn, x, residual=None, relu=True):
     return _f(bn, x, residual, relu)
 
 
-def conv_bn_act(conv, bn, x, residual=None, relu=True, fold_res=False):
+def conv_bn_act(conv, bn, x, residual=None, relu=True, fold_res=False, fold_ds=False):
     """relu(bn(conv(x)) + residual); on the native path the convolution epilogue also yields the
     batch statistics, so no reduction pass runs over the activation."""
     from ..ops.bn import conv_bn_act as _f
 
-    return _f(conv, bn, x, residual, relu, fold_res)
+    return _f(conv, bn, x, residual, relu, fold_res, fold_ds)
+
+
+def fold_shortcut_ok(conv, shortcut, x) -> bool:
+    """Whether a down-sampling block's strided convolution ``conv`` can compute the input gradient of the
+    block's (1x1 convolution, batch-norm) ``shortcut`` in the same launch as its own."""
+    import torch.nn as nn
+
+    if not (x.is_cuda and isinstance(shortcut, nn.Sequential) and len(shortcut) == 2
+            and isinstance(shortcut[0], nn.Conv2d) and isinstance(shortcut[1], nn.BatchNorm2d)):
+        return False
+    from ..ops.conv import fold_shortcut_ok as _f
+
+    return _f(conv, shortcut[0], x)
 
 
 def fold_residual_ok(conv, x) -> bool:

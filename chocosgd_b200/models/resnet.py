@@ -11,13 +11,13 @@ import torch.nn as nn
 from . import layers as L
 
 
-def _shortcut(downsample, x):
+def _shortcut(downsample, x, fold_ds=False):
     """The skip connection: identity, or the (1x1 convolution, batch-norm) pair run as one fused pair
     (the convolution's epilogue yields the batch statistics)."""
     if downsample is None:
         return x
     if isinstance(downsample, nn.Sequential) and len(downsample) == 2 and isinstance(downsample[1], nn.BatchNorm2d):
-        return L.conv_bn_act(downsample[0], downsample[1], x, relu=False)
+        return L.conv_bn_act(downsample[0], downsample[1], x, relu=False, fold_ds=fold_ds)
     return downsample(x)
 
 
@@ -35,12 +35,15 @@ class BasicBlock(nn.Module):
         self.stride = stride
 
     def forward(self, x):
-        residual = _shortcut(self.downsample, x)
         # identity blocks on the native kernels: the skip gradient is added inside conv1's
         # input-gradient kernel instead of by a separate add
         fold = self.downsample is None and self.training and L.fold_residual_ok(self.conv1, x) \
             and L.fold_residual_ok(self.conv2, x)
-        out = L.conv_bn_act(self.conv1, self.bn1, x, fold_res=fold)
+        # down-sampling blocks: conv1's input-gradient kernel also computes the shortcut's
+        fold_ds = self.downsample is not None and self.training and L.fold_shortcut_ok(self.conv1, self.downsample, x)
+        out = L.conv_bn_act(self.conv1, self.bn1, x, fold_res=fold, fold_ds=fold_ds)
+        # (the shortcut is evaluated after conv1: autograd then runs its backward before conv1's)
+        residual = _shortcut(self.downsample, x, fold_ds)
         return L.conv_bn_act(self.conv2, self.bn2, out, residual=residual, fold_res=fold)
 
 

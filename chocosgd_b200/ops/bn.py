@@ -187,11 +187,13 @@ def fold_residual_ok(conv, x) -> bool:
     return conv.in_channels != 3 and conv_supported(conv, x)
 
 
-def conv_bn_act(conv, bn, x, residual=None, relu=True, fold_res=False):
+def conv_bn_act(conv, bn, x, residual=None, relu=True, fold_res=False, fold_ds=False):
     """``relu(bn(conv(x)) + residual)``.  When both layers run their native kernels the convolution
     epilogue also produces the batch statistics, so the batch-norm needs no reduction pass.
     ``fold_res`` (decided by the block with ``fold_residual_ok``): the gradient of the skip connection
-    travels from this block's last batch-norm to its first convolution outside autograd."""
+    travels from this block's last batch-norm to its first convolution outside autograd.  ``fold_ds``
+    (``fold_shortcut_ok``): the 1x1 shortcut's input gradient is computed by the block's strided 3x3
+    convolution."""
     from . import nn as native_nn
 
     if (native_nn.native_enabled("conv") and native_nn.native_enabled("bn") and bn.training and x.is_cuda
@@ -200,10 +202,10 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True, fold_res=False):
 
         if (any_conv_supported(conv, x) and (conv.out_channels // 4) <= 256
                 and 256 % (conv.out_channels // 4) == 0):
-            y, stats = conv2d_native(conv, x, want_stats=True, fold_res=fold_res and residual is None)
+            y, stats = conv2d_native(conv, x, want_stats=True, fold_res=fold_res and residual is None, fold_ds=fold_ds)
             return bn_act(bn, y, residual, relu, stats=stats, fold_res=fold_res)
-    if fold_res:
-        raise RuntimeError("fold_res was requested for a layer pair that does not run the native kernels")
+    if fold_res or fold_ds:
+        raise RuntimeError("a backward fusion was requested for a layer pair that does not run the native kernels")
     return bn_act(bn, conv(x), residual, relu)
 
 

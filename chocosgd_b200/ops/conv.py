@@ -56,6 +56,13 @@ def _declare():
         lib.conv_wgrad_gen_parts.restype = i
         lib.conv_wgrad_gen.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, vp]
         lib.conv_wgrad_gen.restype = i
+        lib.conv3x3s2_dgrad_supported.argtypes = [i, i, i, i, i, i]
+        lib.conv3x3s2_dgrad_supported.restype = i
+        lib.conv3x3s2_dgrad_grid.argtypes = [i, i, i, i]
+        lib.conv3x3s2_dgrad_grid.restype = i
+        lib.conv3x3s2_dgrad_fused.argtypes = [vp] * 11 + [i] * 6 + [vp]
+        lib.conv3x3s2_dgrad_fused.restype = i
+        lib.conv_flip_entry_size.restype = i
         lib._conv_declared = True
     return lib
 
@@ -176,13 +183,16 @@ class _Fusion:
       over the skip; the block's first convolution adds it in its input-gradient epilogue (no add
       kernel, and its batch-norm sums then cover the whole gradient);
     * ``masked``: a gradient the epilogue already multiplied with the ReLU mask -> the per-CTA rows
-      of batch-norm backward sums it produced; the batch-norm backward then skips its reduction.
+      of batch-norm backward sums it produced; the batch-norm backward then skips its reduction;
+    * ``pending_ds``: the input of a down-sampling block -> (gradient of the 1x1 shortcut's output,
+      transposed shortcut filter); the block's strided 3x3 convolution computes both input gradients
+      in one launch.
 
     Keys are data pointers; every entry keeps its tensors alive so that the address cannot be reused
     while the entry exists.  ``clear()`` runs at the start of a step and when a backward pass ends."""
 
     def __init__(self):
-        self.bn_of_output, self.pending_res, self.masked = {}, {}, {}
+        self.bn_of_output, self.pending_res, self.masked, self.pending_ds = {}, {}, {}, {}
         self._callback_queued = False
         #: CHOCO_BWD_FUSION=0 keeps every layer's backward self-contained (A/B switch, tests)
         self.enabled = os.environ.get("CHOCO_BWD_FUSION", "1") != "0"
@@ -191,6 +201,7 @@ class _Fusion:
         self.bn_of_output.clear()
         self.pending_res.clear()
         self.masked.clear()
+        self.pending_ds.clear()
         self._callback_queued = False
 
     def clear_after_backward(self):
@@ -222,7 +233,9 @@ def conv3x3_dgrad_fused(dy, flipped, cin, add=None, mask=None, bn=None):
 
 
 class FlippedWeights:
-    """Flipped filters of all native convolutions of a model, refreshed by ONE kernel per step.
+    """Filters of all native convolutions of a model in the layout of their input-gradient kernels
+    (3x3: taps reversed, channel roles exchanged; 1x1 shortcut: transposed), refreshed by ONE kernel
+    per step.
 
     ``refresh()`` is called at the start of a training step (the weights do not change between the
     forward and the backward of a step); ``get(weight)`` returns the buffer for the input-gradient
@@ -234,21 +247,24 @@ class FlippedWeights:
         self.entries = {}
         rows = []
         for m in model.modules():
-            if (isinstance(m, torch.nn.Conv2d) and m.kernel_size == (3, 3) and m.stride == (1, 1) and m.weight.is_cuda
-                    and m.weight.dtype == torch.float32 and m.bias is None and m.groups == 1
+            if (isinstance(m, torch.nn.Conv2d) and m.kernel_size in ((3, 3), (1, 1)) and m.stride in ((1, 1), (2, 2))
+                    and m.weight.is_cuda and m.weight.dtype == torch.float32 and m.bias is None and m.groups == 1
                     and m.weight.is_contiguous(memory_format=torch.channels_last)
                     and m.in_channels % 16 == 0 and m.out_channels % 16 == 0):
                 buf = torch.empty(m.weight.numel(), dtype=torch.float32, device=m.weight.device)
                 self.entries[m.weight.data_ptr()] = buf
-                rows.append((m.weight.data_ptr(), buf.data_ptr(), m.out_channels, m.in_channels))
+                rows.append((m.weight.data_ptr(), buf.data_ptr(), m.out_channels, m.in_channels,
+                             m.kernel_size[0] * m.kernel_size[1], 0))
         self.n = len(rows)
         self.valid = False
         if self.n:
-            dt = np.dtype([("w", np.uint64), ("out", np.uint64), ("cout", np.int32), ("cin", np.int32)])
+            dt = np.dtype([("w", np.uint64), ("out", np.uint64), ("cout", np.int32), ("cin", np.int32),
+                           ("taps", np.int32), ("pad", np.int32)])
+            assert dt.itemsize == _declare().conv_flip_entry_size(), "FlipEntry layout mismatch"
             host = np.array(rows, dtype=dt)
             dev = next(iter(self.entries.values())).device
             self.table = torch.from_numpy(host.view(np.uint8).copy()).to(dev)
-            self.max_elems = max(r[2] * r[3] * 9 for r in rows)
+            self.max_elems = max(r[2] * r[3] * r[4] for r in rows)
 
     def refresh(self):
         if not self.n:
@@ -269,6 +285,41 @@ _ACTIVE_FLIPS = None
 def set_active_flips(f):
     global _ACTIVE_FLIPS
     _ACTIVE_FLIPS = f
+
+
+def _flipped_filter(weight):
+    """The filter in input-gradient layout: from the per-step cache, else computed here."""
+    flipped = _ACTIVE_FLIPS.get(weight) if _ACTIVE_FLIPS is not None else None
+    if flipped is not None:
+        return flipped
+    cout, cin, kh, kw = weight.shape
+    if kh == 1:
+        return weight.detach().reshape(cout, cin).t().contiguous()
+    flipped = torch.empty(weight.numel(), dtype=torch.float32, device=weight.device)
+    rc = _declare().conv_flip_weights(_lib.ptr(weight), _lib.ptr(flipped), cout, cin, _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"conv_flip_weights failed ({rc})")
+    return flipped
+
+
+def conv3x3s2_dgrad_fused(dy, flipped, cx, ds=None, mask=None, bn=None):
+    """``(dx, stats)`` of a 3x3 / stride 2 convolution; ``ds = (dy2, w2_t)`` adds the input gradient of
+    the 1x1 / stride 2 shortcut; mask / bn as in ``conv3x3_dgrad_fused``."""
+    lib = _declare()
+    n, cdy, ho, wo = dy.shape
+    dx = torch.empty((n, cx, 2 * ho, 2 * wo), dtype=torch.float32, device=dy.device, memory_format=torch.channels_last)
+    stats = bnx = mean = invstd = None
+    if bn is not None:
+        bnx, mean, invstd = bn
+        stats = torch.empty((lib.conv3x3s2_dgrad_grid(n, ho, wo, cx), 2 * cx), dtype=torch.float32, device=dy.device)
+    dy2, w2t = ds if ds is not None else (None, None)
+    rc = lib.conv3x3s2_dgrad_fused(_lib.ptr(dy), _lib.ptr(flipped), _lib.ptr(dy2), _lib.ptr(w2t), _lib.ptr(dx), None,
+                                   _lib.ptr(mask), _lib.ptr(bnx), _lib.ptr(mean), _lib.ptr(invstd), _lib.ptr(stats),
+                                   n, ho, wo, cdy, cx, dy2.shape[1] if dy2 is not None else 0, _lib.stream_ptr())
+    if rc != 0:
+        raise RuntimeError(f"conv3x3s2_dgrad_fused failed ({rc})")
+    _lib.count(1)
+    return dx, stats
 
 
 class _Conv3x3Fn(torch.autograd.Function):
@@ -319,12 +370,7 @@ class _Conv3x3Fn(torch.autograd.Function):
             fork = _WGRAD_STREAM.enabled and weight.grad is None and not torch.is_grad_enabled()
             dw = _WGRAD_STREAM.run(fn, (x, dy), x.device) if fork else fn()
         if ctx.needs_input_grad[0]:
-            flipped = _ACTIVE_FLIPS.get(weight) if _ACTIVE_FLIPS is not None else None
-            if flipped is None:
-                flipped = torch.empty(cin * 9 * cout, dtype=torch.float32, device=x.device)
-                rc = lib.conv_flip_weights(_lib.ptr(weight), _lib.ptr(flipped), cout, cin, _lib.stream_ptr())
-                if rc != 0:
-                    raise RuntimeError(f"conv_flip_weights failed ({rc})")
+            flipped = _flipped_filter(weight)
             add = FUSION.pending_res.pop(x.data_ptr(), None) if ctx.fold_res else None
             if ctx.bn_in or add is not None:
                 bn = ctx.saved_tensors[2:5] if ctx.bn_in else None
@@ -360,15 +406,24 @@ def gen_conv_supported(m, x) -> bool:
 
 class _ConvGenFn(torch.autograd.Function):
     """Strided 3x3 / 1x1 convolution: forward on the persistent tcgen05 kernel (strided tensor map),
-    weight gradient on ``conv_wgrad_gen.cu``."""
+    weight gradient on ``conv_wgrad_gen.cu``, input gradient of the 3x3 / stride 2 form on the same
+    persistent kernel (four parity classes of the result).  ``fold_ds``: this layer and the block's
+    other strided convolution read the same tensor; the 1x1 shortcut then hands its output gradient to
+    the 3x3 convolution, which produces the sum of both input gradients in one launch."""
 
     @staticmethod
-    def forward(ctx, x, weight, ks, stride, want_stats=False):
+    def forward(ctx, x, weight, ks, stride, want_stats=False, fold_ds=False):
         lib = _declare()
         n, cin, h, w = x.shape
         cout, ho, wo = weight.shape[0], h // stride, w // stride
-        ctx.save_for_backward(x, weight)
+        ent = FUSION.bn_of_output.get(x.data_ptr()) if (FUSION.enabled and ks == 3) else None
+        ctx.bn_in = ent is not None and ent[0].shape == x.shape
+        if ctx.bn_in:
+            ctx.save_for_backward(x, weight, ent[1], ent[2], ent[3])
+        else:
+            ctx.save_for_backward(x, weight)
         ctx.geom = (ks, stride)
+        ctx.fold_ds = bool(fold_ds)
         ctx.set_materialize_grads(False)
         y = torch.empty((n, cout, ho, wo), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
         stats = None
@@ -387,28 +442,58 @@ class _ConvGenFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, _dstats=None):
         if dy is None:
-            return None, None, None, None, None
-        x, weight = ctx.saved_tensors
+            return None, None, None, None, None, None
+        x, weight = ctx.saved_tensors[:2]
         ks, stride = ctx.geom
         lib = _declare()
         dy = dy.contiguous(memory_format=torch.channels_last)
         n, cin, h, w = x.shape
-        cout = weight.shape[0]
+        cout, ho, wo = weight.shape[0], h // stride, w // stride
         geom = ((stride, stride), (ks // 2, ks // 2), (1, 1), False, (0, 0), 1)
         dx = dw = None
         from . import nn as native_nn
 
         if ctx.needs_input_grad[1]:
-            if native_nn.native_enabled("wgrad") and lib.conv_wgrad_gen_parts(n, h // stride, w // stride, cin, cout, ks,
-                                                                            stride) > 0:
+            if native_nn.native_enabled("wgrad") and lib.conv_wgrad_gen_parts(n, ho, wo, cin, cout, ks, stride) > 0:
                 fn = lambda: conv_wgrad_gen(x, dy, weight, ks, stride)
             else:
                 fn = lambda: torch.ops.aten.convolution_backward(dy, x, weight, None, *geom, (False, True, False))[1]
             fork = _WGRAD_STREAM.enabled and weight.grad is None and not torch.is_grad_enabled()
             dw = _WGRAD_STREAM.run(fn, (x, dy), x.device) if fork else fn()
         if ctx.needs_input_grad[0]:
-            dx = torch.ops.aten.convolution_backward(dy, x, weight, None, *geom, (True, False, False))[0]
-        return dx, dw, None, None, None
+            if ks == 1 and ctx.fold_ds:
+                # handed to the block's 3x3 / stride 2 convolution, whose backward runs after this one
+                FUSION.pending_ds[x.data_ptr()] = (x, dy, _flipped_filter(weight))
+                FUSION.clear_after_backward()
+            elif ks == 3 and stride == 2 and lib.conv3x3s2_dgrad_supported(n, ho, wo, cout, cin, 0):
+                ds = FUSION.pending_ds.pop(x.data_ptr(), None) if ctx.fold_ds else None
+                if ctx.fold_ds and ds is None:
+                    raise RuntimeError("the shortcut's gradient was not handed over before the strided convolution's backward")
+                bn = ctx.saved_tensors[2:5] if ctx.bn_in else None
+                dx, stats = conv3x3s2_dgrad_fused(dy, _flipped_filter(weight), cin, ds=ds[1:] if ds is not None else None,
+                                                  mask=x if ctx.bn_in else None, bn=bn)
+                if stats is not None:
+                    FUSION.masked[dx.data_ptr()] = (dx, stats)
+                    FUSION.clear_after_backward()
+            else:
+                dx = torch.ops.aten.convolution_backward(dy, x, weight, None, *geom, (True, False, False))[0]
+        return dx, dw, None, None, None, None
+
+
+def fold_shortcut_ok(conv, shortcut_conv, x) -> bool:
+    """True when a down-sampling block's strided 3x3 convolution can take over the input gradient of its
+    1x1 / stride 2 shortcut (both read ``x``; both run the native kernels)."""
+    from . import nn as native_nn
+
+    if not (native_nn.native_enabled("conv") and FUSION.enabled and x.is_cuda and x.requires_grad
+            and torch.is_grad_enabled()):
+        return False
+    if conv.kernel_size != (3, 3) or conv.stride != (2, 2) or shortcut_conv.kernel_size != (1, 1):
+        return False
+    if shortcut_conv.stride != (2, 2) or not (gen_conv_supported(conv, x) and gen_conv_supported(shortcut_conv, x)):
+        return False
+    n, c, h, w = x.shape
+    return bool(_declare().conv3x3s2_dgrad_supported(n, h // 2, w // 2, conv.out_channels, c, shortcut_conv.out_channels))
 
 
 class _WgradStream:
@@ -554,11 +639,11 @@ class _ConvFirstFn(torch.autograd.Function):
         return None, dw, None
 
 
-def conv2d_native(m, x, want_stats=False, fold_res=False):
+def conv2d_native(m, x, want_stats=False, fold_res=False, fold_ds=False):
     if m.in_channels == 3:
         return _ConvFirstFn.apply(x, m.weight, want_stats)
     if m.stride != (1, 1) or m.kernel_size != (3, 3):
-        return _ConvGenFn.apply(x, m.weight, m.kernel_size[0], m.stride[0], want_stats)
+        return _ConvGenFn.apply(x, m.weight, m.kernel_size[0], m.stride[0], want_stats, fold_ds)
     return _Conv3x3Fn.apply(x, m.weight, want_stats, fold_res)
 
 

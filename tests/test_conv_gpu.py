@@ -223,6 +223,62 @@ def test_residual_blocks_with_fused_backward_epilogues():
     assert n_u - n_f == 4, (n_u, n_f)
 
 
+@pytest.mark.parametrize("cin,hw,n", [(16, 32, 8), (32, 16, 6), (16, 32, 128)])
+def test_downsampling_block_with_shortcut_gradient_in_the_strided_dgrad(cin, hw, n):
+    """A stage's first block (3x3 / 2 convolution + 1x1 / 2 shortcut): the strided convolution's
+    input-gradient launch also produces the shortcut's input gradient, applies the ReLU mask and
+    leaves the batch-norm backward sums; compared with self-contained layer backwards (same native
+    kernels) and with the library composition."""
+    from chocosgd_b200.models import layers as L
+    from chocosgd_b200.models.resnet import BasicBlock
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.conv import FUSION, last_error
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv1 = L.Conv2d(cin, cin, 3, padding=1, bias=False)
+            self.bn1 = L.BatchNorm2d(cin)
+            ds = torch.nn.Sequential(L.Conv2d(cin, 2 * cin, kernel_size=1, stride=2, bias=False), L.BatchNorm2d(2 * cin))
+            self.b1 = BasicBlock(cin, 2 * cin, 2, ds)
+
+        def forward(self, x):
+            return self.b1(L.conv_bn_act(self.conv1, self.bn1, x))
+
+    torch.manual_seed(6)
+    net = Net().cuda().to(memory_format=torch.channels_last)
+    for m in net.modules():
+        if isinstance(m, torch.nn.BatchNorm2d):
+            m.weight.data.uniform_(0.5, 1.5)
+            m.bias.data.uniform_(-0.3, 0.3)
+    x = torch.randn(n, cin, hw, hw, device="cuda").contiguous(memory_format=torch.channels_last).requires_grad_()
+    g = torch.randn(n, 2 * cin, hw // 2, hw // 2, device="cuda").contiguous(memory_format=torch.channels_last)
+    params = [p for p in net.parameters()]
+    results = {}
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        for mode in ("fused", "unfused", "library"):
+            nnn.set_native(mode != "library", which=("conv", "wgrad", "bn"))
+            FUSION.enabled = mode == "fused"
+            FUSION.clear()
+            net.train()
+            out = net(x)
+            grads = torch.autograd.grad(out, [x] + params, g)
+            torch.cuda.synchronize()
+            results[mode] = (out, grads)
+    finally:
+        FUSION.enabled = True
+        FUSION.clear()
+        nnn.set_native(False)
+        torch.backends.cudnn.allow_tf32 = True
+    assert last_error() == 0
+    assert torch.equal(results["fused"][0], results["unfused"][0])
+    for a, b in zip(results["fused"][1], results["unfused"][1]):
+        assert (a - b).abs().max().item() <= 2e-3 * b.abs().max().item() + 1e-5
+    for a, b in zip((results["fused"][0],) + tuple(results["fused"][1]), (results["library"][0],) + tuple(results["library"][1])):
+        assert (a - b).abs().max().item() <= 1e-2 * b.abs().max().item() + 1e-3
+
+
 GEN_SHAPES = [  # n, cin, h, w (input), cout, ks, stride
     (8, 16, 32, 32, 32, 3, 2), (128, 16, 32, 32, 32, 3, 2), (8, 32, 16, 16, 64, 3, 2), (128, 32, 16, 16, 64, 3, 2),
     (8, 16, 32, 32, 32, 1, 2), (128, 16, 32, 32, 32, 1, 2), (6, 32, 16, 16, 64, 1, 2), (128, 32, 16, 16, 64, 1, 2),
