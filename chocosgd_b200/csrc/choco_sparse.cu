@@ -58,15 +58,9 @@ __device__ void find_bucket(const uint32_t* __restrict__ hist, int nbins, uint32
 
 // pass 2: digit-2 histogram of keys whose digit 1 equals the selected bucket
 // pass 3: digit-3 histogram of keys whose digits 1 and 2 equal the selected buckets
-__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_hist_kernel(const ChocoParams* __restrict__ params,
-                                                                      int pass) {
-  pdl_wait();
-  pdl_trigger();
-  const ChocoParams& p = params[blockIdx.y];
+__device__ void topk_hist_chunk(const ChocoParams& p, int chunk, int pass, uint32_t* sh /*[258]*/,
+                                uint32_t* sh_hist /*[2048]*/) {
   const SegTable& tb = p.tab;
-  const int chunk = blockIdx.x;
-  __shared__ uint32_t sh[CHOCO_THREADS + 2];
-  __shared__ uint32_t sh_hist[2048];
   const int seg = tb.chunk_seg[chunk];
   const int start = tb.chunk_start[chunk];
   const int valid = tb.chunk_valid[chunk];
@@ -101,6 +95,16 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_hist_kernel(const Ch
   uint32_t* out = gh + (pass == 2 ? 2048 : 4096);
   for (int i = threadIdx.x; i < nb; i += CHOCO_THREADS)
     if (sh_hist[i]) atomicAdd(out + i, sh_hist[i]);
+  __syncthreads();   // sh_hist may be reused by the caller's next chunk
+}
+
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_hist_kernel(const ChocoParams* __restrict__ params,
+                                                                      int pass) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ uint32_t sh[CHOCO_THREADS + 2];
+  __shared__ uint32_t sh_hist[2048];
+  topk_hist_chunk(params[blockIdx.y], blockIdx.x, pass, sh, sh_hist);
 }
 
 extern "C" int choco_topk_hist(const void* params_dev, int n_chunks, int n_ranks, int pass, cudaStream_t stream) {
@@ -110,14 +114,8 @@ extern "C" int choco_topk_hist(const void* params_dev, int n_chunks, int n_ranks
 }
 
 // threshold key and per-chunk counts
-__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_count_kernel(const ChocoParams* __restrict__ params) {
-  pdl_wait();
-  pdl_trigger();
-  const ChocoParams& p = params[blockIdx.y];
+__device__ void topk_count_chunk(const ChocoParams& p, int chunk, uint32_t* sh /*[258]*/) {
   const SegTable& tb = p.tab;
-  const int chunk = blockIdx.x;
-  __shared__ uint32_t sh[CHOCO_THREADS + 2];
-  __shared__ float red[32];
   const int seg = tb.chunk_seg[chunk];
   const int start = tb.chunk_start[chunk];
   const int valid = tb.chunk_valid[chunk];
@@ -171,7 +169,14 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_count_kernel(const C
       p.sel[seg * 4 + 1] = k3;  // how many keys equal to thr are kept (lowest indices first)
     }
   }
-  (void)red;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_count_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ uint32_t sh[CHOCO_THREADS + 2];
+  topk_count_chunk(params[blockIdx.y], blockIdx.x, sh);
 }
 
 extern "C" int choco_topk_count(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
@@ -196,14 +201,8 @@ __device__ __forceinline__ void publish_if_last(const ChocoParams& p, uint32_t n
 }
 
 // ordered compaction: payload = [sum_k int32 indices][sum_k fp32 values]
-__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const ChocoParams* __restrict__ params) {
-  pdl_wait();
-  pdl_trigger();
-  const ChocoParams& p = params[blockIdx.y];
+__device__ void topk_emit_chunk(const ChocoParams& p, int chunk, uint32_t* sh /*[258]*/, uint32_t* sh_base /*[2]*/) {
   const SegTable& tb = p.tab;
-  const int chunk = blockIdx.x;
-  __shared__ uint32_t sh[CHOCO_THREADS + 2];
-  __shared__ uint32_t sh_base[2];
   const int seg = tb.chunk_seg[chunk];
   const int start = tb.chunk_start[chunk];
   const int valid = tb.chunk_valid[chunk];
@@ -324,7 +323,18 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const Ch
     uint32_t* gh = p.hist + (size_t)seg * CHOCO_HIST_WORDS;
     for (int i = threadIdx.x; i < CHOCO_HIST_WORDS; i += CHOCO_THREADS) gh[i] = 0;
   }
-  publish_if_last(p, (uint32_t)tb.n_chunks, t);
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_topk_emit_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
+  const ChocoParams& p = params[blockIdx.y];
+  __shared__ uint32_t sh[CHOCO_THREADS + 2];
+  __shared__ uint32_t sh_base[2];
+  const uint32_t t = p.step[0];
+  topk_emit_chunk(p, blockIdx.x, sh, sh_base);
+  publish_if_last(p, (uint32_t)p.tab.n_chunks, t);
 }
 
 extern "C" int choco_topk_emit(const void* params_dev, int n_chunks, int n_ranks, cudaStream_t stream) {
@@ -343,12 +353,8 @@ __device__ __forceinline__ int segment_of_entry(const SegTable& tb, int e) {
 }
 
 // random-k: payload = [sum_k fp32 values]; entry e of tensor `seg` is element perm(e - koff)
-__global__ void __launch_bounds__(CHOCO_THREADS) choco_randk_emit_kernel(const ChocoParams* __restrict__ params) {
-  pdl_wait();
-  pdl_trigger();
-  const ChocoParams& p = params[blockIdx.y];
+__device__ void randk_emit_entries(const ChocoParams& p, uint32_t t) {
   const SegTable& tb = p.tab;
-  const uint32_t t = p.step[0];
   const int PW = p.payload_words, par_cur = t & 1;
   const int sum_k = PW;
   for (int e = blockIdx.x * CHOCO_THREADS + threadIdx.x; e < sum_k; e += gridDim.x * CHOCO_THREADS) {
@@ -362,6 +368,14 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_randk_emit_kernel(const C
     p.outbox[par_cur * PW + e] = vb;
     for (int k = 0; k < p.n_peers; ++k) p.peer_inbox[k][par_cur * PW + e] = vb;
   }
+}
+
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_randk_emit_kernel(const ChocoParams* __restrict__ params) {
+  pdl_wait();
+  pdl_trigger();
+  const ChocoParams& p = params[blockIdx.y];
+  const uint32_t t = p.step[0];
+  randk_emit_entries(p, t);
   publish_if_last(p, gridDim.x, t);
 }
 
@@ -391,16 +405,8 @@ extern "C" int choco_wait_flags(const void* params_dev, int n_ranks, cudaStream_
 // Apply one source payload of step t-1:  src < 0: own (x_hat += v, s += w_ii v);  src = k: s += w_ik v.
 // codec 1 = top-k (indices in the payload), 2 = random-k (indices regenerated from the sender's seed).
 // mark_done: this is the last source; record that step t-1 has been applied.
-__global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_decode_kernel(const ChocoParams* __restrict__ params,
-                                                                          int src, int codec, int mark_done) {
-  pdl_wait();
-  pdl_trigger();
-  const ChocoParams& p = params[blockIdx.y];
+__device__ void sparse_decode_entries(const ChocoParams& p, uint32_t t, int src, int codec) {
   const SegTable& tb = p.tab;
-  const uint32_t t = p.step[0];
-  if (t == 0 || p.step[2] >= t || p.status[0] != CHOCO_OK) return;
-  if (src >= p.n_peers) return;  // this logical rank has fewer neighbours than the launch covers
-  (void)mark_done;
   const int PW = p.payload_words, par_prev = (t - 1) & 1;
   const int sum_k = codec == 1 ? PW / 2 : PW;
   const uint32_t* pay = (src < 0 ? p.outbox : p.my_inbox[src]) + par_prev * PW;
@@ -432,6 +438,18 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_decode_kernel(cons
   }
 }
 
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_decode_kernel(const ChocoParams* __restrict__ params,
+                                                                          int src, int codec, int mark_done) {
+  pdl_wait();
+  pdl_trigger();
+  const ChocoParams& p = params[blockIdx.y];
+  const uint32_t t = p.step[0];
+  if (t == 0 || p.step[2] >= t || p.status[0] != CHOCO_OK) return;
+  if (src >= p.n_peers) return;  // this logical rank has fewer neighbours than the launch covers
+  (void)mark_done;
+  sparse_decode_entries(p, t, src, codec);
+}
+
 __global__ void choco_mark_decoded_kernel(const ChocoParams* __restrict__ params) {
   pdl_wait();
   pdl_trigger();
@@ -450,4 +468,174 @@ extern "C" int choco_sparse_decode(const void* params_dev, int n_blocks, int n_r
   dim3 grid(n_blocks, n_ranks);
   launch_k(choco_sparse_decode_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, src, codec, 0);
   return (int)cudaGetLastError();
+}
+
+// ---- the whole step of a sparsifying codec as ONE cooperative kernel ---------------------------
+// Phases, separated by grid barriers of this logical rank's CTAs (gridDim.x CTAs, all co-resident:
+// a cooperative launch):
+//   wait for the neighbours' payloads of step t-1 | apply own payload | apply each neighbour's |
+//   SGD + consensus step, d = x - x_hat (+ first radix histogram) | [top-k: histogram 2 | histogram 3 |
+//   threshold and per-chunk counts |] compaction + push | raise the flags.
+// The work inside a phase is the same device code as the stand-alone kernels above, walked with a
+// grid-stride loop; only the launch boundaries are replaced.  Sources are applied one after the other
+// (not with atomics) so that s and x_hat stay bitwise reproducible.
+
+// Bounded barrier of the gridDim.x CTAs with blockIdx.y == this rank: bar[0] arrivals, bar[1] generation.
+// Returns false (in every thread of the CTA) when the budget ran out.
+__device__ bool rank_grid_barrier(uint32_t* bar, long long budget_ns, int* sh_ok) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const uint32_t gen = ld_acquire_sys(bar + 1);
+    __threadfence();
+    if (atomicAdd(bar, 1u) == gridDim.x - 1) {
+      bar[0] = 0;
+      __threadfence();
+      st_release_sys(bar + 1, gen + 1u);
+    } else {
+      const long long t0 = global_ns();
+      while (ld_acquire_sys(bar + 1) == gen) {
+        __nanosleep(32);
+        if (global_ns() - t0 > budget_ns) { ok = 0; break; }
+      }
+    }
+    *sh_ok = ok;
+  }
+  __syncthreads();
+  const bool ok = *sh_ok != 0;
+  __syncthreads();
+  return ok;
+}
+
+// SGD step + consensus step + difference for one chunk (the non-decoding path of choco_dense_prep)
+__device__ void sparse_prep_chunk(const ChocoParams& p, int chunk, int codec, uint32_t* sh_hist /*[2048]*/) {
+  const SegTable& tb = p.tab;
+  const int seg = tb.chunk_seg[chunk], start = tb.chunk_start[chunk], valid = tb.chunk_valid[chunk];
+  const int span = (valid + 31) & ~31;
+  const float lr = p.hyper[HYP_LR], mu = p.hyper[HYP_MOMENTUM], gamma = p.hyper[HYP_GAMMA];
+  const bool nesterov = p.hyper[HYP_NESTEROV] != 0.f;
+  const float gscale = p.hyper[HYP_GSCALE];
+  const bool mom_init = p.step[1] != 0;
+  const float wd = tb.seg_wd[seg];
+  if (codec == 1) {
+    for (int i = threadIdx.x; i < 2048; i += CHOCO_THREADS) sh_hist[i] = 0;
+    __syncthreads();
+  }
+  for (int base = threadIdx.x * 4; base < span; base += CHOCO_THREADS * 4) {
+    const int pos = start + base;
+    const float4 xh = *reinterpret_cast<const float4*>(p.x_hat + pos);
+    const float4 sv = *reinterpret_cast<const float4*>(p.s + pos);
+    const float4 xv = *reinterpret_cast<const float4*>(p.x + pos);
+    const float4 gv = load_grad4(p, seg, pos, base, valid);
+    const float xh_a[4] = {xh.x, xh.y, xh.z, xh.w}, s_a[4] = {sv.x, sv.y, sv.z, sv.w};
+    float x_a[4] = {xv.x, xv.y, xv.z, xv.w}, g_a[4] = {gv.x, gv.y, gv.z, gv.w};
+    float m_a[4] = {0.f, 0.f, 0.f, 0.f}, d_a[4] = {0.f, 0.f, 0.f, 0.f};
+    if (mu != 0.f && mom_init) {
+      const float4 mv = *reinterpret_cast<const float4*>(p.m + pos);
+      m_a[0] = mv.x; m_a[1] = mv.y; m_a[2] = mv.z; m_a[3] = mv.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (base + e < valid) {
+        const float d = sgd_direction(x_a[e], g_a[e] * gscale, m_a[e], wd, mu, nesterov, mom_init);
+        float xn = fmaf(-lr, d, x_a[e]);
+        xn = fmaf(gamma, s_a[e] - xh_a[e], xn);
+        x_a[e] = xn;
+        const float diff = xn - xh_a[e];
+        d_a[e] = diff;
+        if (codec == 1) atomicAdd(&sh_hist[(__float_as_uint(diff) & 0x7FFFFFFFu) >> 20], 1u);
+      }
+    *reinterpret_cast<float4*>(p.x + pos) = make_float4(x_a[0], x_a[1], x_a[2], x_a[3]);
+    if (mu != 0.f) *reinterpret_cast<float4*>(p.m + pos) = make_float4(m_a[0], m_a[1], m_a[2], m_a[3]);
+    clear_grad4(p, pos);
+    *reinterpret_cast<float4*>(p.scratch_d + pos) = make_float4(d_a[0], d_a[1], d_a[2], d_a[3]);
+  }
+  if (codec == 1) {
+    __syncthreads();
+    uint32_t* gh = p.hist + (size_t)seg * CHOCO_HIST_WORDS;
+    for (int i = threadIdx.x; i < 2048; i += CHOCO_THREADS)
+      if (sh_hist[i]) atomicAdd(gh + i, sh_hist[i]);
+    __syncthreads();
+  }
+}
+
+// mode bit 0: apply the payloads of step t-1; bit 1: take the step and push (0 alone = decode only)
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_coop_kernel(const ChocoParams* __restrict__ params, int codec,
+                                                                        int mode) {
+  const ChocoParams& p = params[blockIdx.y];
+  const SegTable& tb = p.tab;
+  __shared__ uint32_t sh[CHOCO_THREADS + 2];
+  __shared__ uint32_t sh_base[2];
+  __shared__ uint32_t sh_hist[2048];
+  __shared__ int sh_ok;
+  uint32_t* bar = p.done_count + 4;   // words 4 (arrivals) and 5 (generation)
+  const uint32_t t = p.step[0];
+  const long long budget = p.wait_budget_ns;
+#define COOP_BARRIER()                                                      \
+  if (!rank_grid_barrier(bar, budget, &sh_ok)) {                            \
+    if (threadIdx.x == 0) report(p.status, CHOCO_TIMEOUT, p.rank, (int)t);  \
+    return;                                                                 \
+  }
+  const bool decode = (mode & 1) && t > 0 && p.step[2] < t;
+  if (decode) {
+    if (blockIdx.x == 0 && threadIdx.x < p.n_peers &&
+        !wait_flag_ge(p.my_flag[threadIdx.x], t, budget))
+      report(p.status, CHOCO_TIMEOUT, p.peer_rank[threadIdx.x], (int)t - 1);
+    COOP_BARRIER();
+    if (__ldcg(p.status) != CHOCO_OK) return;      // the same answer in every CTA: written before the barrier
+    for (int src = -1; src < p.n_peers; ++src) {
+      sparse_decode_entries(p, t, src, codec);
+      COOP_BARRIER();
+    }
+  } else if ((mode & 2) && t > 0 && p.step[2] < t) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) report(p.status, CHOCO_BAD_STEP, -1, (int)t);
+  }
+  if (!(mode & 2)) {
+    if (decode && blockIdx.x == 0 && threadIdx.x == 0) p.step[2] = t;
+    return;
+  }
+  for (int c = blockIdx.x; c < tb.n_chunks; c += gridDim.x) sparse_prep_chunk(p, c, codec, sh_hist);
+  COOP_BARRIER();
+  if (codec == 1) {
+    for (int c = blockIdx.x; c < tb.n_chunks; c += gridDim.x) topk_hist_chunk(p, c, 2, sh, sh_hist);
+    COOP_BARRIER();
+    for (int c = blockIdx.x; c < tb.n_chunks; c += gridDim.x) topk_hist_chunk(p, c, 3, sh, sh_hist);
+    COOP_BARRIER();
+    for (int c = blockIdx.x; c < tb.n_chunks; c += gridDim.x) topk_count_chunk(p, c, sh);
+    COOP_BARRIER();
+    for (int c = blockIdx.x; c < tb.n_chunks; c += gridDim.x) topk_emit_chunk(p, c, sh, sh_base);
+  } else {
+    randk_emit_entries(p, t);
+  }
+  // every CTA's pushes are ordered before its arrival; one thread then raises the flags
+  __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
+  COOP_BARRIER();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    for (int k = 0; k < p.n_peers; ++k) st_release_sys(p.peer_flag[k], t + 1);
+    if (decode) p.step[2] = t;
+    p.step[1] = 1;
+    __threadfence();
+    p.step[0] = t + 1;
+  }
+#undef COOP_BARRIER
+}
+
+// Largest gridDim.x such that gridDim.x * n_ranks CTAs are co-resident on the current device.
+extern "C" int choco_sparse_coop_max_grid(int n_ranks) {
+  int dev = 0, sms = 0, per_sm = 0;
+  if (n_ranks < 1 || cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, choco_sparse_coop_kernel, CHOCO_THREADS, 0) != cudaSuccess)
+    return -1;
+  return sms * per_sm / n_ranks;
+}
+
+extern "C" int choco_sparse_coop_step(const void* params_dev, int grid_x, int n_ranks, int codec, int mode,
+                                      cudaStream_t stream) {
+  if (grid_x < 1 || n_ranks < 1 || !(codec == 1 || codec == 2)) return -1;
+  dim3 grid(grid_x, n_ranks);
+  void* args[] = {(void*)&params_dev, (void*)&codec, (void*)&mode};
+  return (int)cudaLaunchCooperativeKernel((const void*)choco_sparse_coop_kernel, grid, dim3(CHOCO_THREADS), args, 0, stream);
 }

@@ -64,7 +64,7 @@ struct ChocoParams {
   const float* hyper;                     // [HYP_N]
   uint32_t* step;                         // [0] pushes completed, [1] momentum initialised, [2] decodes completed
   uint32_t* seg_count;                    // [T] chunk arrival counters (self-resetting)
-  uint32_t* done_count;                   // [4] CTA arrival counters (self-resetting)
+  uint32_t* done_count;                   // [8] CTA arrival counters (self-resetting); [4], [5]: grid barrier
   float* partial;                         // [n_chunks] per-chunk partial norms
   uint32_t* hist;                         // [T][HIST_WORDS] radix-select histograms
   uint32_t* chunk_cnt;                    // [n_chunks][2] (#greater, #equal) per chunk

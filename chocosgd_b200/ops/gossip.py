@@ -24,6 +24,7 @@ sequences plus three flatten/unflatten copies and ``isend``/``irecv`` per step).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -97,6 +98,9 @@ class SegTables:
 
 
 ALLREDUCE = "allreduce"
+#: arenas up to this many elements run a sparsifying CHOCO step as one cooperative kernel (above it the
+#: step is bandwidth bound and the multi-kernel chain, with many more CTAs in flight, is faster)
+COOP_MAX_ELEMS = 4 << 20
 
 
 class ArPlanC(ctypes.Structure):
@@ -147,6 +151,7 @@ class ChocoEngine:
         seed: int = 1234,
         wait_budget_ms: float = 2000.0,
         chunk_elems: Optional[int] = None,
+        coop: Optional[bool] = None,
     ):
         if comm_op is not None and comm_op != ALLREDUCE and comm_op not in CODEC_ID:
             raise NotImplementedError(f"fused gossip kernels do not cover comm_op={comm_op!r}")
@@ -203,7 +208,7 @@ class ChocoEngine:
             res = {
                 "step": z(4, torch.int32),
                 "seg_count": z(T, torch.int32),
-                "done_count": z(4, torch.int32),
+                "done_count": z(8, torch.int32),
                 "partial": z(nc, torch.float32),
                 "status": z(4, torch.int32),
                 "outbox": z(2 * self.payload_words, torch.int32),
@@ -246,7 +251,21 @@ class ChocoEngine:
         self._pp = ctypes.c_void_p(self.params.data_ptr())
         self._steps = 0
         self.sparse = sparse
-        self.entry_blocks = max(1, min(1184, (self.tables.sum_k + 255) // 256)) if sparse else 1
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.entry_blocks = max(1, min(8 * sms, (self.tables.sum_k + 255) // 256)) if sparse else 1
+        # Sparsifying codecs of plain CHOCO-SGD: the whole step as ONE cooperative kernel (grid barriers
+        # instead of launch boundaries) while the arena is small enough to be latency bound; large arenas
+        # keep the multi-kernel chain, whose phases run with far more CTAs than can be co-resident.
+        self.coop, self.coop_grid = False, 0
+        if sparse and type(self) is ChocoEngine:
+            want = coop
+            if want is None:
+                env = os.environ.get("CHOCO_SPARSE_COOP", "auto")
+                want = None if env == "auto" else env not in ("0", "off")
+            if want is None:
+                want = seg.total <= COOP_MAX_ELEMS
+            if want:
+                self._init_coop(sms)
 
     # ---- construction helpers --------------------------------------------------------------
     @classmethod
@@ -310,6 +329,22 @@ class ChocoEngine:
     launches_per_step = 0
     _n_launch = 0
 
+    def _init_coop(self, sms):
+        L = self.lib
+        L.choco_sparse_coop_max_grid.argtypes = [ctypes.c_int]
+        L.choco_sparse_coop_max_grid.restype = ctypes.c_int
+        L.choco_sparse_coop_step.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                             ctypes.c_void_p]
+        L.choco_sparse_coop_step.restype = ctypes.c_int
+        with torch.cuda.device(self.device):
+            cap = L.choco_sparse_coop_max_grid(self.n_local)
+        if cap < 1:
+            return  # cannot be made co-resident (many logical ranks on one device): keep the chain
+        work = max(self.tables.n_chunks, self.entry_blocks)
+        # two CTAs per SM at most: more CTAs make every grid barrier slower than the phase it ends
+        self.coop_grid = max(1, min(work, cap, max(1, 2 * sms // self.n_local)))
+        self.coop = True
+
     def _chk(self, code, what):
         self._n_launch += 1
         _lib.count(1)
@@ -325,6 +360,8 @@ class ChocoEngine:
         elif self.codec == 0:
             self._chk(L.choco_dense_prep(pp, nc, nr, MODE_DECODE, 0, sp), "choco_dense_prep")
             self._chk(L.choco_qsgd_pack_nbits(pp, nc, nr, int(self.nbits), sp), "choco_qsgd_pack")
+        elif self.coop:
+            self._chk(L.choco_sparse_coop_step(pp, self.coop_grid, nr, self.codec, 3, sp), "choco_sparse_coop_step")
         else:
             self._launch_sparse_decode(sp)
             self._chk(L.choco_dense_prep(pp, nc, nr, 0, self.codec, sp), "choco_dense_prep")
@@ -353,6 +390,8 @@ class ChocoEngine:
             self._chk(L.choco_sign_step(pp, nc, nr, MODE_DECODE, self.peers_hint, sp), "choco_sign_decode")
         elif self.codec == 0:
             self._chk(L.choco_qsgd_decode(pp, nc, nr, sp), "choco_qsgd_decode")
+        elif self.coop:
+            self._chk(L.choco_sparse_coop_step(pp, self.coop_grid, nr, self.codec, 1, sp), "choco_sparse_coop_decode")
         else:
             self._launch_sparse_decode(sp)
 

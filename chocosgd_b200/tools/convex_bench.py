@@ -25,6 +25,13 @@ def main(argv=None):
     A, y = synthetic_logistic(a.samples, a.features, seed=0, noise=0.1)
     n, d = A.shape
     k = max(1, d // 100)
+    if a.device != "cpu":
+        # context creation, library load and the first transfers are not part of an iteration's cost
+        warm = Parameters(num_epoch=1, lr_type="decay", initial_lr=0.1, tau=float(d), regularizer=1.0 / n, estimate="final",
+                          n_cores=a.nodes, topology="ring", distribute_data=True, split_data_strategy="random",
+                          method="choco", quantization="top", coordinates_to_keep=k, consensus_lr=0.04, random_seed=1,
+                          split_data_random_seed=1)
+        LogisticDecentralizedSGD(warm, device=a.device).fit(A[: 50 * a.nodes], y[: 50 * a.nodes])
     for method, quant, extra in (("choco", "top", dict(coordinates_to_keep=k, consensus_lr=0.04)), ("plain", "full", {})):
         prm = Parameters(num_epoch=a.epochs, lr_type="decay", initial_lr=0.1, tau=float(d), regularizer=1.0 / n,
                          estimate="final", n_cores=a.nodes, topology="ring", distribute_data=True,

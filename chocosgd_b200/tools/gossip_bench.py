@@ -164,7 +164,9 @@ def run(args):
                 bufs = {rank: RankBuffers(x, mk(), mk(), mk(), mk())}
                 mb = (lambda pw: DistributedMailbox(graph, pw, dev)) if world > 1 else (
                     lambda pw: LoopbackMailbox({rank: []}, pw, dev))
-                eng = ChocoEngine([rank], bufs, {rank: graph.get_neighborhood()}, seg, [0.0], comm_op, mb, dev, **kw)
+                coop = None if args.coop == "auto" else args.coop == "on"
+                eng = ChocoEngine([rank], bufs, {rank: graph.get_neighborhood()}, seg, [0.0], comm_op, mb, dev, coop=coop,
+                                  **kw)
                 eng.set_hyper(0.0, 0.0, 0.5, False)
                 step = eng.launch_step
                 nbits, payload_bytes, launches = eng.nbits, 4 * eng.payload_words, None
@@ -257,6 +259,8 @@ def main(argv=None):
     p.add_argument("--steps", type=int, default=20)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--graph", type=int, default=1)
+    p.add_argument("--coop", default="auto", choices=("auto", "on", "off"),
+                   help="top-k / random-k step as one cooperative kernel (auto: arenas up to 4 Mi elements)")
     run(p.parse_args(argv))
 
 

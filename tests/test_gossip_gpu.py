@@ -76,9 +76,11 @@ def test_sign_is_bitwise_reproducible():
     assert torch.equal(a.x, b.x) and torch.equal(a.x_hat, b.x_hat) and torch.equal(a.s, b.s)
 
 
+@pytest.mark.parametrize("coop", [True, False])   # one cooperative kernel per step / chain of kernels
 @pytest.mark.parametrize("topo,n", [("ring", 1), ("ring", 4), ("complete", 5)])
-def test_topk_matches_simulator(topo, n):
-    sim, world, _ = _run("compress_top_k", topo, n, compress_ratio=0.9)
+def test_topk_matches_simulator(topo, n, coop):
+    sim, world, _ = _run("compress_top_k", topo, n, compress_ratio=0.9, coop=coop)
+    assert world.engine.coop == coop and (world.engine.launches_per_step == 1) == coop
     torch.testing.assert_close(world.x.cpu(), sim.x, rtol=2e-5, atol=2e-6)
     # same coordinates selected: x_hat has the same support
     assert torch.equal(world.x_hat.cpu() != 0, sim.x_hat != 0)
@@ -103,9 +105,11 @@ def test_topk_with_ties_takes_lowest_indices():
         assert nz.tolist() == list(range(k))
 
 
+@pytest.mark.parametrize("coop", [True, False])
 @pytest.mark.parametrize("topo,n", [("ring", 1), ("ring", 4)])
-def test_randomk_matches_simulator(topo, n):
-    sim, world, _ = _run("compress_random_k", topo, n, compress_ratio=0.8)
+def test_randomk_matches_simulator(topo, n, coop):
+    sim, world, _ = _run("compress_random_k", topo, n, compress_ratio=0.8, coop=coop)
+    assert world.engine.coop == coop and (world.engine.launches_per_step == 1) == coop
     torch.testing.assert_close(world.x.cpu(), sim.x, rtol=2e-5, atol=2e-6)
     torch.testing.assert_close(world.x_hat.cpu(), sim.x_hat, rtol=2e-5, atol=2e-6)
     torch.testing.assert_close(world.s.cpu(), sim.s, rtol=2e-5, atol=2e-6)
@@ -119,6 +123,41 @@ def test_qsgd_matches_simulator(kw):
     for a, b in ((world.x.cpu(), sim.x), (world.x_hat.cpu(), sim.x_hat), (world.s.cpu(), sim.s)):
         bad = ~torch.isclose(a, b, rtol=1e-4, atol=1e-5)
         assert bad.float().mean() < 2e-3, float(bad.float().mean())
+
+
+@pytest.mark.parametrize("comm_op", ["compress_top_k", "compress_random_k"])
+def test_cooperative_step_equals_the_kernel_chain_bitwise(comm_op):
+    """Multi-chunk tensors, several steps: same x, x_hat, s from the one-kernel step and the chain."""
+    a = _run(comm_op, "ring", 3, chunk=1024, compress_ratio=0.9, coop=True)[1]
+    b = _run(comm_op, "ring", 3, chunk=1024, compress_ratio=0.9, coop=False)[1]
+    assert a.engine.coop and not b.engine.coop
+    assert torch.equal(a.x, b.x) and torch.equal(a.x_hat, b.x_hat) and torch.equal(a.s, b.s)
+
+
+def test_cooperative_step_times_out_without_hanging():
+    """The one-kernel top-k step with a neighbour that never publishes: the flag wait runs out, every CTA
+    leaves at the next grid barrier, the host raises, the context stays usable."""
+    from chocosgd_b200.ops.gossip import ChocoEngine, RankBuffers
+    from chocosgd_b200.parallel.symm import LoopbackMailbox
+    from chocosgd_b200.utils.error_handler import GossipTimeout
+
+    seg = Segments.from_sizes([5000, 40])
+    dev = torch.device("cuda")
+    mk = lambda: torch.zeros(seg.total, device=dev)
+    bufs = {0: RankBuffers(torch.ones(seg.total, device=dev), mk(), mk(), mk(), mk())}
+    eng = ChocoEngine([0], bufs, {0: {0: 0.5, 1: 0.5}}, seg, [0.0, 0.0], "compress_top_k",
+                      lambda pw: LoopbackMailbox({0: [1], 1: [0]}, pw, dev), dev, wait_budget_ms=20.0,
+                      compress_ratio=0.9, chunk_elems=1024, coop=True)
+    assert eng.coop and eng.coop_grid > 1
+    eng.set_hyper(0.1, 0.0, 0.5, False)
+    eng.launch_step()
+    eng.check()
+    eng.launch_step()  # waits for rank 1's payload of step 0, which never comes
+    torch.cuda.synchronize()
+    with pytest.raises(GossipTimeout) as ei:
+        eng.check()
+    assert ei.value.peer == 1 and ei.value.step == 0
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0
 
 
 def test_wait_times_out_without_hanging():
