@@ -254,6 +254,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--steps", default=None, type=int, help="stop after this many local steps")
     p.add_argument("--wait_budget_ms", default=2000.0, type=float,
                    help="upper bound of every in-kernel wait on a peer flag")
+    p.add_argument("--nvls", default="auto", choices=("auto", "off"),
+                   help="all-reduce of the averaged-model evaluation inside the NVSwitch (multimem kernels) when the "
+                   "system has NVLink multicast; off = the process group's all_reduce")
     p.add_argument("--elastic", default=False, type=str2bool,
                    help="keep training on the survivors when a rank leaves or goes silent (heartbeat through the "
                    "rendezvous store, survivor graph with Metropolis weights)")

@@ -31,18 +31,20 @@ __device__ void find_bucket(const uint32_t* __restrict__ hist, int nbins, uint32
     local[j] = __ldcg(hist + threadIdx.x * per + j);
     sum += local[j];
   }
-  __syncthreads();
-  sh[threadIdx.x] = sum;
-  __syncthreads();
-  // inclusive suffix sums over the 256 thread sums (Hillis-Steele)
-  for (int off = 1; off < CHOCO_THREADS; off <<= 1) {
-    uint32_t v = (threadIdx.x + off < CHOCO_THREADS) ? sh[threadIdx.x + off] : 0u;
-    __syncthreads();
-    sh[threadIdx.x] += v;
-    __syncthreads();
+  // counts in the bins of all higher threads: suffix sums inside the warp by shuffles, then the totals
+  // of the higher warps
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  uint32_t suf = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t v = __shfl_down_sync(0xffffffffu, suf, o);
+    if (lane + o < 32) suf += v;
   }
-  uint32_t above = (threadIdx.x + 1 < CHOCO_THREADS) ? sh[threadIdx.x + 1] : 0u;  // bins of higher threads
+  __syncthreads();   // sh may still be read by a previous call
+  if (lane == 0) sh[wid] = suf;
   __syncthreads();
+  uint32_t above = suf - sum;
+  for (int w = wid + 1; w < CHOCO_THREADS / 32; ++w) above += sh[w];
   for (int j = per - 1; j >= 0; --j) {
     if (above < k && k <= above + local[j]) {
       sh[CHOCO_THREADS] = threadIdx.x * per + j;
@@ -486,25 +488,31 @@ __device__ bool rank_grid_barrier(uint32_t* bar, long long budget_ns, int* sh_ok
   __syncthreads();
   if (threadIdx.x == 0) {
     int ok = 1;
-    const uint32_t gen = ld_acquire_sys(bar + 1);
+    uint32_t gen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(bar + 1) : "memory");
     __threadfence();
     if (atomicAdd(bar, 1u) == gridDim.x - 1) {
       bar[0] = 0;
-      __threadfence();
-      st_release_sys(bar + 1, gen + 1u);
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bar + 1), "r"(gen + 1u) : "memory");
     } else {
-      const long long t0 = global_ns();
-      while (ld_acquire_sys(bar + 1) == gen) {
-        __nanosleep(32);
-        if (global_ns() - t0 > budget_ns) { ok = 0; break; }
+      // tight polling (a barrier is a few microseconds); the clock is read once per 256 polls only
+      long long t0 = 0;
+      for (bool done = false; !done;) {
+        for (int i = 0; i < 256; ++i) {
+          uint32_t now;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(bar + 1) : "memory");
+          if (now != gen) { done = true; break; }
+        }
+        if (done) break;
+        const long long tn = global_ns();
+        if (t0 == 0) t0 = tn;
+        else if (tn - t0 > budget_ns) { ok = 0; break; }
       }
     }
     *sh_ok = ok;
   }
   __syncthreads();
-  const bool ok = *sh_ok != 0;
-  __syncthreads();
-  return ok;
+  return *sh_ok != 0;   // (the next barrier's write to sh_ok comes after its own __syncthreads)
 }
 
 // SGD step + consensus step + difference for one chunk (the non-decoding path of choco_dense_prep)
@@ -571,8 +579,9 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_coop_kernel(const 
   uint32_t* bar = p.done_count + 4;   // words 4 (arrivals) and 5 (generation)
   const uint32_t t = p.step[0];
   const long long budget = p.wait_budget_ns;
+  // (a barrier may have to outwait CTA 0's flag wait: twice the budget plus a margin)
 #define COOP_BARRIER()                                                      \
-  if (!rank_grid_barrier(bar, budget, &sh_ok)) {                            \
+  if (!rank_grid_barrier(bar, 2 * budget + 1000000, &sh_ok)) {              \
     if (threadIdx.x == 0) report(p.status, CHOCO_TIMEOUT, p.rank, (int)t);  \
     return;                                                                 \
   }

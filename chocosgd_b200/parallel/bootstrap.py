@@ -60,6 +60,15 @@ def shutdown(collective: bool = True):
     is gone (an elastic run after a membership change), so nothing that waits for all of its ranks may
     run; the groups are dropped without a closing hand-shake."""
     if dist.is_available() and dist.is_initialized():
+        from . import nvls
+
+        if nvls.active() is not None:
+            # no rank may drop its multicast binding while another rank's kernel can still use it
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            if collective:
+                dist.barrier()
+            nvls.close()
         if collective:
             dist.destroy_process_group()
         else:

@@ -260,7 +260,7 @@ def main(argv=None):
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--graph", type=int, default=1)
     p.add_argument("--coop", default="auto", choices=("auto", "on", "off"),
-                   help="top-k / random-k step as one cooperative kernel (auto: arenas up to 4 Mi elements)")
+                   help="top-k / random-k step as one cooperative kernel (auto: the engine's default, the kernel chain)")
     run(p.parse_args(argv))
 
 

@@ -138,6 +138,22 @@ def inference(model, criterion, metrics, _input, _target, tracker=None, hidden=N
     return loss, hidden
 
 
+def _world_average(conf, run, optimizer, x):
+    """The world-averaged flat parameters: in the NVSwitch (``parallel/nvls.py``) when the system has
+    multicast and no rank may leave (not ``--elastic``, whole-world group), else the group's all-reduce."""
+    from ..parallel import nvls
+
+    group = getattr(run, "group", None)
+    if getattr(conf, "nvls", "auto") != "off" and not getattr(conf, "elastic", False) and group is None:
+        ar = nvls.enable(x.numel(), device=x.device)
+        if ar is not None:
+            out = ar.all_reduce(x, average=True).clone()
+            torch.cuda.current_stream(x.device).synchronize()
+            ar.check()
+            return out
+    return optimizer.world_aggregator._agg(x.clone(), op="avg")
+
+
 def validate(conf, graph, run, model, optimizer, criterion, scheduler, metrics, data_loader, label="local_model",
              force_evaluate_on_averaged_model=True, device=None, rank_slice=None):
     is_nlp = "rnn_lm" in conf.arch
@@ -170,7 +186,7 @@ def validate(conf, graph, run, model, optimizer, criterion, scheduler, metrics, 
 
             optimizer.finalize()
             x_local = arena.x.clone()
-            x_bar = optimizer.world_aggregator._agg(arena.x.clone(), op="avg")
+            x_bar = _world_average(conf, run, optimizer, arena.x)
             distance = float(sq_distance(x_local, x_bar).sqrt())
             arena.x.copy_(x_bar)
             try:

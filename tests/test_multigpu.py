@@ -290,3 +290,68 @@ def test_rank_leaves_between_steps_and_the_rest_continue(world):
         sim.step(lambda i, tt, x, t=t: grad_flat(survivors[i], t, seg))   # (the simulator's own clock restarts at 0)
     for i, r in enumerate(survivors):
         np.testing.assert_allclose(res[r]["x"], sim.x[i].numpy(), rtol=1e-4, atol=1e-5, err_msg=f"rank {r}")
+
+
+def _worker_nvls(rank, world, port, out):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from chocosgd_b200.parallel import nvls
+
+    try:
+        res = {}
+        ar = nvls.enable(1 << 20)
+        if ar is None:
+            res["skip"] = nvls.why_not()
+        else:
+            for n in (4, 1000, 65536 + 12, 1 << 20):
+                g = torch.Generator(device="cuda").manual_seed(1000 * rank + n)
+                x = torch.randn(n, device="cuda", generator=g)
+                ref = x.clone()
+                dist.all_reduce(ref)
+                for average in (False, True):
+                    got = ar.all_reduce(x, average=average).clone()
+                    torch.cuda.synchronize()
+                    ar.check()
+                    want = ref / world if average else ref
+                    res[(n, average)] = float((got - want).abs().max() / want.abs().max())
+                    # every rank holds the same bits: each element is computed by exactly one rank
+                    same = [torch.empty_like(got) for _ in range(world)]
+                    dist.all_gather(same, got)
+                    res[(n, average, "same")] = all(torch.equal(same[0], s) for s in same)
+        out[rank] = res
+        torch.cuda.synchronize()
+        dist.barrier()
+        nvls.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_multimem_allreduce_matches_the_library(world):
+    """``multimem.ld_reduce`` / ``multimem.st`` all-reduce kernel against NCCL (skips where the system has
+    no NVLink multicast)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    if os.environ.get("NCCL_NVLS_ENABLE", "1") == "0":
+        pytest.skip("multicast switched off for this run")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    port = free_port()
+    procs = [ctx.Process(target=_worker_nvls, args=(r, world, port, out)) for r in range(world)]
+    [p.start() for p in procs]
+    [p.join(300) for p in procs]
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    res = dict(out)
+    if "skip" in res[0]:
+        pytest.skip("no multicast: " + res[0]["skip"])
+    for r in range(world):
+        for k, v in res[r].items():
+            if len(k) == 3:
+                assert v, (r, k)
+            else:
+                assert v < 1e-5, (r, k, v)
