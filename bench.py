@@ -63,6 +63,9 @@ def parse():
     p.add_argument("--comm_op", default=None,
                    choices=("compress_top_k", "sign", "quantize_qsgd", "compress_random_k"))
     p.add_argument("--no_graph", action="store_true")
+    p.add_argument("--gossip_bucket_mb", type=float, default=None,
+                   help="gossip launched per bucket of tensors during the backward pass (sign codec); default: "
+                   "off for resnet20 / lstm, 25 for resnet50")
     p.add_argument("--native_layers", default="auto", choices=("auto", "all", "on", "off", "bn", "conv"))
     a = p.parse_args()
     a.wl = WORKLOADS[a.model]
@@ -273,7 +276,9 @@ def run_ours(args, rank, world, local):
         kw = dict(metrics=Metrics(model), amp_dtype=torch.bfloat16)
     else:
         kw = dict(metrics=Metrics(model))
-    step = TrainStep(model, criterion, optimizer, xs[0], ys[0], use_cuda_graph=not args.no_graph, **kw)
+    bucket_mb = args.gossip_bucket_mb if args.gossip_bucket_mb is not None else (25.0 if args.model == "resnet50" else 0.0)
+    step = TrainStep(model, criterion, optimizer, xs[0], ys[0], use_cuda_graph=not args.no_graph,
+                     gossip_bucket_mb=bucket_mb, **kw)
     model.train()
     loss_host = torch.zeros(args.steps + args.warmup + 8, dtype=torch.float32).pin_memory()
 
@@ -306,7 +311,8 @@ def run_ours(args, rank, world, local):
     launches = per_step * args.steps
     return dev_ms, e2e_ms, clocks, launches, float(losses[-1]), step.h2d_bytes, {
         "graph": step.use_graph, "native_layers": args.native_layers,
-        "gossip_kernels_per_step": optimizer.engine.launches_per_step, "native_kernels_per_step": per_step}
+        "gossip_kernels_per_step": optimizer.engine.launches_per_step, "native_kernels_per_step": per_step,
+        "gossip_buckets": len(optimizer.bucket_plan(step._bucket_bytes)) if step._bucket_bytes else 0}
 
 
 def run_reference(args, rank, world, local):

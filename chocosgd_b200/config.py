@@ -254,6 +254,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--steps", default=None, type=int, help="stop after this many local steps")
     p.add_argument("--wait_budget_ms", default=2000.0, type=float,
                    help="upper bound of every in-kernel wait on a peer flag")
+    p.add_argument("--gossip_bucket_mb", default=0.0, type=float,
+                   help="> 0: with the sign codec the gossip step is launched per bucket of tensors of about this "
+                   "size from gradient hooks, on a side stream, overlapping the rest of the backward pass")
     p.add_argument("--nvls", default="auto", choices=("auto", "off"),
                    help="all-reduce of the averaged-model evaluation inside the NVSwitch (multimem kernels) when the "
                    "system has NVLink multicast; off = the process group's all_reduce")

@@ -30,13 +30,17 @@ __device__ __forceinline__ float sel_sign(uint32_t word, int bit, float mag) {
 }
 
 // NP = number of peers known at compile time (unrolled register arrays), or -1 = runtime.
+// chunk0: first chunk of this launch.  A step may be issued as several launches over disjoint chunk
+// ranges (buckets of tensors, each as soon as its gradients exist): the arrival counters run over all
+// chunks of the arena, so the CTA that completes the LAST range publishes the step.
 template <int NP>
-__global__ void __launch_bounds__(CHOCO_THREADS) choco_sign_kernel(const ChocoParams* __restrict__ params, int mode) {
+__global__ void __launch_bounds__(CHOCO_THREADS) choco_sign_kernel(const ChocoParams* __restrict__ params, int mode,
+                                                                 int chunk0) {
   pdl_wait();
   pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const SegTable& tb = p.tab;
-  const int chunk = blockIdx.x;
+  const int chunk = chunk0 + blockIdx.x;
   constexpr int MAXP = NP >= 0 ? (NP > 0 ? NP : 1) : CHOCO_MAX_PEERS;
   const int n_peers = NP >= 0 ? NP : p.n_peers;
 
@@ -235,17 +239,24 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_sign_kernel(const ChocoPa
 
 // n_peers_hint: compile-time specialisation to use when every logical rank of this launch
 // has that many peers (0, 1, 2, 4, 7), anything else selects the runtime-loop variant.
-extern "C" int choco_sign_step(const void* params_dev, int n_chunks, int n_ranks, int mode, int n_peers_hint,
-                               cudaStream_t stream) {
+// chunks [chunk0, chunk0 + n_chunks) of every logical rank
+extern "C" int choco_sign_step_range(const void* params_dev, int chunk0, int n_chunks, int n_ranks, int mode,
+                                     int n_peers_hint, cudaStream_t stream) {
+  if (chunk0 < 0 || n_chunks < 1) return -1;
   dim3 grid(n_chunks, n_ranks);
   const ChocoParams* p = reinterpret_cast<const ChocoParams*>(params_dev);
   switch (n_peers_hint) {
-    case 0: launch_k(choco_sign_kernel<0>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
-    case 1: launch_k(choco_sign_kernel<1>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
-    case 2: launch_k(choco_sign_kernel<2>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
-    case 4: launch_k(choco_sign_kernel<4>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
-    case 7: launch_k(choco_sign_kernel<7>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
-    default: launch_k(choco_sign_kernel<-1>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode); break;
+    case 0: launch_k(choco_sign_kernel<0>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
+    case 1: launch_k(choco_sign_kernel<1>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
+    case 2: launch_k(choco_sign_kernel<2>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
+    case 4: launch_k(choco_sign_kernel<4>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
+    case 7: launch_k(choco_sign_kernel<7>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
+    default: launch_k(choco_sign_kernel<-1>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
   }
   return (int)cudaGetLastError();
+}
+
+extern "C" int choco_sign_step(const void* params_dev, int n_chunks, int n_ranks, int mode, int n_peers_hint,
+                               cudaStream_t stream) {
+  return choco_sign_step_range(params_dev, 0, n_chunks, n_ranks, mode, n_peers_hint, stream);
 }

@@ -67,11 +67,25 @@ __global__ void __launch_bounds__(CHOCO_THREADS) nvls_allreduce_kernel(NvlsArgs 
   const long long n4 = a.n / 4;
   const long long per = (n4 + a.world - 1) / a.world;
   const long long lo = per * a.rank, hi = lo + per < n4 ? lo + per : n4;
-  for (long long i = lo + (long long)blockIdx.x * CHOCO_THREADS + threadIdx.x; i < hi;
-       i += (long long)gridDim.x * CHOCO_THREADS) {
-    float4 v = multimem_ld_reduce_add(a.mc + 4 * i);
-    v.x *= a.scale; v.y *= a.scale; v.z *= a.scale; v.w *= a.scale;
-    multimem_st(a.mc + 4 * i, v);
+  // a load-reduce is a round trip through the switch (microseconds): NVLS_UNROLL of them are in flight per
+  // thread before the first result is used
+  constexpr int NVLS_UNROLL = 4;
+  const long long stride = (long long)gridDim.x * CHOCO_THREADS;
+  for (long long i0 = lo + (long long)blockIdx.x * CHOCO_THREADS + threadIdx.x; i0 < hi; i0 += stride * NVLS_UNROLL) {
+    float4 v[NVLS_UNROLL];
+#pragma unroll
+    for (int u = 0; u < NVLS_UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < hi) v[u] = multimem_ld_reduce_add(a.mc + 4 * i);
+    }
+#pragma unroll
+    for (int u = 0; u < NVLS_UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < hi) {
+        v[u].x *= a.scale; v[u].y *= a.scale; v[u].z *= a.scale; v[u].w *= a.scale;
+        multimem_st(a.mc + 4 * i, v[u]);
+      }
+    }
   }
   // ---- round 2: my shard has been written everywhere ------------------------------------------------
   __syncthreads();

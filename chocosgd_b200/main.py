@@ -78,6 +78,14 @@ def main(conf):
         metrics = Metrics(model, task="classification")
         best = BestPerf(best_perf=run.best_perf, larger_is_better=True)
     scheduler.set_best_tracker(best)
+    if (world > 1 and graph.on_cuda and getattr(conf, "nvls", "auto") != "off" and not conf.elastic
+            and getattr(optimizer, "arena", None) is not None):
+        # flat all-reduces (averaged-model evaluation, centralized aggregation) run inside the NVSwitch
+        # where the system has NVLink multicast; never in elastic runs, where a rank may leave
+        from .parallel import nvls
+
+        if nvls.enable(optimizer.arena.x.numel(), device=optimizer.arena.x.device) is None and rank == 0:
+            print(f"[nvls] in-switch all-reduce not used: {nvls.why_not()}")
     if conf.elastic and world > 1:
         import torch.distributed as dist
 

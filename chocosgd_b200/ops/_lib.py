@@ -129,6 +129,7 @@ def _declare(lib):
     lib.choco_cuda_error_string.argtypes = [i]
     sigs = {
         "choco_sign_step": [vp, i, i, i, i, vp],
+        "choco_sign_step_range": [vp, i, i, i, i, i, vp],
         "fused_sgd_step": [vp, i, i, i, vp],
         "grad_clip_coef": [vp, i, i, f, vp, vp],
         "sign_pack": [vp, ll, vp, vp],

@@ -555,6 +555,18 @@ class _WgradStream:
 _WGRAD_STREAM = _WgradStream()
 
 
+def wgrad_side_stream(device):
+    """The stream weight gradients are forked onto (None before its first use or when switched off)."""
+    if not _WGRAD_STREAM.enabled:
+        return None
+    device = torch.device(device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    for d, st in _WGRAD_STREAM._streams.items():
+        if d.type == device.type and (d.index if d.index is not None else torch.cuda.current_device()) == index:
+            return st
+    return None
+
+
 def set_wgrad_side_stream(on: bool):
     _WGRAD_STREAM.join()
     _WGRAD_STREAM.enabled = bool(on)

@@ -372,6 +372,26 @@ class ChocoEngine:
         self._steps += 1
         self.launches_per_step = self._n_launch
 
+    # ---- a step issued bucket by bucket (sign codec) ------------------------------------------------
+    def segment_chunk_range(self, seg_first: int, seg_last: int):
+        """Chunks of the segments ``seg_first .. seg_last`` (inclusive): ``(first chunk, count)``."""
+        first = self.tables.t["seg_first_chunk"][seg_first:seg_last + 1].tolist()
+        count = self.tables.t["seg_n_chunks"][seg_first:seg_last + 1].tolist()
+        return int(first[0]), int(first[-1] + count[-1] - first[0])
+
+    def launch_step_range(self, chunk0: int, n_chunks: int, stream=None, last: bool = False):
+        """The sign-codec step for the chunks ``[chunk0, chunk0 + n_chunks)`` only.  All ranges of a step
+        together must cover every chunk exactly once; the range that completes the arena publishes the
+        step on the device (whichever it is), ``last=True`` closes the host-side accounting."""
+        if self.codec != 3:
+            raise NotImplementedError("range launches exist for the sign codec")
+        self._chk(self.lib.choco_sign_step_range(self._pp, int(chunk0), int(n_chunks), self.n_local,
+                                                 MODE_DECODE | MODE_PUSH, self.peers_hint, _lib.stream_ptr(stream)),
+                  "choco_sign_step_range")
+        if last:
+            self._steps += 1
+            self.launches_per_step = self._n_launch
+
     def _launch_sparse_decode(self, sp):
         L, pp, nr = self.lib, self._pp, self.n_local
         self._chk(L.choco_wait_flags(pp, nr, sp), "choco_wait_flags")

@@ -118,7 +118,84 @@ class ChocoSGD(DistributedOptimizer):
 
     def launch(self, stream=None):
         """Device side of a fused step: the gossip kernels, nothing else."""
+        if self._buckets_fired is not None:
+            self._finish_buckets(stream)
+            return
         self.engine.launch_step(stream)
+
+    # ---- the step bucket by bucket, overlapped with the backward pass ---------------------------------
+    # With per-tensor compression (sign + L1 norm of each tensor) the step of one tensor depends on that
+    # tensor's gradient only.  Tensors are grouped, in arena order, into buckets of about ``bucket_bytes``;
+    # a post-accumulate-grad hook launches a bucket's part of the step on a side stream as soon as the
+    # last gradient of the bucket exists, while the backward pass of the earlier layers still runs
+    # (the reference overlaps the exchange of step t with the computation of step t + 1 from a helper
+    # thread: dl_code/pcode/optim/parallel_choco_v.py:111-113, 144-154).  ``launch()`` then only joins.
+    _buckets_fired = None
+
+    def bucket_plan(self, bucket_bytes: int):
+        """``[(param indices, first chunk, chunk count)]`` in arena order."""
+        sizes = [int(n) * 4 for n in self.seg.sizes]
+        plan, cur, acc = [], [], 0
+        for i, b in enumerate(sizes):
+            cur.append(i)
+            acc += b
+            if acc >= bucket_bytes:
+                plan.append(cur)
+                cur, acc = [], 0
+        if cur:
+            plan.append(cur)
+        return [(idx,) + self.engine.segment_chunk_range(idx[0], idx[-1]) for idx in plan]
+
+    def supports_buckets(self) -> bool:
+        return self.impl == "fused" and self.engine.codec == 3 and type(self.engine).__name__ == "ChocoEngine"
+
+    def arm_buckets(self, bucket_bytes: int, side_stream, extra_streams=()):
+        """Install the hooks for ONE backward pass (call before it; ``launch()`` disarms).  ``extra_streams``:
+        streams on which gradients may be produced besides the current one (weight-gradient stream)."""
+        plan = self.bucket_plan(bucket_bytes)
+        params = self.arena.params
+        self._buckets_fired = [False] * len(plan)
+        self._bucket_plan, self._bucket_stream = plan, side_stream
+        left = [len(idx) for idx, _, _ in plan]
+        self._bucket_handles = []
+        self.engine._n_launch = 0
+
+        def make_hook(b):
+            def hook(_p):
+                left[b] -= 1
+                if left[b] == 0:
+                    self._fire_bucket(b, extra_streams)
+            return hook
+
+        for b, (idx, _, _) in enumerate(plan):
+            for i in idx:
+                self._bucket_handles.append(params[i].register_post_accumulate_grad_hook(make_hook(b)))
+
+    def _fire_bucket(self, b, extra_streams=()):
+        side = self._bucket_stream
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        capturing = torch.cuda.is_current_stream_capturing()
+        for st in extra_streams:
+            with torch.cuda.stream(st):
+                joined = torch.cuda.is_current_stream_capturing()
+            if joined or not capturing:   # (a stream outside the running capture has no work of this step)
+                side.wait_stream(st)
+        _, c0, nc = self._bucket_plan[b]
+        self.engine.launch_step_range(c0, nc, stream=side)
+        self._buckets_fired[b] = True
+
+    def _finish_buckets(self, stream=None):
+        main = stream if stream is not None else torch.cuda.current_stream(self.device)
+        for h in self._bucket_handles:
+            h.remove()
+        # tensors whose gradient never arrived through a hook (unused parameters): their buckets go now
+        for b, fired in enumerate(self._buckets_fired):
+            if not fired:
+                self._fire_bucket(b)
+        main.wait_stream(self._bucket_stream)
+        self.engine._steps += 1
+        self.engine.launches_per_step = self.engine._n_launch
+        self._buckets_fired = None
 
     # ---- public ------------------------------------------------------------------------------
     def step(self, closure=None, **kargs):

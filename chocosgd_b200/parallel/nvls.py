@@ -80,10 +80,6 @@ class NvlsAllReduce:
         self.capacity = (int(capacity) + 4 * self.world - 1) // (4 * self.world) * (4 * self.world)
         total = self.capacity + FLAG_WORDS
         try:
-            try:
-                symm.enable_symm_mem_for_group(group.group_name)
-            except Exception:
-                pass  # newer releases enable every group implicitly
             self.buf = symm.empty(total, dtype=torch.float32, device=self.device)
             self.handle = symm.rendezvous(self.buf, group)
             mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
@@ -127,7 +123,7 @@ class NvlsAllReduce:
             self.data[n:n4].zero_()
         a = self.args
         a.n, a.scale = n4, (1.0 / self.world) if average else 1.0
-        grid = max(1, min(self.max_grid, 2 * self.sms, (n4 // 4 // self.world + 255) // 256))
+        grid = max(1, min(self.max_grid, 4 * self.sms, (n4 // 4 // self.world + 1023) // 1024))
         _lib.check(self.lib.nvls_allreduce(ctypes.byref(a), grid, _lib.stream_ptr(stream)), "nvls_allreduce")
         _lib.count(1)
         return self.data[:n]

@@ -41,6 +41,7 @@ class TrainStep:
         amp_dtype: Optional[torch.dtype] = None,
         warmup_iters: int = 3,
         channels_last: Optional[bool] = None,
+        gossip_bucket_mb: float = 0.0,
     ):
         self.model, self.criterion, self.opt, self.metrics = model, criterion, optimizer, metrics
         self.device = optimizer.device
@@ -70,6 +71,15 @@ class TrainStep:
         self.bn_counters = None
         self._fused_ce = False
         self._copy_stream = None
+        # gossip bucket by bucket from gradient hooks, overlapped with the rest of the backward pass
+        # (captured step, per-tensor codec, no global-norm clipping, at least two buckets)
+        self._bucket_bytes = 0
+        if (gossip_bucket_mb and self.use_graph and clip_grad_norm is None
+                and getattr(optimizer, "supports_buckets", lambda: False)()):
+            nbytes = int(gossip_bucket_mb * (1 << 20))
+            if len(optimizer.bucket_plan(nbytes)) >= 2:
+                self._bucket_bytes = nbytes
+                self._gossip_stream = torch.cuda.Stream(device=self.device)
         if self.is_cuda:
             from ..ops import nn as native_nn
 
@@ -223,6 +233,11 @@ class TrainStep:
 
         n0 = _lib.LAUNCHES[0]
         with torch.cuda.graph(self.graph, stream=s):
+            if self._bucket_bytes:
+                from ..ops.conv import wgrad_side_stream
+
+                ws = wgrad_side_stream(self.device)
+                self.opt.arm_buckets(self._bucket_bytes, self._gossip_stream, (ws,) if ws is not None else ())
             self._forward_backward()
             if self.clip is not None:
                 grad_clip_(eng, self.clip)

@@ -281,6 +281,7 @@ def train_and_validate(conf, graph, run, model, criterion, scheduler, optimizer,
                         use_cuda_graph=conf.use_cuda_graph and _input.size(0) == (conf.rnn_bptt_len if is_nlp else conf.batch_size),
                         clip_grad_norm=conf.rnn_clip if is_nlp else None, hidden=hidden,
                         amp_dtype=torch.bfloat16 if conf.dtype == "bf16" else None,
+                        gossip_bucket_mb=getattr(conf, "gossip_bucket_mb", 0.0),
                     )
             with timer("forward_pass", epoch=scheduler.epoch_):
                 loss = step_fn(_input, _target, timer=timer, scheduler=scheduler)

@@ -133,3 +133,33 @@ def test_native_layers_in_a_step_count_batches_and_join_the_side_stream():
     assert n_n == n_r == 6 and c_n == c_r and set(c_n) == {6}
     assert abs(l_n[0] - l_r[0]) < 0.02 * abs(l_r[0])  # same first step: the capture's warm-up left no trace
     assert l_n[-1] < l_n[0] and l_r[-1] < l_r[0]
+
+
+def test_gossip_issued_bucket_by_bucket_during_backward_equals_one_launch():
+    """Sign codec: the step launched per bucket of tensors from gradient hooks (side stream, inside the
+    captured graph) gives the same parameters as the single launch after the backward pass."""
+    from chocosgd_b200.train.engine import TrainStep
+    from chocosgd_b200.train.metrics import Metrics
+
+    def run(bucket_mb):
+        conf, model, opt = _build("resnet20", "sign", "fused")
+        g = torch.Generator().manual_seed(1)
+        x = torch.randn(16, 3, 32, 32, generator=g).pin_memory()
+        y = torch.randint(0, 10, (16,), generator=g).pin_memory()
+        step = TrainStep(model, torch.nn.CrossEntropyLoss(), opt, x, y, metrics=Metrics(model), use_cuda_graph=True,
+                         warmup_iters=1, gossip_bucket_mb=bucket_mb)
+        model.train()
+        torch.backends.cudnn.benchmark = False
+        torch.backends.cudnn.deterministic = True
+        for _ in range(3):
+            step(x, y)
+        opt.finalize()
+        opt.engine.check()
+        assert opt.engine.step_index() >= 3
+        return opt.arena.x.clone(), opt.x_hat.clone(), step.kernel_launches_per_step, bool(step._bucket_bytes)
+
+    x1, h1, n1, b1 = run(0.0)
+    x2, h2, n2, b2 = run(0.2)      # 1.1 MB of parameters -> 6 buckets
+    assert not b1 and b2 and n2 > n1
+    assert (x1 - x2).abs().max() <= 2e-3 * x1.abs().max()
+    assert (h1 - h2).abs().max() <= 2e-3 * h1.abs().max() + 1e-6
