@@ -109,7 +109,7 @@ def available():
     return os.path.isdir(os.path.join(REF, "pcode"))
 
 
-def build(rank, world, comm_op, batch_size, device, consensus_stepsize=0.5, model_name="resnet20"):
+def build(rank, world, comm_op, batch_size, device, consensus_stepsize=0.5, model_name="resnet20", init_state=None):
     """Reference model + optimizer + metrics for one of the benchmark workloads:
     ``resnet20`` (CIFAR shapes, fp32), ``resnet50`` (ImageNet shapes; the caller runs it under bf16
     autocast) or ``lstm`` (2 x 650 tied-weight language model, vocabulary 33 278, clip 0.4)."""
@@ -148,6 +148,8 @@ def build(rank, world, comm_op, batch_size, device, consensus_stepsize=0.5, mode
                              weight_norm=False).to(device)
     else:
         model = models.resnet(conf).to(device)
+    if init_state is not None:   # trajectory comparison: start from a given set of weights (a state dict file)
+        model.load_state_dict(torch.load(init_state, map_location=device))
     optimizer = create_optimizer.define_optimizer(conf, model)
     metrics = create_metrics.Metrics(model, task="language_modeling" if is_lm else "classification")
     if not is_lm:

@@ -63,9 +63,13 @@ def parse():
     p.add_argument("--comm_op", default=None,
                    choices=("compress_top_k", "sign", "quantize_qsgd", "compress_random_k"))
     p.add_argument("--no_graph", action="store_true")
+    p.add_argument("--trajectory", type=int, default=0,
+                   help="no timing: run this many steps from the weights in --init_file (written by the 'ours' arm, "
+                   "read by the reference arm) on the same batches and print loss and consensus error per step")
+    p.add_argument("--init_file", default=os.path.join(ROOT, "gpurun_out", "trajectory_init.pt"))
     p.add_argument("--gossip_bucket_mb", type=float, default=None,
                    help="gossip launched per bucket of tensors during the backward pass (sign codec); default: "
-                   "off for resnet20 / lstm, 25 for resnet50")
+                   "off")
     p.add_argument("--native_layers", default="auto", choices=("auto", "all", "on", "off", "bn", "conv"))
     a = p.parse_args()
     a.wl = WORKLOADS[a.model]
@@ -233,6 +237,27 @@ def keep_load_until_sampled(sampler, fn, world, quiesce=None, want=3, limit_s=6.
         torch.cuda.synchronize()
 
 
+def trajectory(args, rank, world, step_fn, flat_fn):
+    """Loss of rank 0 and consensus error sqrt(mean_i ||x_i - x_bar||^2) after every step; one JSON line."""
+    rows = []
+    for i in range(args.trajectory):
+        loss = step_fn(i)
+        torch.cuda.synchronize()
+        x = flat_fn().detach().float().clone()
+        mean = x.clone()
+        if world > 1:
+            dist.all_reduce(mean)
+            mean /= world
+        err = (x - mean).pow(2).sum()
+        if world > 1:
+            dist.all_reduce(err)
+        rows.append((float(loss), float((err / world).sqrt())))
+    if rank == 0:
+        emit({"trajectory": args.impl, "model": args.model, "comm_op": args.comm_op, "n_gpus": world,
+              "loss": [round(r[0], 5) for r in rows], "consensus_error": [round(r[1], 6) for r in rows]})
+    return None
+
+
 def run_ours(args, rank, world, local):
     from chocosgd_b200.config import get_args
     from chocosgd_b200.models import define_model
@@ -264,6 +289,13 @@ def run_ours(args, rank, world, local):
     native_nn.configure_native("auto" if args.native_layers == "on" else args.native_layers)
     loader = {"n_tokens": 33278} if args.model == "lstm" else None
     model = define_model(conf, graph, data_loader=loader, device=device, verbose=False)
+    if args.trajectory:
+        if rank == 0:
+            os.makedirs(os.path.dirname(args.init_file), exist_ok=True)
+            torch.save({k: v.detach().cpu() for k, v in model.state_dict().items()}, args.init_file)
+        if world > 1:
+            dist.barrier()
+        model.load_state_dict(torch.load(args.init_file, map_location=device))   # every rank: rank 0's weights
     optimizer = define_optimizer(conf, model, graph)
     criterion = torch.nn.CrossEntropyLoss()
     xs, ys = host_batches(rank, args.model)
@@ -276,10 +308,13 @@ def run_ours(args, rank, world, local):
         kw = dict(metrics=Metrics(model), amp_dtype=torch.bfloat16)
     else:
         kw = dict(metrics=Metrics(model))
-    bucket_mb = args.gossip_bucket_mb if args.gossip_bucket_mb is not None else (25.0 if args.model == "resnet50" else 0.0)
+    # (bucketed launches measured 27.41 ms against 27.31 ms per ResNet-50 step on one GPU: off unless asked for)
+    bucket_mb = args.gossip_bucket_mb if args.gossip_bucket_mb is not None else 0.0
     step = TrainStep(model, criterion, optimizer, xs[0], ys[0], use_cuda_graph=not args.no_graph,
                      gossip_bucket_mb=bucket_mb, **kw)
     model.train()
+    if args.trajectory:
+        return trajectory(args, rank, world, lambda i: step(xs[i % nb], ys[i % nb]), lambda: optimizer.arena.x)
     loss_host = torch.zeros(args.steps + args.warmup + 8, dtype=torch.float32).pin_memory()
 
     # warm-up: graph capture + W untimed steps through the public call
@@ -328,7 +363,8 @@ def run_reference(args, rank, world, local):
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
     torch.backends.cudnn.benchmark = True
     batch = args.wl["batch"]
-    state = ref.build(rank, world, args.comm_op, batch, device, GAMMA[args.comm_op], model_name=args.model)
+    state = ref.build(rank, world, args.comm_op, batch, device, GAMMA[args.comm_op], model_name=args.model,
+                      init_state=args.init_file if args.trajectory else None)
     xs, ys = host_batches(rank, args.model)
     nb = len(xs)
     out = {}
@@ -344,6 +380,17 @@ def run_reference(args, rank, world, local):
         it.n += 1
 
     it.n = 0
+    if args.trajectory:
+        def flat():
+            return torch.cat([p.data.reshape(-1) for p in state[1].parameters()])
+
+        def one(i):
+            it(i)
+            return out["loss"] if torch.is_tensor(out["loss"]) else torch.tensor(float(out["loss"]))
+
+        res = trajectory(args, rank, world, one, flat)
+        ref.finish(state)
+        return res
     sampler = ClockSampler(rank == 0, local)
     for i in range(max(args.warmup, 3)):
         it(i)
@@ -380,6 +427,12 @@ def main():
         emit({"impl": args.impl, "unavailable": "no CUDA device"})
         return
     rank, world, local = init_dist(args.gpus)
+    if args.trajectory:
+        (run_reference if args.impl == "reference" else run_ours)(args, rank, world, local)
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if args.impl == "reference":
         try:
             res = run_reference(args, rank, world, local)

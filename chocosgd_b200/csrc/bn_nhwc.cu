@@ -20,28 +20,7 @@
 
 #define BN_THREADS 256
 
-struct BnArgs {
-  const float* x;        // [P, C]
-  const float* dy;       // backward: upstream gradient
-  const float* y;        // backward: forward output (ReLU mask)
-  const float* residual; // forward: optional
-  const float* gamma;
-  const float* beta;
-  float* out;            // forward: y ; backward: dx
-  float* out2;           // backward: dresidual (optional)
-  float* mean;           // [C] batch mean (saved)
-  float* invstd;         // [C] 1/sqrt(var + eps) (saved)
-  float* running_mean;   // optional
-  float* running_var;    // optional
-  float* dgamma;         // [C]
-  float* dbeta;          // [C]
-  float* partial;        // [grid][2 C] scratch
-  unsigned* counter;     // arrival counter (self-resetting)
-  int P, C, relu;
-  float eps, momentum;
-  int n_partials;        // G: CTAs of the reduction kernel (set by the launcher)
-  int fused_finalize;    // 1: the elementwise kernel adds the partials (set by the launcher)
-};
+#include "bn_args.h"
 
 // per-channel sums of (a, b) over this CTA's rows -> partial; last CTA finalises
 template <bool BACKWARD>

@@ -133,7 +133,15 @@ class ChocoSGD(DistributedOptimizer):
     _buckets_fired = None
 
     def bucket_plan(self, bucket_bytes: int):
-        """``[(param indices, first chunk, chunk count)]`` in arena order."""
+        """``[(param indices, first chunk, chunk count)]`` in arena order (cached: the chunk table lives on the
+        device and must not be read while a graph is being captured)."""
+        cache = self.__dict__.setdefault("_bucket_plans", {})
+        if bucket_bytes in cache:
+            return cache[bucket_bytes]
+        cache[bucket_bytes] = plan = self._make_bucket_plan(bucket_bytes)
+        return plan
+
+    def _make_bucket_plan(self, bucket_bytes: int):
         sizes = [int(n) * 4 for n in self.seg.sizes]
         plan, cur, acc = [], [], 0
         for i, b in enumerate(sizes):
