@@ -39,6 +39,14 @@ def _lib_bn():
         lib.bn_last_error.restype = ctypes.c_int
         lib.bn_args_size.restype = ctypes.c_int
         assert lib.bn_args_size() == ctypes.sizeof(BnArgsC)
+        for name in ("bn16_forward", "bn16_backward"):
+            fn = getattr(lib, name)
+            fn.argtypes = [ctypes.POINTER(BnArgsC), ctypes.c_void_p]
+            fn.restype = ctypes.c_int
+        for name in ("bn16_supported", "bn16_reduce_grid"):
+            fn = getattr(lib, name)
+            fn.argtypes = [ctypes.c_int, ctypes.c_int]
+            fn.restype = ctypes.c_int
         lib._bn_declared = True
     return lib
 
@@ -54,6 +62,78 @@ def _get_scratch(device, P, C, lib):
                torch.zeros(1, dtype=torch.int32, device=device))
         _scratch[key] = buf
     return buf
+
+
+def _get_scratch16(device, lib):
+    """Partial-sum rows of the bf16 kernels: allocated once per device at the largest size the kernels can
+    ask for (4 CTAs per SM x 2 x 2048 channels), so that a captured graph never sees it replaced."""
+    key = (device.index, "bf16")
+    buf = _scratch.get(key)
+    if buf is None:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        buf = _scratch[key] = torch.empty(4 * sms * 2 * 2048, dtype=torch.float32, device=device)
+    return buf
+
+
+def supported16(x, C) -> bool:
+    """bf16 activations (an autocast ImageNet ResNet): ``csrc/bn_nhwc_bf16.cu``."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and x.numel() < 2 ** 31
+            and x.is_contiguous(memory_format=torch.channels_last)
+            and bool(_lib_bn().bn16_supported(x.numel() // C, C)))
+
+
+class _BnAct16Fn(torch.autograd.Function):
+    """``relu(bn(x) + residual)`` on bf16 NHWC tensors: three kernels each way (partial sums, finalize,
+    elementwise) instead of the library's statistics / transform kernels plus add and ReLU kernels."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, residual, running_mean, running_var, relu, momentum, eps):
+        lib = _lib_bn()
+        N, C, H, W = x.shape
+        y = torch.empty_like(x)
+        mean = torch.empty(C, dtype=torch.float32, device=x.device)
+        invstd = torch.empty_like(mean)
+        a = BnArgsC()
+        a.x, a.gamma, a.beta, a.out = x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr()
+        a.residual = residual.data_ptr() if residual is not None else 0
+        a.mean, a.invstd = mean.data_ptr(), invstd.data_ptr()
+        a.running_mean = running_mean.data_ptr() if running_mean is not None else 0
+        a.running_var = running_var.data_ptr() if running_var is not None else 0
+        a.partial = _get_scratch16(x.device, lib).data_ptr()
+        a.P, a.C, a.relu, a.eps, a.momentum = N * H * W, C, int(relu), float(eps), float(momentum)
+        rc = lib.bn16_forward(ctypes.byref(a), _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"bn16_forward failed ({rc})")
+        _lib.count(3)
+        ctx.save_for_backward(x, y, gamma, mean, invstd)
+        ctx.relu, ctx.has_res = bool(relu), residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib_bn()
+        x, y, gamma, mean, invstd = ctx.saved_tensors
+        N, C, H, W = x.shape
+        if dy.dtype != x.dtype:
+            dy = dy.to(x.dtype)
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = torch.empty_like(x)
+        dres = torch.empty_like(x) if (ctx.has_res and ctx.relu) else None
+        dgamma = torch.empty(C, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty_like(dgamma)
+        a = BnArgsC()
+        a.x, a.dy, a.y, a.gamma = x.data_ptr(), dy.data_ptr(), y.data_ptr(), gamma.data_ptr()
+        a.out, a.out2 = dx.data_ptr(), dres.data_ptr() if dres is not None else 0
+        a.mean, a.invstd, a.dgamma, a.dbeta = mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr()
+        a.partial = _get_scratch16(x.device, lib).data_ptr()
+        a.P, a.C, a.relu = N * H * W, C, int(ctx.relu)
+        rc = lib.bn16_backward(ctypes.byref(a), _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"bn16_backward failed ({rc})")
+        _lib.count(3)
+        if ctx.has_res and dres is None:
+            dres = dy   # no ReLU: the skip gradient is the incoming gradient itself
+        return dx, dgamma.to(gamma.dtype), dbeta.to(gamma.dtype), dres, None, None, None, None, None
 
 
 def last_error() -> int:
@@ -165,6 +245,16 @@ def bn_act(bn, x, residual=None, relu=True, stats=None, fold_res=False):
         rm = bn.running_mean if bn.track_running_stats else None
         rv = bn.running_var if bn.track_running_stats else None
         return _BnActFn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps, stats, fold_res)
+    if (native_nn.native_enabled("bn") and bn.training and bn.track_running_stats is not None and bn.affine
+            and stats is None and not fold_res and bn.weight.dtype == torch.float32 and supported16(x, bn.num_features)
+            and (residual is None or (residual.shape == x.shape and residual.dtype == x.dtype
+                                      and residual.is_contiguous(memory_format=torch.channels_last)))):
+        if bn.track_running_stats and bn.num_batches_tracked is not None and not getattr(bn, "_fused_counter", False):
+            bn.num_batches_tracked.add_(1)
+        mom = bn.momentum if bn.momentum is not None else 0.1
+        rm = bn.running_mean if bn.track_running_stats else None
+        rv = bn.running_var if bn.track_running_stats else None
+        return _BnAct16Fn.apply(x, bn.weight, bn.bias, residual, rm, rv, relu, mom, bn.eps)
     out = stock_forward(bn, x)
     if residual is not None:
         out = out + residual

@@ -83,3 +83,52 @@ print("ok")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("shape,use_res,relu", [((8, 64, 56, 56), False, True), ((4, 256, 28, 28), True, True),
+                                                ((2, 2048, 7, 7), True, True), ((3, 512, 14, 14), True, False),
+                                                ((16, 64, 112, 112), False, True), ((5, 1024, 9, 7), False, False)])
+def test_bf16_bn_act_matches_fp32_reference(shape, use_res, relu):
+    """bf16 activations (autocast ImageNet models): against the same composition computed in fp32 from
+    the bf16 inputs; differences are the bf16 rounding of the stored outputs only."""
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.bn import _BnAct16Fn, bn_act
+
+    torch.manual_seed(0)
+    C = shape[1]
+    x = (torch.randn(shape, device="cuda") * 2 + 0.5).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_()
+    res = None
+    if use_res:
+        res = torch.randn(shape, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_()
+    bn_a, bn_b = torch.nn.BatchNorm2d(C).cuda(), torch.nn.BatchNorm2d(C).cuda()
+    with torch.no_grad():
+        bn_a.weight.uniform_(0.5, 1.5)
+        bn_a.bias.uniform_(-0.5, 0.5)
+        bn_b.load_state_dict(bn_a.state_dict())
+    bn_a.train(), bn_b.train()
+    xf = x.detach().float().requires_grad_()
+    rf = res.detach().float().requires_grad_() if use_res else None
+    ref = bn_a(xf)
+    if use_res:
+        ref = ref + rf
+    if relu:
+        ref = F.relu(ref)
+    g = torch.randn_like(ref).bfloat16()
+    ins_ref = (xf, bn_a.weight, bn_a.bias) + ((rf,) if use_res else ())
+    grads_ref = torch.autograd.grad(ref, ins_ref, g.float())
+    nnn.set_native(True, which=("bn",))
+    try:
+        out = bn_act(bn_b, x, res, relu)
+        assert out.dtype == torch.bfloat16 and isinstance(out.grad_fn, _BnAct16Fn._backward_cls)
+        ins = (x, bn_b.weight, bn_b.bias) + ((res,) if use_res else ())
+        grads = torch.autograd.grad(out, ins, g)
+    finally:
+        nnn.set_native(False)
+    torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=1e-2)            # bf16 has 8 bits of mantissa
+    # a ReLU decision can differ where the pre-activation rounds to zero in bf16: compare in bulk
+    for a, b in zip(grads, grads_ref):
+        a, b = a.float(), b.float()
+        assert (a - b).norm() <= 1e-2 * b.norm() + 1e-3, ((a - b).norm().item(), b.norm().item())
+    torch.testing.assert_close(bn_b.running_mean, bn_a.running_mean, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(bn_b.running_var, bn_a.running_var, rtol=1e-4, atol=1e-5)
+    assert int(bn_b.num_batches_tracked) == 1
