@@ -15,7 +15,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib
-from .gemm import gemm
+from .gemm import gemm, gemm_x3, split_pad
 
 
 def _declare():
@@ -45,11 +45,22 @@ def last_error() -> int:
     return _declare().lstm_rec_last_error()
 
 
-def _mm_nt(a, b):
-    """a [M, K] @ b[N, K]^T."""
-    if a.shape[1] % 4 == 0 and b.shape[0] % 4 == 0 and a.is_contiguous() and b.is_contiguous():
-        return gemm(a, b)
-    return a @ b.t()
+#: the four large GEMMs of a layer (input projection; dX, dW_ih, dW_hh over the whole sequence) on the
+#: tcgen05 GEMM with split operands (fp32-grade products); False: library GEMMs
+NATIVE_GEMM = [True]
+MIN_GEMM_WORK = 1 << 28   # multiply-adds below which the library GEMM is used
+
+
+def _big(m, n, k) -> bool:
+    return NATIVE_GEMM[0] and m * n * k >= MIN_GEMM_WORK
+
+
+def _mm_nt(a, b, bias=None):
+    """a [M, K] @ b[N, K]^T (+ bias)."""
+    if _big(a.shape[0], b.shape[0], a.shape[1]):
+        return gemm_x3(split_pad(a), split_pad(b), bias)
+    out = a @ b.t()
+    return out.add_(bias) if bias is not None else out
 
 
 class _LSTMLayerFn(torch.autograd.Function):
@@ -58,7 +69,10 @@ class _LSTMLayerFn(torch.autograd.Function):
         lib = _declare()
         T, B, _ = x.shape
         H = w_hh.shape[1]
-        gates = _mm_nt(x.reshape(T * B, -1).contiguous(), w_ih).add_(b_ih + b_hh).view(T, B, 4 * H)
+        gates = _mm_nt(x.reshape(T * B, -1).contiguous(), w_ih, b_ih + b_hh)
+        if gates.stride(0) != 4 * H:
+            gates = gates.contiguous()
+        gates = gates.view(T, B, 4 * H)
         hs = torch.empty(T + 1, B, H, dtype=x.dtype, device=x.device)
         cs = torch.empty(T + 1, B, H, dtype=x.dtype, device=x.device)
         hs[0].copy_(h0)
@@ -104,9 +118,22 @@ class _LSTMLayerFn(torch.autograd.Function):
                                              _lib.ptr(dc), B, H, sp), "lstm_cell_bwd")
                 dh = dgates[t] @ w_hh
         dg2 = dgates.view(T * B, 4 * H)
-        dx = (dg2 @ w_ih).view_as(x)
-        dw_ih = dg2.t() @ x.reshape(T * B, -1)
-        dw_hh = dg2.t() @ hs[:-1].reshape(T * B, H)
+        x2, h2 = x.reshape(T * B, -1), hs[:-1].reshape(T * B, H)
+        if _big(T * B, 4 * H, x2.shape[1]):
+            dgs = split_pad(dg2)
+            m, k = x2.shape
+            tiles = -(-m // 128) * -(-k // 128)
+            dx = gemm_x3(dgs, split_pad(w_ih), b_mn=True, split_k=max(1, min(16, 296 // max(tiles, 1))),
+                         out=torch.empty((m, k), dtype=torch.float32, device=x.device)).view_as(x)
+            # weight gradients: the reduction runs over the T * B rows
+            dw_ih = gemm_x3(dgs, split_pad(x2), a_mn=True, b_mn=True,
+                            out=torch.empty_like(w_ih, memory_format=torch.contiguous_format))
+            dw_hh = gemm_x3(dgs, split_pad(h2), a_mn=True, b_mn=True,
+                            out=torch.empty_like(w_hh, memory_format=torch.contiguous_format))
+        else:
+            dx = (dg2 @ w_ih).view_as(x)
+            dw_ih = dg2.t() @ x2
+            dw_hh = dg2.t() @ h2
         db = dg2.sum(dim=0)
         return dx, dh, dc, dw_ih, dw_hh, db, db.clone()
 
