@@ -127,32 +127,48 @@ __global__ void __launch_bounds__(BN16_THREADS) bn16_reduce_kernel(BnArgs a) {
   }
 }
 
-// one thread per channel adds the G partial rows in order (double accumulation)
+// A CTA finalizes 16 channels: 16 threads per channel add strided subsets of the G partial rows (four
+// independent loads per trip), then the 16 sub-sums are added in order (double accumulation, a fixed
+// order: reproducible).
+#define BN16_FIN_CH 16
+#define BN16_FIN_SUB (BN16_THREADS / BN16_FIN_CH)
 template <bool BACKWARD>
 __global__ void __launch_bounds__(BN16_THREADS) bn16_finalize_kernel(BnArgs a) {
   pdl_wait();
   pdl_trigger();
-  const int c = blockIdx.x * BN16_THREADS + threadIdx.x;
-  if (c >= a.C) return;
+  __shared__ double sh0[BN16_FIN_SUB][BN16_FIN_CH], sh1[BN16_FIN_SUB][BN16_FIN_CH];
+  const int cl = threadIdx.x % BN16_FIN_CH, sub = threadIdx.x / BN16_FIN_CH;
+  const int c = blockIdx.x * BN16_FIN_CH + cl;
   const int C2 = 2 * a.C, G = a.n_partials;
   double t0 = 0.0, t1 = 0.0;
-  int b = 0;
-  for (; b + 3 < G; b += 4) {   // four independent loads per trip; the adds keep their order
-    float u0[4], u1[4];
+  if (c < a.C) {
+    int b = sub;
+    for (; b + 3 * BN16_FIN_SUB < G; b += 4 * BN16_FIN_SUB) {
+      float u0[4], u1[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      u0[q] = __ldcg(a.partial + (size_t)(b + q) * C2 + c);
-      u1[q] = __ldcg(a.partial + (size_t)(b + q) * C2 + a.C + c);
+      for (int q = 0; q < 4; ++q) {
+        u0[q] = __ldcg(a.partial + (size_t)(b + q * BN16_FIN_SUB) * C2 + c);
+        u1[q] = __ldcg(a.partial + (size_t)(b + q * BN16_FIN_SUB) * C2 + a.C + c);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        t0 += (double)u0[q];
+        t1 += (double)u1[q];
+      }
     }
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      t0 += (double)u0[q];
-      t1 += (double)u1[q];
+    for (; b < G; b += BN16_FIN_SUB) {
+      t0 += (double)__ldcg(a.partial + (size_t)b * C2 + c);
+      t1 += (double)__ldcg(a.partial + (size_t)b * C2 + a.C + c);
     }
   }
-  for (; b < G; ++b) {
-    t0 += (double)__ldcg(a.partial + (size_t)b * C2 + c);
-    t1 += (double)__ldcg(a.partial + (size_t)b * C2 + a.C + c);
+  sh0[sub][cl] = t0;
+  sh1[sub][cl] = t1;
+  __syncthreads();
+  if (sub != 0 || c >= a.C) return;
+  t0 = 0.0; t1 = 0.0;
+  for (int j = 0; j < BN16_FIN_SUB; ++j) {
+    t0 += sh0[j][cl];
+    t1 += sh1[j][cl];
   }
   if (!BACKWARD) {
     const double mean = t0 / a.P;
@@ -207,7 +223,7 @@ __global__ void __launch_bounds__(BN16_THREADS) bn16_fwd_apply_kernel(BnArgs a) 
     for (int u = 0; u < 2; ++u) {
       if (!in[u]) continue;
       const size_t i = i0 + u * stride;
-      const int col = (int)(i % c8) * 8;
+      const int col = (int)(i & (size_t)(c8 - 1)) * 8;   // C / 8 is a power of two
       F8 y;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -254,7 +270,7 @@ __global__ void __launch_bounds__(BN16_THREADS) bn16_bwd_apply_kernel(BnArgs a) 
     for (int u = 0; u < 2; ++u) {
       if (!in[u]) continue;
       const size_t i = i0 + u * stride;
-      const int col = (int)(i % c8) * 8;
+      const int col = (int)(i & (size_t)(c8 - 1)) * 8;   // C / 8 is a power of two
       F8 dx, g;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -292,7 +308,7 @@ extern "C" int bn16_reduce_grid(int P, int C) {
   const int rpb = BN16_THREADS / (C / 8);
   const long long trips = ((long long)P + rpb * 4 - 1) / (rpb * 4);
   long long g = (trips + 1) / 2;               // at least two trips per CTA
-  const long long cap = 4LL * bn16_sm_count();
+  const long long cap = 2LL * bn16_sm_count();
   if (g > cap) g = cap;
   return (int)(g < 1 ? 1 : g);
 }
@@ -310,7 +326,7 @@ extern "C" int bn16_forward(const BnArgs* args, cudaStream_t st) {
   if (!bn16_supported(a.P, a.C) || a.partial == nullptr) return -1;
   a.n_partials = bn16_reduce_grid(a.P, a.C);
   launch_k(bn16_reduce_kernel<false>, dim3(a.n_partials), dim3(BN16_THREADS), 0, st, a);
-  launch_k(bn16_finalize_kernel<false>, dim3((a.C + BN16_THREADS - 1) / BN16_THREADS), dim3(BN16_THREADS), 0, st, a);
+  launch_k(bn16_finalize_kernel<false>, dim3((a.C + BN16_FIN_CH - 1) / BN16_FIN_CH), dim3(BN16_THREADS), 0, st, a);
   launch_k(bn16_fwd_apply_kernel, dim3(bn16_apply_grid((long long)a.P * a.C / 8)), dim3(BN16_THREADS), 0, st, a);
   return (int)cudaGetLastError();
 }
@@ -321,7 +337,7 @@ extern "C" int bn16_backward(const BnArgs* args, cudaStream_t st) {
   if (!bn16_supported(a.P, a.C) || a.partial == nullptr) return -1;
   a.n_partials = bn16_reduce_grid(a.P, a.C);
   launch_k(bn16_reduce_kernel<true>, dim3(a.n_partials), dim3(BN16_THREADS), 0, st, a);
-  launch_k(bn16_finalize_kernel<true>, dim3((a.C + BN16_THREADS - 1) / BN16_THREADS), dim3(BN16_THREADS), 0, st, a);
+  launch_k(bn16_finalize_kernel<true>, dim3((a.C + BN16_FIN_CH - 1) / BN16_FIN_CH), dim3(BN16_THREADS), 0, st, a);
   launch_k(bn16_bwd_apply_kernel, dim3(bn16_apply_grid((long long)a.P * a.C / 8)), dim3(BN16_THREADS), 0, st, a);
   return (int)cudaGetLastError();
 }

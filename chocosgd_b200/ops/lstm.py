@@ -122,8 +122,8 @@ class _LSTMLayerFn(torch.autograd.Function):
         if _big(T * B, 4 * H, x2.shape[1]):
             dgs = split_pad(dg2)
             m, k = x2.shape
-            tiles = -(-m // 128) * -(-k // 128)
-            dx = gemm_x3(dgs, split_pad(w_ih), b_mn=True, split_k=max(1, min(16, 296 // max(tiles, 1))),
+            # (no split-K: its partial sums meet in atomics, and this layer promises run-to-run identical bits)
+            dx = gemm_x3(dgs, split_pad(w_ih), b_mn=True,
                          out=torch.empty((m, k), dtype=torch.float32, device=x.device)).view_as(x)
             # weight gradients: the reduction runs over the T * B rows
             dw_ih = gemm_x3(dgs, split_pad(x2), a_mn=True, b_mn=True,
