@@ -313,9 +313,15 @@ extern "C" int bn16_reduce_grid(int P, int C) {
   return (int)(g < 1 ? 1 : g);
 }
 
-static int bn16_apply_grid(long long n8) {
+// CTAs of an elementwise kernel: exactly one resident wave (every CTA walks the tensor with a grid stride),
+// so that no partial last wave leaves SMs idle
+template <typename K>
+static int bn16_apply_grid(K kernel, long long n8) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, BN16_THREADS, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 2;
   long long b = (n8 + 2 * BN16_THREADS - 1) / (2 * BN16_THREADS);
-  const long long cap = 8LL * bn16_sm_count();
+  const long long cap = (long long)per_sm * bn16_sm_count();
   if (b > cap) b = cap;
   return (int)(b < 1 ? 1 : b);
 }
@@ -327,7 +333,7 @@ extern "C" int bn16_forward(const BnArgs* args, cudaStream_t st) {
   a.n_partials = bn16_reduce_grid(a.P, a.C);
   launch_k(bn16_reduce_kernel<false>, dim3(a.n_partials), dim3(BN16_THREADS), 0, st, a);
   launch_k(bn16_finalize_kernel<false>, dim3((a.C + BN16_FIN_CH - 1) / BN16_FIN_CH), dim3(BN16_THREADS), 0, st, a);
-  launch_k(bn16_fwd_apply_kernel, dim3(bn16_apply_grid((long long)a.P * a.C / 8)), dim3(BN16_THREADS), 0, st, a);
+  launch_k(bn16_fwd_apply_kernel, dim3(bn16_apply_grid(bn16_fwd_apply_kernel, (long long)a.P * a.C / 8)), dim3(BN16_THREADS), 0, st, a);
   return (int)cudaGetLastError();
 }
 
@@ -338,6 +344,6 @@ extern "C" int bn16_backward(const BnArgs* args, cudaStream_t st) {
   a.n_partials = bn16_reduce_grid(a.P, a.C);
   launch_k(bn16_reduce_kernel<true>, dim3(a.n_partials), dim3(BN16_THREADS), 0, st, a);
   launch_k(bn16_finalize_kernel<true>, dim3((a.C + BN16_FIN_CH - 1) / BN16_FIN_CH), dim3(BN16_THREADS), 0, st, a);
-  launch_k(bn16_bwd_apply_kernel, dim3(bn16_apply_grid((long long)a.P * a.C / 8)), dim3(BN16_THREADS), 0, st, a);
+  launch_k(bn16_bwd_apply_kernel, dim3(bn16_apply_grid(bn16_bwd_apply_kernel, (long long)a.P * a.C / 8)), dim3(BN16_THREADS), 0, st, a);
   return (int)cudaGetLastError();
 }
