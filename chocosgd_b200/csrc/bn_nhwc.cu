@@ -453,9 +453,9 @@ static int grid_for(long long n4, int fused = 0) {
   static int cap_fused = 0;
   if (cap_fused == 0) {
     const char* e = getenv("CHOCO_BN_APPLY_CTAS");
-    cap_fused = e != nullptr && atoi(e) > 0 ? atoi(e) : 148 * 4;
+    cap_fused = e != nullptr && atoi(e) > 0 ? atoi(e) : sm_count() * 4;
   }
-  const long long cap = fused ? cap_fused : 148 * 8;
+  const long long cap = fused ? cap_fused : sm_count() * 8;
   long long b = (n4 + BN_THREADS - 1) / BN_THREADS;
   if (b > cap) b = cap;
   return (int)(b < 1 ? 1 : b);
@@ -470,7 +470,7 @@ extern "C" int bn_reduce_grid(int P, int C) {
   static int cap = 0, cap_last = 0;
   if (cap == 0) {
     const char* e = getenv("CHOCO_BN_GRID_CAP");
-    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : 148;
+    cap = e != nullptr && atoi(e) > 0 ? atoi(e) : sm_count();
     cap_last = cap < 74 ? cap : 74;
   }
   int g = (trips + 3) / 4;

@@ -170,7 +170,7 @@ extern "C" int conv_first_wgrad_parts(int N, int H, int W, int Cout) {
   const long long P = (long long)N * H * W;
   const int ppb = CF_THREADS / (Cout / 2);
   long long g = (P + ppb - 1) / ppb;
-  if (g > 148 * 2) g = 148 * 2;
+  if (g > sm_count() * 2) g = sm_count() * 2;
   return (int)(g < 1 ? 1 : g);
 }
 

@@ -190,7 +190,7 @@ extern "C" int conv3x3_wgrad16_supported(int N, int H, int W) {
 extern "C" int conv3x3_wgrad16_parts(int N, int H, int W) {
   const int th = 128 / W;
   const int n_tiles = N * (H / th);
-  const int per = (n_tiles + 147) / 148;
+  const int per = (n_tiles + sm_count() - 1) / sm_count();
   return (n_tiles + per - 1) / per;
 }
 
@@ -204,7 +204,7 @@ extern "C" int conv3x3_wgrad16(const void* x, const void* dy, void* dw, void* sc
   g.partial = reinterpret_cast<float*>(scratch);
   g.N = N; g.H = H; g.W = W;
   g.TH = 128 / W; g.tiles_h = H / g.TH; g.n_tiles = N * g.tiles_h;
-  g.tiles_per_cta = (g.n_tiles + 147) / 148;
+  g.tiles_per_cta = (g.n_tiles + sm_count() - 1) / sm_count();
   const int grid = (g.n_tiles + g.tiles_per_cta - 1) / g.tiles_per_cta;
   const int hh = g.TH + 2, hw = W + 2;
   const int smem = 2 * (128 * WG16_PS + hh * hw * WG16_PS) * 4;

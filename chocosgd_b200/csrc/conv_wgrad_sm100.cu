@@ -235,7 +235,7 @@ extern "C" int conv3x3_wgrad_parts(int N, int H, int W) {
   if (th > H) th = H;
   const int tn = 128 / (W * th);
   const int n_tiles = (N / tn) * (H / th);
-  const int per = (n_tiles + 147) / 148;
+  const int per = (n_tiles + sm_count() - 1) / sm_count();
   return (n_tiles + per - 1) / per;
 }
 
@@ -268,7 +268,7 @@ extern "C" int conv3x3_wgrad_tf32(const void* x, const void* dy, void* dw, void*
   if (g.error == nullptr) return -13;
   g.H = H; g.W = W; g.C = C; g.TH = th; g.TN = tn; g.tiles_h = H / th;
   g.n_tiles = (N / tn) * (H / th);
-  g.tiles_per_cta = (g.n_tiles + 147) / 148;
+  g.tiles_per_cta = (g.n_tiles + sm_count() - 1) / sm_count();
   dim3 grid((g.n_tiles + g.tiles_per_cta - 1) / g.tiles_per_cta, C == 64 ? 2 : 1);
   const int rc = C == 32 ? launch_wgrad<32>(mdy, mx, g, grid, st) : launch_wgrad<64>(mdy, mx, g, grid, st);
   if (rc) return rc;

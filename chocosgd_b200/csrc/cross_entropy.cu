@@ -155,7 +155,7 @@ extern "C" int cross_entropy_fused_ld(const void* logits, const void* target, vo
   if (may_ignore) {
     const long long n = (long long)B * ld;   // padding columns included: scaling them is harmless
     long long blocks = (n + 255) / 256;
-    if (blocks > 1184) blocks = 1184;
+    if (blocks > 8 * sm_count()) blocks = 8 * sm_count();
     launch_k(ce_rescale_kernel, dim3((int)blocks), dim3(256), 0, st, reinterpret_cast<float*>(dlogits), reinterpret_cast<const float*>(out), n, B);
   }
   return (int)cudaGetLastError();

@@ -10,6 +10,7 @@
 //   sq_distance    deterministic ||a - b||^2 (consensus distance ||x_i - xbar||,
 //                  dl_code/pcode/utils/auxiliary.py:18-24)
 #include "common.cuh"
+#include "launch.cuh"
 
 struct ExchangeArgs {
   const uint32_t* src;                        // payload to publish
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) dpsgd_mix_kernel(ExchangeArgs a
 
 static int grid_for_words(long long n4) {
   long long b = (n4 + CHOCO_THREADS - 1) / CHOCO_THREADS;
-  if (b > 148 * 8) b = 148 * 8;
+  if (b > sm_count() * 8) b = sm_count() * 8;
   return (int)(b < 1 ? 1 : b);
 }
 

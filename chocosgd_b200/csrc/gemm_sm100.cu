@@ -15,6 +15,7 @@
 // Every mbarrier wait is bounded: on expiry the CTA records an error code, skips to the
 // teardown (TMEM is always freed) and returns.
 #include "tc_common.cuh"
+#include "launch.cuh"
 #include <stdlib.h>
 
 #define GEMM_BM 128
@@ -555,7 +556,7 @@ extern "C" int tf32_split_pad(const void* src, long long rows, int cols, long lo
   if (rows <= 0 || cols <= 0 || ldd < cols || ldd % 4 != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(hi) & 15) != 0 || (reinterpret_cast<uintptr_t>(lo) & 15) != 0) return -1;
   long long blocks = (rows * (ldd / 4) + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   tf32_split_pad_kernel<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const float*>(src), rows, cols, lds,
                                                     reinterpret_cast<float*>(hi), reinterpret_cast<float*>(lo), ldd);
   return (int)cudaGetLastError();

@@ -4,6 +4,7 @@
 // (a 40 000 x 2000 GEMV ten times per epoch).  One warp per data row: fp32 features, fp64 dot product
 // and accumulation, a numerically stable softplus, deterministic two-level reduction.
 #include <cuda_runtime.h>
+#include "launch.cuh"
 #include <stdint.h>
 
 #define LR_THREADS 256
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(LR_THREADS) logreg_loss_kernel(const float* __
   }
 }
 
-extern "C" int logreg_loss_blocks() { return 148 * 4; }
+extern "C" int logreg_loss_blocks() { return sm_count() * 4; }
 
 // A [N, d] fp32 row-major (d % 4 == 0 and 16-byte aligned rows), y [N] fp32 (+1 / -1), x [d] fp64.
 // scratch: (blocks + 1) doubles.  out: 1 double.

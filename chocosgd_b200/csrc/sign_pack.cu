@@ -3,6 +3,7 @@
 // :129-163).  One warp ballot produces one 32-bit word: bit b of word w = (x[32 w + b] < 0).
 // Unpacking writes +1 / -1 (zero decodes to +1, like the reference's -(v - 1) mapping).
 #include "common.cuh"
+#include "launch.cuh"
 
 __global__ void sign_pack_kernel(const float* __restrict__ x, long long n, uint32_t* __restrict__ words) {
   const long long n_pad = (n + 31) & ~31ll;
@@ -27,7 +28,7 @@ extern "C" int sign_pack(const void* x, long long n, void* words, cudaStream_t s
   if (n <= 0) return 0;
   const long long n_pad = (n + 31) & ~31ll;
   long long blocks = (n_pad + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   sign_pack_kernel<<<(int)blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), n,
                                                    reinterpret_cast<uint32_t*>(words));
   return (int)cudaGetLastError();
@@ -36,7 +37,7 @@ extern "C" int sign_pack(const void* x, long long n, void* words, cudaStream_t s
 extern "C" int sign_unpack(const void* words, long long n, void* out, float scale, cudaStream_t stream) {
   if (n <= 0) return 0;
   long long blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   sign_unpack_kernel<<<(int)blocks, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(words), n,
                                                      reinterpret_cast<float*>(out), scale);
   return (int)cudaGetLastError();

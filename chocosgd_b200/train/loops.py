@@ -81,6 +81,21 @@ class _Elastic:
             return lost
         return []
 
+    def after_failure(self, error):
+        """A step failed (a send to a peer that is gone, a bounded wait that ran out): the ranks lost
+        according to the membership record, waiting up to the staleness limit for it to show one;
+        re-raises ``error`` when nobody is missing (the failure was something else)."""
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        deadline = time.time() + (self.m.stale_after_s or 5.0) + 1.0
+        lost = self.m.lost()
+        while not lost and time.time() < deadline:
+            time.sleep(0.1)
+            lost = self.m.lost()
+        if not lost:
+            raise error
+        return lost
+
     def recover(self, seen_lost, graph, model, optimizer, scheduler):
         from ..parallel.elastic import rebuild_optimizer
 
@@ -283,8 +298,21 @@ def train_and_validate(conf, graph, run, model, criterion, scheduler, optimizer,
                         amp_dtype=torch.bfloat16 if conf.dtype == "bf16" else None,
                         gossip_bucket_mb=getattr(conf, "gossip_bucket_mb", 0.0),
                     )
-            with timer("forward_pass", epoch=scheduler.epoch_):
-                loss = step_fn(_input, _target, timer=timer, scheduler=scheduler)
+            try:
+                with timer("forward_pass", epoch=scheduler.epoch_):
+                    loss = step_fn(_input, _target, timer=timer, scheduler=scheduler)
+            except RuntimeError as e:
+                # a rank left between this rank's membership check and its exchange: the send / receive (or
+                # the bounded device wait) fails instead of hanging; continue on the survivors
+                if elastic is None:
+                    raise
+                seen = elastic.after_failure(e)
+                pending.flush(logger, graph, tracker_tr, metrics.metric_names, False)
+                graph, optimizer = elastic.recover(seen, graph, model, optimizer, scheduler)
+                tracker_tr = RuntimeTracker(metrics.metric_names, on_cuda=graph.on_cuda,
+                                            world_aggregator=optimizer.world_aggregator)
+                step_fn, step_cache = None, {}
+                break
             n_bits = optimizer.n_bits
             pending.add({"n": _input.size(1) if is_nlp else _input.size(0), "bits": n_bits, "sched": _SchedView(scheduler)},
                         loss, step_fn.perf)
