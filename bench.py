@@ -386,7 +386,8 @@ def run_reference(args, rank, world, local):
 
         def one(i):
             it(i)
-            return out["loss"] if torch.is_tensor(out["loss"]) else torch.tensor(float(out["loss"]))
+            ref.finish(state)   # the helper thread's exchange must not be in flight under the collectives below
+            return out["loss"]
 
         res = trajectory(args, rank, world, one, flat)
         ref.finish(state)

@@ -49,8 +49,9 @@ __device__ __forceinline__ void bn16_st8(void* base, size_t elem_off, const F8& 
 
 // per-channel sums over this CTA's rows -> partial[blockIdx.x][2 C]
 //   forward : (sum x, sum x^2)        backward: (sum g, sum g * xhat), g = dy * [y > 0]
+// (two CTAs per SM also in the backward form, whose three operand streams need the registers)
 template <bool BACKWARD>
-__global__ void __launch_bounds__(BN16_THREADS) bn16_reduce_kernel(BnArgs a) {
+__global__ void __launch_bounds__(BN16_THREADS, 2) bn16_reduce_kernel(BnArgs a) {
   pdl_wait();
   pdl_trigger();
   __shared__ float sh[BN16_THREADS * 16];
@@ -67,12 +68,13 @@ __global__ void __launch_bounds__(BN16_THREADS) bn16_reduce_kernel(BnArgs a) {
     mu[e] = BACKWARD ? a.mean[col + e] : 0.f;
     is[e] = BACKWARD ? a.invstd[col + e] : 1.f;
   }
-  // four rows per trip: all their loads are issued before the first accumulate
-  for (int r = r0 + rsub; r < r1; r += 4 * rpb) {
-    F8 xv[4], gv[4], yv[4];
-    bool in[4];
+  // UN rows per trip: all their loads are issued before the first accumulate
+  constexpr int UN = BACKWARD ? 2 : 4;
+  for (int r = r0 + rsub; r < r1; r += UN * rpb) {
+    F8 xv[UN], gv[UN], yv[UN];
+    bool in[UN];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < UN; ++u) {
       const int rr = r + u * rpb;
       in[u] = rr < r1;
       const size_t off = (size_t)(in[u] ? rr : r) * C + col;
@@ -83,7 +85,7 @@ __global__ void __launch_bounds__(BN16_THREADS) bn16_reduce_kernel(BnArgs a) {
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < UN; ++u) {
       if (!in[u]) continue;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {

@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_sign_kernel(const ChocoPa
 }
 
 // n_peers_hint: compile-time specialisation to use when every logical rank of this launch
-// has that many peers (0, 1, 2, 4, 7), anything else selects the runtime-loop variant.
+// has that many peers (0, 1, 2, 3, 4, 7), anything else selects the runtime-loop variant.
 // chunks [chunk0, chunk0 + n_chunks) of every logical rank
 extern "C" int choco_sign_step_range(const void* params_dev, int chunk0, int n_chunks, int n_ranks, int mode,
                                      int n_peers_hint, cudaStream_t stream) {
@@ -249,6 +249,7 @@ extern "C" int choco_sign_step_range(const void* params_dev, int chunk0, int n_c
     case 0: launch_k(choco_sign_kernel<0>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
     case 1: launch_k(choco_sign_kernel<1>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
     case 2: launch_k(choco_sign_kernel<2>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
+    case 3: launch_k(choco_sign_kernel<3>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
     case 4: launch_k(choco_sign_kernel<4>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
     case 7: launch_k(choco_sign_kernel<7>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;
     default: launch_k(choco_sign_kernel<-1>, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, mode, chunk0); break;

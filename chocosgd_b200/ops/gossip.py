@@ -179,7 +179,7 @@ class ChocoEngine:
             raise ValueError(f"a rank has {peers_max} neighbours; the fused kernels support {_lib.MAX_PEERS}")
         self.max_peers = peers_max
         same = all(len([j for j in neighborhoods[r] if j != r]) == peers_max for r in self.ranks)
-        self.peers_hint = peers_max if (same and peers_max in (0, 1, 2, 4, 7)) else -1
+        self.peers_hint = peers_max if (same and peers_max in (0, 1, 2, 3, 4, 7)) else -1
 
         T, nc, dev = seg.n_segments, self.tables.n_chunks, self.device
         z = lambda n, dt: torch.zeros(n, dtype=dt, device=dev)
