@@ -184,7 +184,10 @@ __device__ __forceinline__ bool gemm_epi_bar_or(bool flag) {
   return r != 0;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// X3: the split-operand product with its three passes fused per k-block: a pipeline stage holds A_hi, A_lo,
+// B_hi and B_lo of one k-block (four TMA loads) and feeds three MMA groups (hi.hi, hi.lo, lo.hi), so every
+// operand tile is fetched once instead of twice: a third less L2 -> shared-memory traffic per FLOP.
+template <int BN, bool A_MN, bool B_MN, bool X3>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
@@ -193,11 +196,13 @@ gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int A_BYTES = GEMM_BM * GEMM_BK * 4;
   constexpr int B_BYTES = BN * GEMM_BK * 4;
+  constexpr int NST = X3 ? GEMM_STAGES / 2 : GEMM_STAGES;       // stages (an X3 stage is twice as large)
+  constexpr int SA = X3 ? 2 * A_BYTES : A_BYTES, SB = X3 ? 2 * B_BYTES : B_BYTES;
   uint8_t* sA = smem;
-  uint8_t* sB = smem + GEMM_STAGES * A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(sB + GEMM_STAGES * B_BYTES);
-  uint64_t* empty = full + GEMM_STAGES;
-  uint64_t* acc_full = empty + GEMM_STAGES;   // [2]
+  uint8_t* sB = smem + NST * SA;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sB + NST * SB);
+  uint64_t* empty = full + NST;
+  uint64_t* acc_full = empty + NST;   // [2]
   uint64_t* acc_empty = acc_full + 2;         // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -206,10 +211,10 @@ gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int tiles_m = (g.M + GEMM_BM - 1) / GEMM_BM, tiles_n = (g.N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   const int n_kb1 = (g.K + GEMM_BK - 1) / GEMM_BK;
-  const int n_kb = n_kb1 * g.passes;
+  const int n_kb = X3 ? n_kb1 : n_kb1 * g.passes;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < GEMM_STAGES; ++s) {
+    for (int s = 0; s < NST; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
     }
@@ -239,26 +244,32 @@ gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int m0 = (tile % tiles_m) * GEMM_BM, n0 = (tile / tiles_m) * BN;
       int ok = 1;
       for (int i = 0; i < n_kb; ++i, ++it) {
-        const uint32_t s = it % GEMM_STAGES;
+        const uint32_t s = it % NST;
         if (lane == 0) {
-          if (it >= GEMM_STAGES && !mbar_wait(empty + s, ((it / GEMM_STAGES) - 1) & 1)) ok = 0;
+          if (it >= NST && !mbar_wait(empty + s, ((it / NST) - 1) & 1)) ok = 0;
           if (*abort_flag) ok = 0;
-          if (ok) mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+          if (ok) mbar_expect_tx(full + s, SA + SB);
           else *abort_flag = 1;
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        const int pass = i / n_kb1;
+        const int pass = X3 ? 0 : i / n_kb1;
         const int k0 = (i % n_kb1) * GEMM_BK;
-        const CUtensorMap* pa = pass == 2 ? &map_a_lo : &map_a;   // passes: (A, B), (A, B_lo), (A_lo, B)
-        const CUtensorMap* pb = pass == 1 ? &map_b_lo : &map_b;
-        if (lane < PA) {
-          if (!A_MN) tma_load_2d(sA + s * A_BYTES, pa, full + s, k0, m0);
-          else tma_load_2d(sA + s * A_BYTES + lane * 4096, pa, full + s, m0 + 32 * lane, k0);
-        } else if (lane < PA + PB) {
-          const int j = lane - PA;
-          if (!B_MN) tma_load_2d(sB + s * B_BYTES, pb, full + s, k0, n0);
-          else tma_load_2d(sB + s * B_BYTES + j * 4096, pb, full + s, n0 + 32 * j, k0);
+        // lanes [0, PA + PB): the (hi) tiles of this iteration; X3: lanes [PA + PB, 2 (PA + PB)) the lo tiles
+        const int half = X3 ? lane / (PA + PB) : 0, l = X3 ? lane % (PA + PB) : lane;
+        const CUtensorMap* pa = (X3 ? half == 1 : pass == 2) ? &map_a_lo : &map_a;   // passes: (A, B), (A, B_lo), (A_lo, B)
+        const CUtensorMap* pb = (X3 ? half == 1 : pass == 1) ? &map_b_lo : &map_b;
+        if (half < (X3 ? 2 : 1)) {
+          if (l < PA) {
+            uint8_t* dst = sA + s * SA + half * A_BYTES;
+            if (!A_MN) tma_load_2d(dst, pa, full + s, k0, m0);
+            else tma_load_2d(dst + l * 4096, pa, full + s, m0 + 32 * l, k0);
+          } else if (l < PA + PB) {
+            const int j = l - PA;
+            uint8_t* dst = sB + s * SB + half * B_BYTES;
+            if (!B_MN) tma_load_2d(dst, pb, full + s, k0, n0);
+            else tma_load_2d(dst + j * 4096, pb, full + s, n0 + 32 * j, k0);
+          }
         }
         __syncwarp();
       }
@@ -276,15 +287,22 @@ gemm_tf32_persist_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc_fence_after();
       const uint32_t d = tmem_base + buf * BN;
       for (int i = 0; i < n_kb; ++i, ++it) {
-        const uint32_t s = it % GEMM_STAGES;
-        if (!mbar_wait(full + s, (it / GEMM_STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+        const uint32_t s = it % NST;
+        if (!mbar_wait(full + s, (it / NST) & 1)) { *abort_flag = 1; ok = false; break; }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+        const uint32_t a_addr = smem_u32(sA + s * SA), b_addr = smem_u32(sB + s * SB);
 #pragma unroll
         for (int k = 0; k < GEMM_BK / 8; ++k) {
           const uint64_t da = A_MN ? make_desc(a_addr + k * 1024, 4096, 512, 1) : make_desc(a_addr + k * 32, 16, 1024);
           const uint64_t db = B_MN ? make_desc(b_addr + k * 1024, 4096, 512, 1) : make_desc(b_addr + k * 32, 16, 1024);
           umma_tf32(d, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          if (X3) {
+            const uint32_t al = a_addr + A_BYTES, bl = b_addr + B_BYTES;
+            const uint64_t dal = A_MN ? make_desc(al + k * 1024, 4096, 512, 1) : make_desc(al + k * 32, 16, 1024);
+            const uint64_t dbl = B_MN ? make_desc(bl + k * 1024, 4096, 512, 1) : make_desc(bl + k * 32, 16, 1024);
+            umma_tf32(d, da, dbl, idesc, 1u);   // hi . lo
+            umma_tf32(d, dal, db, idesc, 1u);   // lo . hi
+          }
         }
         tc_commit(empty + s);
       }
@@ -422,19 +440,32 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   return (int)cudaGetLastError();
 }
 
-template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm_persist(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mal,
-                               const CUtensorMap& mbl, const GemmArgs& g, int grid, cudaStream_t st) {
+template <int BN, bool A_MN, bool B_MN, bool X3>
+static int launch_gemm_persist_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mal,
+                                 const CUtensorMap& mbl, const GemmArgs& g, int grid, cudaStream_t st) {
   constexpr int smem = GEMM_STAGES * (GEMM_BM * GEMM_BK * 4 + BN * GEMM_BK * 4) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_persist_kernel<BN, A_MN, B_MN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_persist_kernel<BN, A_MN, B_MN, X3>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gemm_tf32_persist_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, mal, mbl, g);
+  gemm_tf32_persist_kernel<BN, A_MN, B_MN, X3><<<grid, GEMM_THREADS, smem, st>>>(ma, mb, mal, mbl, g);
   return (int)cudaGetLastError();
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm_persist(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mal,
+                               const CUtensorMap& mbl, const GemmArgs& g, int grid, cudaStream_t st) {
+  // the fused three-pass form needs 2 (PA + PB) producer lanes: 24 at most (MN-major 128 x 256 tiles)
+  static int fused = -1;
+  if (fused < 0) {
+    const char* e = getenv("CHOCO_GEMM_X3_FUSED");
+    fused = e == nullptr || atoi(e) != 0;
+  }
+  if (g.passes == 3 && fused) return launch_gemm_persist_t<BN, A_MN, B_MN, true>(ma, mb, mal, mbl, g, grid, st);
+  return launch_gemm_persist_t<BN, A_MN, B_MN, false>(ma, mb, mal, mbl, g, grid, st);
 }
 
 template <int BN>

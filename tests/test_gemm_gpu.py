@@ -86,7 +86,9 @@ def test_gemm_split_operands_reach_fp32_accuracy(a_mn, b_mn):
     from chocosgd_b200.ops.gemm import gemm, gemm_x3, last_error, split_pad
 
     g = torch.Generator(device="cuda").manual_seed(11)
-    for (M, N, K, split_k) in ((300, 270, 650, 1), (2048, 2304, 332, 1), (130, 70, 4099, 4)):
+    # (the two large cases run the persistent kernel, whose three passes share one load of each operand tile)
+    for (M, N, K, split_k) in ((300, 270, 650, 1), (2048, 2304, 332, 1), (130, 70, 4099, 4), (4736, 2560, 650, 1),
+                               (4700, 2300, 333, 1)):
         a = torch.randn((K, M) if a_mn else (M, K), device="cuda", generator=g)
         b = torch.randn((K, N) if b_mn else (N, K), device="cuda", generator=g)
         ah, al = split_pad(a)
