@@ -59,7 +59,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   int kb_end = kb_begin + g.k_blocks_per_split;
   if (kb_end > total_kb) kb_end = total_kb;
   const int n_kb1 = kb_end - kb_begin;
-  const int n_kb = n_kb1 * g.passes;      // pipeline iterations: every pass walks the same k-blocks
+  // split-operand product (passes == 3): one pipeline stage holds A_hi, A_lo, B_hi, B_lo of a k-block and
+  // feeds the three MMA groups hi.hi, hi.lo, lo.hi (every operand tile is fetched once)
+  const bool x3 = g.passes == 3;
+  const int n_kb = n_kb1;
+  const int NST = x3 ? GEMM_STAGES / 2 : GEMM_STAGES;
+  const int SA = x3 ? 2 * A_BYTES : A_BYTES, SB = x3 ? 2 * B_BYTES : B_BYTES;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GEMM_STAGES; ++s) {
@@ -85,25 +90,26 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 4 && lane == 0) {
       // ---------------- TMA producer ----------------
       for (int i = 0; i < n_kb; ++i) {
-        const int s = i % GEMM_STAGES;
-        if (i >= GEMM_STAGES && !mbar_wait(empty + s, ((i / GEMM_STAGES) - 1) & 1)) { *abort_flag = 1; break; }
+        const int s = i % NST;
+        if (i >= NST && !mbar_wait(empty + s, ((i / NST) - 1) & 1)) { *abort_flag = 1; break; }
         if (*abort_flag) break;
-        const int pass = i / n_kb1;
-        const int k0 = (kb_begin + i % n_kb1) * GEMM_BK;
-        const CUtensorMap* pa = pass == 2 ? &map_a_lo : &map_a;   // passes: (A, B), (A, B_lo), (A_lo, B)
-        const CUtensorMap* pb = pass == 1 ? &map_b_lo : &map_b;
-        mbar_expect_tx(full + s, A_BYTES + B_BYTES);
-        if (!A_MN) {
-          tma_load_2d(sA + s * A_BYTES, pa, full + s, k0, m0);
-        } else {
-          for (int j = 0; j < GEMM_BM / 32; ++j)
-            tma_load_2d(sA + s * A_BYTES + j * 4096, pa, full + s, m0 + 32 * j, k0);
-        }
-        if (!B_MN) {
-          tma_load_2d(sB + s * B_BYTES, pb, full + s, k0, n0);
-        } else {
-          for (int j = 0; j < BN / 32; ++j)
-            tma_load_2d(sB + s * B_BYTES + j * 4096, pb, full + s, n0 + 32 * j, k0);
+        const int k0 = (kb_begin + i) * GEMM_BK;
+        mbar_expect_tx(full + s, SA + SB);
+        for (int half = 0; half < (x3 ? 2 : 1); ++half) {
+          const CUtensorMap* pa = half ? &map_a_lo : &map_a;
+          const CUtensorMap* pb = half ? &map_b_lo : &map_b;
+          uint8_t* dA = sA + s * SA + half * A_BYTES;
+          uint8_t* dB = sB + s * SB + half * B_BYTES;
+          if (!A_MN) {
+            tma_load_2d(dA, pa, full + s, k0, m0);
+          } else {
+            for (int j = 0; j < GEMM_BM / 32; ++j) tma_load_2d(dA + j * 4096, pa, full + s, m0 + 32 * j, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(dB, pb, full + s, k0, n0);
+          } else {
+            for (int j = 0; j < BN / 32; ++j) tma_load_2d(dB + j * 4096, pb, full + s, n0 + 32 * j, k0);
+          }
         }
       }
     } else if (warp == 5 && lane == 0) {
@@ -113,10 +119,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GEMM_BM >> 4) << 24);
       bool ok = true;
       for (int i = 0; i < n_kb && ok; ++i) {
-        const int s = i % GEMM_STAGES;
-        if (!mbar_wait(full + s, (i / GEMM_STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+        const int s = i % NST;
+        if (!mbar_wait(full + s, (i / NST) & 1)) { *abort_flag = 1; ok = false; break; }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(sA + s * A_BYTES), b_addr = smem_u32(sB + s * B_BYTES);
+        const uint32_t a_addr = smem_u32(sA + s * SA), b_addr = smem_u32(sB + s * SB);
 #pragma unroll
         for (int k = 0; k < GEMM_BK / 8; ++k) {
           // K-major: 32 bytes further inside the 128-byte row; MN-major: next 8 k-rows (two
@@ -124,6 +130,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint64_t da = A_MN ? make_desc(a_addr + k * 1024, 4096, 512, 1) : make_desc(a_addr + k * 32, 16, 1024);
           const uint64_t db = B_MN ? make_desc(b_addr + k * 1024, 4096, 512, 1) : make_desc(b_addr + k * 32, 16, 1024);
           umma_tf32(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          if (x3) {
+            const uint32_t al = a_addr + A_BYTES, bl = b_addr + B_BYTES;
+            const uint64_t dal = A_MN ? make_desc(al + k * 1024, 4096, 512, 1) : make_desc(al + k * 32, 16, 1024);
+            const uint64_t dbl = B_MN ? make_desc(bl + k * 1024, 4096, 512, 1) : make_desc(bl + k * 32, 16, 1024);
+            umma_tf32(tmem_base, da, dbl, idesc, 1u);   // hi . lo
+            umma_tf32(tmem_base, dal, db, idesc, 1u);   // lo . hi
+          }
         }
         tc_commit(empty + s);  // frees this stage once the MMAs above have read it
       }
