@@ -66,7 +66,7 @@ def parse():
     p.add_argument("--trajectory", type=int, default=0,
                    help="no timing: run this many steps from the weights in --init_file (written by the 'ours' arm, "
                    "read by the reference arm) on the same batches and print loss and consensus error per step")
-    p.add_argument("--init_file", default=os.path.join(ROOT, "gpurun_out", "trajectory_init.pt"))
+    p.add_argument("--init_file", default=os.path.join(tempfile.gettempdir(), "choco_trajectory_init.pt"))
     p.add_argument("--gossip_bucket_mb", type=float, default=None,
                    help="gossip launched per bucket of tensors during the backward pass (sign codec); default: "
                    "off")

@@ -10,7 +10,7 @@
 // one rank (all replicas end up bit-identical).  Replaces the averaged-model all-reduce and the
 // centralized aggregators' all_reduce (dl_code/pcode/utils/communication.py:114-122, 173-181).
 //
-// Synchronisation: two rounds of flags written into every rank's flag array with plain release
+// Synchronisation: two exchanges of flags written into every rank's flag array with plain release
 // stores over the peer mapping (slot = writer's rank, value = 2 e + 1 / 2 e + 2 for the e-th collective
 // of this buffer): "my input is in place" before the first load, "my shard is everywhere" before the
 // kernel ends.  Every wait is bounded; on expiry the kernel records {status, peer, epoch} and all CTAs
@@ -57,7 +57,7 @@ __device__ bool nvls_wait_all(const NvlsArgs& a, uint32_t want, uint32_t e, int*
 __global__ void __launch_bounds__(CHOCO_THREADS) nvls_allreduce_kernel(NvlsArgs a) {
   __shared__ int sh_ok;
   const uint32_t e = a.epoch[0];
-  // ---- round 1: every rank's input is in its buffer (it was written before this kernel started) ----
+  // ---- first flag exchange: every rank's input is in its buffer (it was written before this kernel started) ----
   if (blockIdx.x == 0 && threadIdx.x < a.world) {
     __threadfence_system();
     st_release_sys(a.flags_peer[threadIdx.x] + a.rank, 2u * e + 1u);
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(CHOCO_THREADS) nvls_allreduce_kernel(NvlsArgs 
       }
     }
   }
-  // ---- round 2: my shard has been written everywhere ------------------------------------------------
+  // ---- second flag exchange: my shard has been written everywhere ------------------------------------------------
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
