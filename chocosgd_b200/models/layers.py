@@ -17,7 +17,7 @@ BatchNorm2d = native_nn.BatchNorm2d
 BatchNorm1d = nn.BatchNorm1d
 Linear = native_nn.Linear
 ReLU = nn.ReLU
-MaxPool2d = nn.MaxPool2d
+MaxPool2d = native_nn.MaxPool2d
 AvgPool2d = nn.AvgPool2d
 Dropout = nn.Dropout
 Embedding = nn.Embedding

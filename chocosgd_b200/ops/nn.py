@@ -11,7 +11,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False, "wgrad": False, "ce": False}
+_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False, "wgrad": False, "ce": False, "pool": False}
 
 
 def set_native(enabled: bool = True, which=("linear", "conv", "lstm", "bn")):
@@ -23,7 +23,7 @@ def available_kinds():
     """Kinds of layers whose native kernels are built into this tree."""
     import importlib.util
 
-    kinds = ["bn", "linear", "wgrad", "ce"]
+    kinds = ["bn", "linear", "wgrad", "ce", "pool"]
     for kind, mod in (("conv", "conv"), ("lstm", "lstm")):
         if importlib.util.find_spec(f"{__package__}.{mod}") is not None:
             kinds.append(kind)
@@ -34,7 +34,7 @@ def available_kinds():
 #: step.  ``linear`` takes only layers large enough to fill the machine (the language model's
 #: decoder: fp32-grade products on the TF32 tensor cores against the library's fp32 FMA GEMM);
 #: ``lstm`` (persistent recurrence kernels) is opt-in through ``set_native`` / ``--native_layers all``.
-AUTO_KINDS = ("bn", "conv", "wgrad", "ce", "linear")
+AUTO_KINDS = ("bn", "conv", "wgrad", "ce", "linear", "pool")
 
 
 def configure_native(mode: str = "auto"):
@@ -75,6 +75,16 @@ class Conv2d(nn.Conv2d):
 
             if any_conv_supported(self, x):
                 return conv2d_native(self, x)
+        return super().forward(x)
+
+
+class MaxPool2d(nn.MaxPool2d):
+    def forward(self, x):
+        if _NATIVE["pool"] and x.is_cuda:
+            from .pool import maxpool_native, maxpool_supported
+
+            if maxpool_supported(self, x):
+                return maxpool_native(x)
         return super().forward(x)
 
 
