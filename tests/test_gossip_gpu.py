@@ -53,7 +53,8 @@ def _run(comm_op, topo, n, steps=6, momentum=0.9, nesterov=True, chunk=None, **k
     return sim, world, seg
 
 
-@pytest.mark.parametrize("topo,n", [("ring", 1), ("ring", 2), ("ring", 4), ("ring", 8), ("complete", 8), ("torus", 9)])
+@pytest.mark.parametrize("topo,n", [("ring", 1), ("ring", 2), ("ring", 4), ("ring", 8), ("complete", 4), ("complete", 8),
+                                    ("torus", 9)])
 def test_sign_matches_simulator(topo, n):
     sim, world, seg = _run("sign", topo, n)
     torch.testing.assert_close(world.x.cpu(), sim.x, rtol=2e-5, atol=2e-6)
