@@ -272,13 +272,11 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_generic_kernel(
       }
       const uint32_t sgn = __ballot_sync(0xffffffffu, ok && d < 0.f);
       if (lane == nbits) mine = sgn;
-      if (lane < pl) {
-        const int off = par_cur * PW + body + ((start + base) >> 5) * pl + lane;
-        p.outbox[off] = mine;
-        for (int k = 0; k < p.n_peers; ++k) p.peer_inbox[k][off] = mine;
-      }
+      if (lane < pl) p.outbox[par_cur * PW + body + ((start + base) >> 5) * pl + lane] = mine;
     }
   }
+  __syncthreads();
+  push_words(p, par_cur * PW + body + (start >> 5) * pl, (span >> 5) * pl);
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
@@ -340,13 +338,13 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_qsgd_pack_kernel(const Ch
         const uint32_t w = __ballot_sync(0xffffffffu, (lv >> b) & 1u);
         mine = (lane == b) ? w : mine;
       }
-      if (lane < PL) {
-        const int off = out0 + (base >> 5) * PL;
-        p.outbox[off] = mine;
-        for (int k = 0; k < n_peers; ++k) p.peer_inbox[k][off] = mine;
-      }
+      if (lane < PL) p.outbox[out0 + (base >> 5) * PL] = mine;
     }
   }
+  // push: the chunk's words are contiguous in the payload; copied to every neighbour's mailbox by the whole
+  // CTA (128 contiguous bytes per warp instruction; 20-byte stores per warp crossed NVLink far below link rate)
+  __syncthreads();
+  push_words(p, par_cur * PW + p.body_off + (start >> 5) * PL, (span >> 5) * PL);
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();

@@ -176,13 +176,18 @@ __global__ void __launch_bounds__(CHOCO_THREADS) choco_sign_kernel(const ChocoPa
       wbits |= __shfl_xor_sync(0xffffffffu, wbits, 1);
       wbits |= __shfl_xor_sync(0xffffffffu, wbits, 2);
       wbits |= __shfl_xor_sync(0xffffffffu, wbits, 4);
-      if (active && (threadIdx.x & 7) == 0) {
-        own_out[word] = wbits;
-#pragma unroll
-        for (int k = 0; k < MAXP; ++k)
-          if (k < n_peers) inbox_out[k][body + word] = wbits;  // NVLink store into the peer's mailbox
-      }
+      if (active && (threadIdx.x & 7) == 0) own_out[word] = wbits;
     }
+  }
+  if (do_push && n_peers > 0) {
+    // push: this chunk's sign words are contiguous; the whole CTA copies them into each neighbour's mailbox
+    // with consecutive words per thread (scattered 4-byte stores crossed NVLink far below link rate)
+    __syncthreads();
+    const int w0 = start >> 5, nw = span >> 5;
+#pragma unroll
+    for (int k = 0; k < MAXP; ++k)
+      if (k < n_peers)
+        for (int i = threadIdx.x; i < nw; i += CHOCO_THREADS) inbox_out[k][body + w0 + i] = own_out[w0 + i];
   }
   if (!do_push) {
     // decode-only launch: the last CTA records that step t-1 has been applied

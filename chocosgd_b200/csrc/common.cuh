@@ -162,6 +162,17 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want
   }
 }
 
+// Copy `n` payload words starting at word `off` of the own outbox into the same place of every
+// neighbour's mailbox: consecutive threads store consecutive words (full NVLink packets).  The words must
+// have been written by this CTA before a __syncthreads().
+__device__ __forceinline__ void push_words(const ChocoParams& p, int off, int n) {
+  for (int k = 0; k < p.n_peers; ++k) {
+    uint32_t* dst = p.peer_inbox[k] + off;
+    const uint32_t* src = p.outbox + off;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
 // ---- reductions ----------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
