@@ -19,6 +19,7 @@
 #include "launch.cuh"
 
 __device__ __forceinline__ uint32_t key_of(float d) { return __float_as_uint(d) & 0x7FFFFFFFu; }
+__device__ __forceinline__ uint32_t koff_of(const SegTable& tb, int seg) { return (uint32_t)tb.seg_koff[seg]; }
 
 // Among `nbins` counts (global memory), find the bin B with  #(bins > B) < k <= #(bins >= B).
 // Returns B and k_rem = k - #(bins > B) to every thread.  nbins is 2048 or 512.
@@ -246,6 +247,7 @@ __device__ void topk_emit_chunk(const ChocoParams& p, int chunk, uint32_t* sh /*
   }
   __syncthreads();
   uint32_t G = sh_base[0], E = sh_base[1];  // running counts before the current tile
+  const uint32_t slot_begin = koff_of(tb, seg) + G + (E < need_eq ? E : need_eq);   // first slot this chunk fills
   const int koff = tb.seg_koff[seg];
   uint32_t* out_idx = p.outbox + par_cur * PW;
   uint32_t* out_val = out_idx + sum_k;
@@ -307,11 +309,6 @@ __device__ void topk_emit_chunk(const ChocoParams& p, int chunk, uint32_t* sh /*
           const uint32_t vbits = __float_as_uint(d8[e]);
           out_idx[slot] = idx;
           out_val[slot] = vbits;
-          for (int k = 0; k < p.n_peers; ++k) {
-            uint32_t* pi = p.peer_inbox[k] + par_cur * PW;
-            pi[slot] = idx;
-            pi[sum_k + slot] = vbits;
-          }
         }
         g_run += is_gt;
         e_run += is_eq;
@@ -319,6 +316,14 @@ __device__ void topk_emit_chunk(const ChocoParams& p, int chunk, uint32_t* sh /*
     }
     G += tile_tot & 0xFFFFu;
     E += tile_tot >> 16;
+  }
+  // push: the chunk's entries occupy a contiguous range of slots; the CTA copies the index and the value
+  // range into every neighbour's mailbox with consecutive words per thread
+  {
+    const uint32_t slot_end = koff_of(tb, seg) + G + (E < need_eq ? E : need_eq);
+    __syncthreads();
+    push_words(p, par_cur * PW + (int)slot_begin, (int)(slot_end - slot_begin));
+    push_words(p, par_cur * PW + sum_k + (int)slot_begin, (int)(slot_end - slot_begin));
   }
   // the first chunk of a segment clears the segment's histograms for the next step
   if (chunk == c0) {
