@@ -170,12 +170,13 @@ __global__ void __launch_bounds__(CHOCO_THREADS) algo_prep_kernel(const ChocoPar
       wbits |= __shfl_xor_sync(0xffffffffu, wbits, 1);
       wbits |= __shfl_xor_sync(0xffffffffu, wbits, 2);
       wbits |= __shfl_xor_sync(0xffffffffu, wbits, 4);
-      if (active && (threadIdx.x & 7) == 0) {
-        const int off = par_cur * PW + body + (pos >> 5);
-        p.outbox[off] = wbits;
-        for (int k = 0; k < n_peers; ++k) p.peer_inbox[k][off] = wbits;
-      }
+      if (active && (threadIdx.x & 7) == 0) p.outbox[par_cur * PW + body + (pos >> 5)] = wbits;
     }
+  }
+  if (codec == CODEC_SIGN) {
+    // the chunk's sign words are contiguous: one coalesced copy per neighbour (see push_words)
+    __syncthreads();
+    push_words(p, par_cur * PW + body + (start >> 5), span >> 5);
   }
 
   if (codec == CODEC_TOPK) {
