@@ -6,6 +6,10 @@
     python -m chocosgd_b200.tools.kernel_bench --case conv --batch 128 --hw 32 --channels 16
     python -m chocosgd_b200.tools.kernel_bench --case wgrad --batch 128 --hw 32 --channels 16
     python -m chocosgd_b200.tools.kernel_bench --case bn --batch 128 --hw 32 --channels 16
+    python -m chocosgd_b200.tools.kernel_bench --case bn16 --batch 64 --hw 112 --channels 64        # bf16, forward + backward
+    python -m chocosgd_b200.tools.kernel_bench --case wgrad_gen --batch 128 --hw 16 --channels 32   # also --ks 1|3 --stride 2
+    python -m chocosgd_b200.tools.kernel_bench --case conv_s2 --batch 128 --hw 32 --channels 16    # strided forward + input gradient
+    python -m chocosgd_b200.tools.kernel_bench --case maxpool --batch 64 --hw 112 --channels 64
 """
 from __future__ import annotations
 
@@ -35,7 +39,10 @@ def timed(fn, iters):
 
 def main(argv=None):
     p = argparse.ArgumentParser()
-    p.add_argument("--case", required=True, choices=("sign", "topk", "qsgd", "randk", "gemm", "conv", "wgrad", "bn"))
+    p.add_argument("--case", required=True, choices=("sign", "topk", "qsgd", "randk", "gemm", "conv", "wgrad", "bn", "bn16", "wgrad_gen",
+                                                    "conv_s2", "maxpool"))
+    p.add_argument("--ks", type=int, default=3)
+    p.add_argument("--stride", type=int, default=1)
     p.add_argument("--elements", type=int, default=64 * 1024 * 1024)
     p.add_argument("--m", type=int, default=4096)
     p.add_argument("--n", type=int, default=4096)
@@ -107,6 +114,90 @@ def main(argv=None):
             dy, x, w, None, (1, 1), (1, 1), (1, 1), False, (0, 0), 1, (False, True, False)), a.iters)
         out.update(batch=a.batch, hw=a.hw, channels=c, ms=ms, ms_cudnn=ms_lib, io_GBps=2 * x.numel() * 4 / ms / 1e6,
                    error=last_error())
+    elif a.case == "bn16":
+        from ..ops import nn as nnn
+        from ..ops.bn import bn_act
+
+        c = a.channels
+        x = torch.randn(a.batch, c, a.hw, a.hw, device=dev).bfloat16().contiguous(memory_format=torch.channels_last)
+        x.requires_grad_()
+        g = torch.randn_like(x)
+        bn = torch.nn.BatchNorm2d(c).cuda().train()
+        nnn.set_native(True, which=("bn",))
+
+        def both():
+            y = bn_act(bn, x, None, True)
+            y.backward(g)
+            x.grad = None
+
+        def lib():
+            y = torch.relu(bn(x))
+            y.backward(g)
+            x.grad = None
+
+        ms = timed(both, a.iters)
+        nnn.set_native(False)
+        ms_lib = timed(lib, a.iters)
+        nbytes = x.numel() * 2
+        out.update(batch=a.batch, hw=a.hw, channels=c, ms=ms, ms_library=ms_lib, tensor_MB=nbytes / 1e6,
+                   io_GBps=(1 + 2 + 3 + 4) * nbytes / ms / 1e6)   # reduce 1, apply 2, backward reduce 3, backward apply 4
+    elif a.case == "wgrad_gen":
+        from ..ops.conv import conv_wgrad_gen, last_error
+
+        cin = a.channels
+        cout = cin if a.stride == 1 else 2 * cin
+        ho = a.hw // a.stride
+        x = torch.randn(a.batch, cin, a.hw, a.hw, device=dev).contiguous(memory_format=torch.channels_last)
+        dy = torch.randn(a.batch, cout, ho, ho, device=dev).contiguous(memory_format=torch.channels_last)
+        w = torch.randn(cout, cin, a.ks, a.ks, device=dev).contiguous(memory_format=torch.channels_last)
+        ms = timed(lambda: conv_wgrad_gen(x, dy, w, a.ks, a.stride), a.iters)
+        torch.backends.cudnn.benchmark = True
+        geom = ((a.stride, a.stride), (a.ks // 2, a.ks // 2), (1, 1), False, (0, 0), 1)
+        ms_lib = timed(lambda: torch.ops.aten.convolution_backward(dy, x, w, None, *geom, (False, True, False)), a.iters)
+        out.update(batch=a.batch, hw=a.hw, cin=cin, cout=cout, ks=a.ks, stride=a.stride, ms=ms, ms_library=ms_lib,
+                   io_GBps=(x.numel() + dy.numel()) * 4 / ms / 1e6, error=last_error())
+    elif a.case == "conv_s2":
+        import torch.nn.functional as F
+
+        from ..ops.conv import _ConvGenFn, last_error
+
+        cin, cout = a.channels, 2 * a.channels
+        x = torch.randn(a.batch, cin, a.hw, a.hw, device=dev).contiguous(memory_format=torch.channels_last).requires_grad_()
+        w = torch.randn(cout, cin, 3, 3, device=dev).contiguous(memory_format=torch.channels_last)
+        g = torch.randn(a.batch, cout, a.hw // 2, a.hw // 2, device=dev).contiguous(memory_format=torch.channels_last)
+
+        def ours():
+            y = _ConvGenFn.apply(x, w, 3, 2, False)
+            (gx,) = torch.autograd.grad(y, x, g)
+            return gx
+
+        def lib():
+            y = F.conv2d(x, w, stride=2, padding=1)
+            (gx,) = torch.autograd.grad(y, x, g)
+            return gx
+
+        ms = timed(ours, a.iters)
+        torch.backends.cudnn.benchmark = True
+        ms_lib = timed(lib, a.iters)
+        out.update(batch=a.batch, hw=a.hw, cin=cin, cout=cout, ms_fwd_plus_dgrad=ms, ms_library=ms_lib, error=last_error())
+    elif a.case == "maxpool":
+        from ..ops.pool import maxpool_native
+
+        c = a.channels
+        x = torch.randn(a.batch, c, a.hw, a.hw, device=dev).bfloat16().contiguous(memory_format=torch.channels_last)
+        x.requires_grad_()
+        g = torch.randn(a.batch, c, (a.hw + 1) // 2, (a.hw + 1) // 2, device=dev).bfloat16().contiguous(
+            memory_format=torch.channels_last)
+
+        def ours():
+            maxpool_native(x).backward(g)
+            x.grad = None
+
+        def lib():
+            torch.nn.functional.max_pool2d(x, 3, 2, 1).backward(g)
+            x.grad = None
+
+        out.update(batch=a.batch, hw=a.hw, channels=c, ms=timed(ours, a.iters), ms_library=timed(lib, a.iters))
     else:
         from ..ops import nn as nnn
         from ..ops.bn import bn_act

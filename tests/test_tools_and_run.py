@@ -191,3 +191,15 @@ def test_every_example_script_parses_with_the_cli():
     assert n_cmds >= 14
     hosts = open(os.path.join(root, "hostfile")).read().split()
     assert hosts[0] == "localhost" and hosts[1].startswith("slots=")
+
+
+def test_kernel_bench_lists_its_cases():
+    """The single-kernel bench parses its arguments without a GPU (``--help`` names every case)."""
+    import subprocess
+    import sys
+
+    r = subprocess.run([sys.executable, "-m", "chocosgd_b200.tools.kernel_bench", "--help"], capture_output=True, text=True,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0
+    for case in ("sign", "topk", "gemm", "conv", "bn16", "wgrad_gen", "conv_s2", "maxpool"):
+        assert case in r.stdout
