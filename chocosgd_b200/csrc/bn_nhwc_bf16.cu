@@ -129,10 +129,10 @@ __global__ void __launch_bounds__(BN16_THREADS, 2) bn16_reduce_kernel(BnArgs a) 
   }
 }
 
-// A CTA finalizes 4 channels: 64 threads per channel add strided subsets of the G partial rows (four
-// independent loads per trip: one or two round trips to L2 for up to 592 rows), then the 64 sub-sums are
-// added in order (double accumulation, a fixed order: reproducible).
-#define BN16_FIN_CH 4
+// A CTA finalizes 16 channels: 16 threads per channel add strided subsets of the G partial rows (four
+// independent loads per trip), then the 16 sub-sums are added in order (double accumulation, a fixed
+// order: reproducible).
+#define BN16_FIN_CH 16
 #define BN16_FIN_SUB (BN16_THREADS / BN16_FIN_CH)
 template <bool BACKWARD>
 __global__ void __launch_bounds__(BN16_THREADS) bn16_finalize_kernel(BnArgs a) {
@@ -305,20 +305,15 @@ extern "C" int bn16_supported(int P, int C) {
 }
 
 // CTAs of the reduction kernel = rows of partials ([grid][2 C] floats of scratch)
-static int bn16_reduce_grid_dir(int P, int C, int backward) {
+extern "C" int bn16_reduce_grid(int P, int C) {
   if (!bn16_supported(P, C)) return 0;
   const int rpb = BN16_THREADS / (C / 8);
   const long long trips = ((long long)P + rpb * 4 - 1) / (rpb * 4);
   long long g = (trips + 1) / 2;               // at least two trips per CTA
-  // one resident wave: the backward form (three operand streams, 94 registers) fits two CTAs per SM, the
-  // forward form four
-  const long long cap = (backward ? 2LL : 4LL) * bn16_sm_count();
+  const long long cap = 2LL * bn16_sm_count();
   if (g > cap) g = cap;
   return (int)(g < 1 ? 1 : g);
 }
-
-// upper bound of the rows of partials either direction writes ([rows][2 C] floats of scratch)
-extern "C" int bn16_reduce_grid(int P, int C) { return bn16_reduce_grid_dir(P, C, 0); }
 
 // CTAs of an elementwise kernel: exactly one resident wave (every CTA walks the tensor with a grid stride),
 // so that no partial last wave leaves SMs idle
@@ -337,7 +332,7 @@ static int bn16_apply_grid(K kernel, long long n8) {
 extern "C" int bn16_forward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (!bn16_supported(a.P, a.C) || a.partial == nullptr) return -1;
-  a.n_partials = bn16_reduce_grid_dir(a.P, a.C, 0);
+  a.n_partials = bn16_reduce_grid(a.P, a.C);
   launch_k(bn16_reduce_kernel<false>, dim3(a.n_partials), dim3(BN16_THREADS), 0, st, a);
   launch_k(bn16_finalize_kernel<false>, dim3((a.C + BN16_FIN_CH - 1) / BN16_FIN_CH), dim3(BN16_THREADS), 0, st, a);
   launch_k(bn16_fwd_apply_kernel, dim3(bn16_apply_grid(bn16_fwd_apply_kernel, (long long)a.P * a.C / 8)), dim3(BN16_THREADS), 0, st, a);
@@ -348,7 +343,7 @@ extern "C" int bn16_forward(const BnArgs* args, cudaStream_t st) {
 extern "C" int bn16_backward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (!bn16_supported(a.P, a.C) || a.partial == nullptr) return -1;
-  a.n_partials = bn16_reduce_grid_dir(a.P, a.C, 1);
+  a.n_partials = bn16_reduce_grid(a.P, a.C);
   launch_k(bn16_reduce_kernel<true>, dim3(a.n_partials), dim3(BN16_THREADS), 0, st, a);
   launch_k(bn16_finalize_kernel<true>, dim3((a.C + BN16_FIN_CH - 1) / BN16_FIN_CH), dim3(BN16_THREADS), 0, st, a);
   launch_k(bn16_bwd_apply_kernel, dim3(bn16_apply_grid(bn16_bwd_apply_kernel, (long long)a.P * a.C / 8)), dim3(BN16_THREADS), 0, st, a);
