@@ -20,7 +20,7 @@ ReLU = nn.ReLU
 MaxPool2d = native_nn.MaxPool2d
 AvgPool2d = nn.AvgPool2d
 Dropout = nn.Dropout
-Embedding = nn.Embedding
+Embedding = native_nn.Embedding
 LSTM = native_nn.LSTM
 
 

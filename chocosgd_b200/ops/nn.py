@@ -11,7 +11,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False, "wgrad": False, "ce": False, "pool": False}
+_NATIVE = {"linear": False, "conv": False, "lstm": False, "bn": False, "wgrad": False, "ce": False, "pool": False, "embed": False}
 
 
 def set_native(enabled: bool = True, which=("linear", "conv", "lstm", "bn")):
@@ -23,7 +23,7 @@ def available_kinds():
     """Kinds of layers whose native kernels are built into this tree."""
     import importlib.util
 
-    kinds = ["bn", "linear", "wgrad", "ce", "pool"]
+    kinds = ["bn", "linear", "wgrad", "ce", "pool", "embed"]
     for kind, mod in (("conv", "conv"), ("lstm", "lstm")):
         if importlib.util.find_spec(f"{__package__}.{mod}") is not None:
             kinds.append(kind)
@@ -34,7 +34,7 @@ def available_kinds():
 #: step.  ``linear`` takes only layers large enough to fill the machine (the language model's
 #: decoder: fp32-grade products on the TF32 tensor cores against the library's fp32 FMA GEMM);
 #: ``lstm`` (persistent recurrence kernels) is opt-in through ``set_native`` / ``--native_layers all``.
-AUTO_KINDS = ("bn", "conv", "wgrad", "ce", "linear", "pool")
+AUTO_KINDS = ("bn", "conv", "wgrad", "ce", "linear", "pool", "embed")
 
 
 def configure_native(mode: str = "auto"):
@@ -76,6 +76,24 @@ class Conv2d(nn.Conv2d):
             if any_conv_supported(self, x):
                 return conv2d_native(self, x)
         return super().forward(x)
+
+
+class Embedding(nn.Embedding):
+    """``tie_to_other_gradient()``: the weight is shared with a layer that produces a dense gradient of it in
+    every backward pass (tied decoder); the look-ups' gradient is then added into that gradient in place."""
+
+    def tie_to_other_gradient(self):
+        self._wants_deferred = True
+
+    def forward(self, idx):
+        if _NATIVE["embed"] and idx.is_cuda and torch.is_grad_enabled() == self.weight.requires_grad:
+            from .embedding import embedding_native, embedding_supported, enable_deferred_grad
+
+            if embedding_supported(self, idx):
+                if getattr(self, "_wants_deferred", False) and self.training and not getattr(self, "deferred_grad", False):
+                    enable_deferred_grad(self)
+                return embedding_native(self, idx)
+        return super().forward(idx)
 
 
 class MaxPool2d(nn.MaxPool2d):
