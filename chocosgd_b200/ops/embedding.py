@@ -31,7 +31,7 @@ def embedding_supported(m, idx) -> bool:
     w = m.weight
     return (idx.is_cuda and idx.dtype == torch.int64 and w.is_cuda and w.dtype == torch.float32 and w.is_contiguous()
             and m.padding_idx is None and m.max_norm is None and not m.sparse and not m.scale_grad_by_freq
-            and idx.numel() > 0)
+            and 0 < idx.numel() <= 65536)
 
 
 def last_error() -> int:
