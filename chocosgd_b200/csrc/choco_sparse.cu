@@ -445,16 +445,36 @@ __device__ void sparse_decode_entries(const ChocoParams& p, uint32_t t, int src,
   }
 }
 
+// flags bit 0: every CTA first waits (bounded) for the neighbours' flags of step t-1 (the first launch of a
+// chain); bit 1: this is the last launch of the chain: its last CTA records that step t-1 has been applied.
 __global__ void __launch_bounds__(CHOCO_THREADS) choco_sparse_decode_kernel(const ChocoParams* __restrict__ params,
-                                                                          int src, int codec, int mark_done) {
+                                                                          int src, int codec, int flags) {
   pdl_wait();
   pdl_trigger();
   const ChocoParams& p = params[blockIdx.y];
   const uint32_t t = p.step[0];
-  if (t == 0 || p.step[2] >= t || p.status[0] != CHOCO_OK) return;
-  if (src >= p.n_peers) return;  // this logical rank has fewer neighbours than the launch covers
-  (void)mark_done;
-  sparse_decode_entries(p, t, src, codec);
+  __shared__ int sh_ok;
+  const bool due = t > 0 && p.step[2] < t;
+  bool ok = due && __ldcg(p.status) == CHOCO_OK;
+  if ((flags & 1) && ok) {
+    if (threadIdx.x < p.n_peers && !wait_flag_ge(p.my_flag[threadIdx.x], t, p.wait_budget_ns))
+      report(p.status, CHOCO_TIMEOUT, p.peer_rank[threadIdx.x], (int)t - 1);
+    __syncthreads();
+    if (threadIdx.x == 0) sh_ok = __ldcg(p.status) == CHOCO_OK;
+    __syncthreads();
+    ok = sh_ok != 0;
+  }
+  if (ok && src < p.n_peers) sparse_decode_entries(p, t, src, codec);   // (fewer neighbours than the launch covers: nothing)
+  if (flags & 2) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(p.done_count + 1, 1u) == gridDim.x - 1) {
+        p.done_count[1] = 0;
+        if (due && __ldcg(p.status) == CHOCO_OK) p.step[2] = t;
+      }
+    }
+  }
 }
 
 __global__ void choco_mark_decoded_kernel(const ChocoParams* __restrict__ params) {
@@ -474,6 +494,15 @@ extern "C" int choco_sparse_decode(const void* params_dev, int n_blocks, int n_r
   }
   dim3 grid(n_blocks, n_ranks);
   launch_k(choco_sparse_decode_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream, p, src, codec, 0);
+  return (int)cudaGetLastError();
+}
+
+// one launch of a decode chain with the flag wait (flags & 1) and / or the completion mark (flags & 2) folded in
+extern "C" int choco_sparse_decode_ex(const void* params_dev, int n_blocks, int n_ranks, int src, int codec, int flags,
+                                      cudaStream_t stream) {
+  dim3 grid(n_blocks, n_ranks);
+  launch_k(choco_sparse_decode_kernel, dim3(grid), dim3(CHOCO_THREADS), 0, stream,
+           reinterpret_cast<const ChocoParams*>(params_dev), src, codec, flags);
   return (int)cudaGetLastError();
 }
 

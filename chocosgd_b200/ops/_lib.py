@@ -175,6 +175,7 @@ def _declare(lib):
         "choco_topk_emit": [vp, i, i, vp],
         "choco_randk_emit": [vp, i, i, vp],
         "choco_sparse_decode": [vp, i, i, i, i, vp],
+        "choco_sparse_decode_ex": [vp, i, i, i, i, i, vp],
         "choco_wait_flags": [vp, i, vp],
         "choco_publish": [vp, i, vp],
     }.items():

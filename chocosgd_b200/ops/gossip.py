@@ -393,11 +393,13 @@ class ChocoEngine:
             self.launches_per_step = self._n_launch
 
     def _launch_sparse_decode(self, sp):
+        """One launch per source payload (own, then each neighbour: sources are applied one after the other so
+        that s stays reproducible); the first also waits for the neighbours' flags, the last records completion."""
         L, pp, nr = self.lib, self._pp, self.n_local
-        self._chk(L.choco_wait_flags(pp, nr, sp), "choco_wait_flags")
+        last = self.max_peers - 1
         for src in range(-1, self.max_peers):
-            self._chk(L.choco_sparse_decode(pp, self.entry_blocks, nr, src, self.codec, sp), "choco_sparse_decode")
-        self._chk(L.choco_sparse_decode(pp, 1, nr, 1000, self.codec, sp), "choco_mark_decoded")
+            flags = (1 if src == -1 else 0) | (2 if src == last else 0)
+            self._chk(L.choco_sparse_decode_ex(pp, self.entry_blocks, nr, src, self.codec, flags, sp), "choco_sparse_decode")
 
     def launch_decode(self, stream=None):
         """Apply the payloads of the last push to x_hat / s (end of training, checkpoints)."""
