@@ -651,6 +651,82 @@ class _ConvFirstFn(torch.autograd.Function):
         return None, dw, None
 
 
+def _declare_stem():
+    lib = _lib.load()
+    if not getattr(lib, "_conv_stem_declared", False):
+        i, vp = ctypes.c_int, ctypes.c_void_p
+        lib.conv_stem_supported.argtypes = [i, i, i, i, i]
+        lib.conv_stem_grid.argtypes = [i, i, i]
+        lib.conv_stem_last_error.argtypes = []
+        lib.conv_stem_forward.argtypes = [vp, vp, vp, vp, i, i, i, vp]
+        lib.conv_stem_wgrad.argtypes = [vp, vp, vp, vp, i, i, i, vp]
+        for n in ("conv_stem_supported", "conv_stem_grid", "conv_stem_last_error", "conv_stem_forward", "conv_stem_wgrad"):
+            getattr(lib, n).restype = i
+        lib._conv_stem_declared = True
+    return lib
+
+
+def stem_conv_supported(m, x) -> bool:
+    """7x7 / stride 2 / pad 3 convolution of a 3-channel fp32 NHWC image into 64 bf16 channels under bf16
+    autocast (``csrc/conv_stem_bf16.cu``): the first layer of the ImageNet ResNets."""
+    if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 4 and m.weight.dtype == torch.float32):
+        return False
+    if not (torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16):
+        return False
+    if m.kernel_size != (7, 7) or m.stride != (2, 2) or m.padding != (3, 3) or m.dilation != (1, 1):
+        return False
+    if m.groups != 1 or m.bias is not None or m.padding_mode != "zeros" or x.requires_grad:
+        return False
+    if not (x.is_contiguous(memory_format=torch.channels_last) and m.weight.is_contiguous(memory_format=torch.channels_last)):
+        return False
+    n, c, h, w = x.shape
+    return bool(_declare_stem().conv_stem_supported(n, h, w, c, m.out_channels))
+
+
+def stem_last_error() -> int:
+    """1 when a bounded wait inside one of the stem kernels ran out since the last call."""
+    return _declare_stem().conv_stem_last_error()
+
+
+class _ConvStemFn(torch.autograd.Function):
+    """ImageNet stem: tcgen05 bf16 kernels that read the fp32 image directly; weight gradient only."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        lib = _declare_stem()
+        n, _, h, w = x.shape
+        ctx.save_for_backward(x, weight)
+        ctx.set_materialize_grads(False)
+        y = torch.empty((n, 64, h // 2, w // 2), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
+        rc = lib.conv_stem_forward(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), None, n, h, w, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"conv_stem_forward failed ({rc})")
+        _lib.count(1)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        if dy is None or not ctx.needs_input_grad[1]:
+            return None, None
+        x, weight = ctx.saved_tensors
+        if dy.dtype != torch.bfloat16:
+            dy = dy.to(torch.bfloat16)
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        lib = _declare_stem()
+        n, _, h, w = x.shape
+        dw = torch.empty_like(weight)
+        scratch = torch.empty(lib.conv_stem_grid(n, h, w) * 64 * 176, dtype=torch.float32, device=x.device)
+        rc = lib.conv_stem_wgrad(_lib.ptr(x), _lib.ptr(dy), _lib.ptr(dw), _lib.ptr(scratch), n, h, w, _lib.stream_ptr())
+        if rc != 0:
+            raise RuntimeError(f"conv_stem_wgrad failed ({rc})")
+        _lib.count(2)
+        return None, dw
+
+
+def conv_stem_native(m, x):
+    return _ConvStemFn.apply(x, m.weight)
+
+
 def conv2d_native(m, x, want_stats=False, fold_res=False, fold_ds=False):
     if m.in_channels == 3:
         return _ConvFirstFn.apply(x, m.weight, want_stats)

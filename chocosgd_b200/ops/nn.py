@@ -71,10 +71,12 @@ class Linear(nn.Linear):
 class Conv2d(nn.Conv2d):
     def forward(self, x):
         if _NATIVE["conv"] and x.is_cuda:
-            from .conv import any_conv_supported, conv2d_native
+            from .conv import any_conv_supported, conv2d_native, conv_stem_native, stem_conv_supported
 
             if any_conv_supported(self, x):
                 return conv2d_native(self, x)
+            if self.in_channels == 3 and stem_conv_supported(self, x):
+                return conv_stem_native(self, x)
         return super().forward(x)
 
 

@@ -10,6 +10,7 @@
     python -m chocosgd_b200.tools.kernel_bench --case wgrad_gen --batch 128 --hw 16 --channels 32   # also --ks 1|3 --stride 2
     python -m chocosgd_b200.tools.kernel_bench --case conv_s2 --batch 128 --hw 32 --channels 16    # strided forward + input gradient
     python -m chocosgd_b200.tools.kernel_bench --case maxpool --batch 64 --hw 112 --channels 64
+    python -m chocosgd_b200.tools.kernel_bench --case stem --batch 64 --hw 224                     # 7x7 / 2 bf16 stem, forward and wgrad
 """
 from __future__ import annotations
 
@@ -40,7 +41,7 @@ def timed(fn, iters):
 def main(argv=None):
     p = argparse.ArgumentParser()
     p.add_argument("--case", required=True, choices=("sign", "topk", "qsgd", "randk", "gemm", "conv", "wgrad", "bn", "bn16", "wgrad_gen",
-                                                    "conv_s2", "maxpool"))
+                                                    "conv_s2", "maxpool", "stem"))
     p.add_argument("--ks", type=int, default=3)
     p.add_argument("--stride", type=int, default=1)
     p.add_argument("--elements", type=int, default=64 * 1024 * 1024)
@@ -180,6 +181,37 @@ def main(argv=None):
         torch.backends.cudnn.benchmark = True
         ms_lib = timed(lib, a.iters)
         out.update(batch=a.batch, hw=a.hw, cin=cin, cout=cout, ms_fwd_plus_dgrad=ms, ms_library=ms_lib, error=last_error())
+    elif a.case == "stem":
+        from ..ops.conv import _ConvStemFn, stem_last_error
+
+        x = torch.randn(a.batch, 3, a.hw, a.hw, device=dev).contiguous(memory_format=torch.channels_last)
+        w = (0.05 * torch.randn(64, 3, 7, 7, device=dev)).contiguous(memory_format=torch.channels_last).requires_grad_()
+        g = torch.randn(a.batch, 64, a.hw // 2, a.hw // 2, device=dev).bfloat16().contiguous(memory_format=torch.channels_last)
+        state = {}
+
+        def fwd():
+            state["y"] = _ConvStemFn.apply(x, w)
+
+        def bwd():
+            state["y"].backward(g, retain_graph=True)
+            w.grad = None
+
+        def lib_fwd():
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                state["yl"] = torch.nn.functional.conv2d(x, w, None, 2, 3)
+
+        def lib_bwd():
+            state["yl"].backward(g, retain_graph=True)
+            w.grad = None
+
+        torch.backends.cudnn.benchmark = True
+        ms_f = timed(fwd, a.iters)
+        ms_b = timed(bwd, a.iters)
+        ms_lf = timed(lib_fwd, a.iters)
+        ms_lb = timed(lib_bwd, a.iters)
+        byt_f = x.numel() * 4 + g.numel() * 2
+        out.update(batch=a.batch, hw=a.hw, ms_fwd=ms_f, ms_wgrad=ms_b, ms_library_fwd=ms_lf, ms_library_wgrad=ms_lb,
+                   fwd_GBps=byt_f / ms_f / 1e6, wgrad_GBps=byt_f / ms_b / 1e6, error=stem_last_error())
     elif a.case == "maxpool":
         from ..ops.pool import maxpool_native
 

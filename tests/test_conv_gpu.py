@@ -338,3 +338,51 @@ def test_wgrad_warp_kernel_32_64_channels(n, c, hw):
     assert torch.equal(a, b)                      # fixed-order reduction: bitwise reproducible
     err = (a - ref).abs().max().item()
     assert err <= 5e-3 * ref.abs().max().item() + 1e-3, (err, ref.abs().max().item())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(4, 64, 64), (3, 40, 56), (2, 224, 224)])
+def test_stem_conv_bf16_matches_fp32_reference(shape):
+    """7x7 / stride 2 stem on tcgen05 (bf16 operands, fp32 accumulation) against an fp32 convolution of the
+    same bf16-rounded operands; the second shape has a ragged last tile."""
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.conv import _ConvStemFn, stem_conv_supported, stem_last_error
+
+    n, h, w = shape
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    x = torch.randn(n, 3, h, w, generator=gen).to(dev).contiguous(memory_format=torch.channels_last)
+    conv = nnn.Conv2d(3, 64, kernel_size=7, stride=2, padding=3, bias=False).to(dev).to(memory_format=torch.channels_last)
+    g = torch.randn(n, 64, h // 2, w // 2, generator=gen).to(dev).bfloat16().contiguous(memory_format=torch.channels_last)
+    nnn.set_native(True, which=("conv",))
+    try:
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            assert stem_conv_supported(conv, x)
+            y = conv(x)
+    finally:
+        nnn.set_native(False, which=("conv",))
+    assert type(y.grad_fn).__name__.startswith("_ConvStemFn")
+    assert y.dtype == torch.bfloat16 and y.is_contiguous(memory_format=torch.channels_last)
+    y.backward(g)
+    dw = conv.weight.grad.clone()
+    assert stem_last_error() == 0
+
+    old = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        xr = x.bfloat16().float()
+        wr = conv.weight.detach().bfloat16().float().requires_grad_()
+        yr = F.conv2d(xr, wr, None, 2, 3)
+        yr.backward(g.float())
+    finally:
+        torch.backends.cudnn.allow_tf32 = old
+    # the result is rounded to bf16 once: half a unit in the last of 8 bits
+    assert (y.float() - yr).abs().max().item() <= 2.0 ** -8 * yr.abs().max().item() + 1e-6
+    rel = ((dw - wr.grad).norm() / wr.grad.norm()).item()
+    assert rel < 1e-4, rel
+    # bit-reproducible (fixed-order slice reduction)
+    conv.weight.grad = None
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y2 = _ConvStemFn.apply(x, conv.weight)
+    y2.backward(g)
+    assert torch.equal(y2, y) and torch.equal(conv.weight.grad, dw)
