@@ -47,6 +47,8 @@ def _lib_bn():
             fn = getattr(lib, name)
             fn.argtypes = [ctypes.c_int, ctypes.c_int]
             fn.restype = ctypes.c_int
+        lib.bn16_last_error.argtypes = []
+        lib.bn16_last_error.restype = ctypes.c_int
         lib._bn_declared = True
     return lib
 
@@ -139,6 +141,11 @@ class _BnAct16Fn(torch.autograd.Function):
 def last_error() -> int:
     """Non-zero when a grid barrier of the one-kernel backward ran out of its wait budget."""
     return _lib_bn().bn_last_error()
+
+
+def last_error16() -> int:
+    """1 when a wait on the copy ring of a bf16 kernel ran out since the last call."""
+    return _lib_bn().bn16_last_error()
 
 
 def supported(x, C) -> bool:

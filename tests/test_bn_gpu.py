@@ -124,6 +124,9 @@ def test_bf16_bn_act_matches_fp32_reference(shape, use_res, relu):
         grads = torch.autograd.grad(out, ins, g)
     finally:
         nnn.set_native(False)
+    from chocosgd_b200.ops.bn import last_error16
+
+    assert last_error16() == 0
     torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=1e-2)            # bf16 has 8 bits of mantissa
     # a ReLU decision can differ where the pre-activation rounds to zero in bf16: compare in bulk
     for a, b in zip(grads, grads_ref):
