@@ -7,7 +7,8 @@
 //
 // Three kernels per direction: per-channel partial sums per CTA (one pass over the activation), a
 // small finalize (partials added per channel in a fixed order, in double precision: reproducible),
-// and one elementwise pass.  Replaces, per layer, the library's statistics + transform kernels and the
+// and one elementwise pass.  (Folding the finalize into the last CTAs of the first kernel was measured
+// slower on the ResNet-50 step, 13.2 ms against 12.9 ms: its two serial levels cost more than a launch.)  Replaces, per layer, the library's statistics + transform kernels and the
 // separate add / ReLU kernels forward, and ReLU-backward + reduce + elementwise kernels backward
 // (dl_code/pcode/models/resnet.py:86-127: conv -> bn -> relu ... conv -> bn -> += residual -> relu).
 //
@@ -119,23 +120,50 @@ __device__ __forceinline__ bool bn16_stream(const void* s0, const void* s1, cons
   return true;
 }
 
+// channel c from its two sums: forward (sum x, sum x^2) -> mean, invstd, running statistics;
+// backward (sum g, sum g xhat) -> dbeta, dgamma
+template <bool BACKWARD>
+__device__ __forceinline__ void bn16_finish(const BnArgs& a, int c, double t0, double t1) {
+  if (!BACKWARD) {
+    const double mean = t0 / a.P;
+    double var = t1 / a.P - mean * mean;
+    if (var < 0.0) var = 0.0;
+    a.mean[c] = (float)mean;
+    a.invstd[c] = (float)(1.0 / sqrt(var + (double)a.eps));
+    if (a.running_mean != nullptr) {
+      const double unbiased = a.P > 1 ? var * a.P / (a.P - 1) : var;
+      a.running_mean[c] = (1.f - a.momentum) * a.running_mean[c] + a.momentum * (float)mean;
+      a.running_var[c] = (1.f - a.momentum) * a.running_var[c] + a.momentum * (float)unbiased;
+    }
+  } else {
+    a.dbeta[c] = (float)t0;
+    a.dgamma[c] = (float)t1;
+  }
+}
+
 // per-channel sums over this CTA's chunks -> partial[blockIdx.x][2 C]
 //   forward : (sum x, sum x^2)        backward: (sum g, sum g * xhat), g = dy * [y > 0]
-// T: operands streamed: 1 forward (x), 2 backward without ReLU (x, dy), 3 backward with ReLU (x, dy, y)
-template <bool BACKWARD, int T>
-__global__ void __launch_bounds__(BN16_THREADS, 2) bn16_reduce_kernel(BnArgs a, int ch) {
+// T: operands streamed: 1 forward (x), 2 backward without the output (x, dy), 3 backward with ReLU (x, dy, y)
+// XMASK (T = 2): ReLU without a residual: the mask [y > 0] is recomputed from x with the forward's own
+// arithmetic (y = max(fma(x, A, B), 0) is positive exactly when the fma is) instead of reading y
+template <bool BACKWARD, int T, bool XMASK = false>
+__global__ void __launch_bounds__(BN16_THREADS, T == 1 ? 3 : 2) bn16_reduce_kernel(BnArgs a, int ch) {
   extern __shared__ __align__(128) uint8_t bn16_smem[];
   const int C = a.C, tpr = C >> 3;             // threads per row
   const int rpb = BN16_THREADS / tpr;           // rows per sweep of the CTA
   const int col = (threadIdx.x % tpr) * 8, rsub = threadIdx.x / tpr;
   pdl_wait();
   pdl_trigger();
-  float s0[8], s1[8], mu[8], is[8];
+  float s0[8], s1[8], mu[8], is[8], fA[8], fB[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     s0[e] = 0.f; s1[e] = 0.f;
     mu[e] = BACKWARD ? a.mean[col + e] : 0.f;
     is[e] = BACKWARD ? a.invstd[col + e] : 1.f;
+    if (XMASK) {
+      fA[e] = a.gamma[col + e] * is[e];
+      fB[e] = a.beta[col + e] - mu[e] * fA[e];
+    }
   }
   const bool ok = bn16_stream<T>(a.x, a.dy, a.y, (size_t)a.P * C * 2, ch, bn16_smem, bn16_error_word_dev,
                                  [&](const uint8_t* slot, size_t, uint32_t bytes) {
@@ -168,6 +196,7 @@ __global__ void __launch_bounds__(BN16_THREADS, 2) bn16_reduce_kernel(BnArgs a, 
         for (int e = 0; e < 8; ++e) {
           float g = gv.v[e];
           if (T >= 3) g = yv.v[e] > 0.f ? g : 0.f;
+          if (XMASK) g = fmaf(xv.v[e], fA[e], fB[e]) > 0.f ? g : 0.f;
           s0[e] += g;
           s1[e] = fmaf(g, (xv.v[e] - mu[e]) * is[e], s1[e]);
         }
@@ -247,21 +276,7 @@ __global__ void __launch_bounds__(BN16_THREADS) bn16_finalize_kernel(BnArgs a) {
     t0 += sh0[j][cl];
     t1 += sh1[j][cl];
   }
-  if (!BACKWARD) {
-    const double mean = t0 / a.P;
-    double var = t1 / a.P - mean * mean;
-    if (var < 0.0) var = 0.0;
-    a.mean[c] = (float)mean;
-    a.invstd[c] = (float)(1.0 / sqrt(var + (double)a.eps));
-    if (a.running_mean != nullptr) {
-      const double unbiased = a.P > 1 ? var * a.P / (a.P - 1) : var;
-      a.running_mean[c] = (1.f - a.momentum) * a.running_mean[c] + a.momentum * (float)mean;
-      a.running_var[c] = (1.f - a.momentum) * a.running_var[c] + a.momentum * (float)unbiased;
-    }
-  } else {
-    a.dbeta[c] = (float)t0;
-    a.dgamma[c] = (float)t1;
-  }
+  bn16_finish<BACKWARD>(a, c, t0, t1);
 }
 
 // Elementwise passes.  Per-channel constants are folded into (scale, shift) pairs, in registers:
@@ -315,15 +330,15 @@ __global__ void __launch_bounds__(BN16_THREADS, 2) bn16_fwd_apply_kernel(BnArgs 
   });
 }
 
-// T: 2 = x and dy (no ReLU), 3 = x, dy and y
-template <int T>
+// T: 2 = x and dy (no ReLU, or XMASK: the ReLU mask recomputed from x), 3 = x, dy and y
+template <int T, bool XMASK = false>
 __global__ void __launch_bounds__(BN16_THREADS, 2) bn16_bwd_apply_kernel(BnArgs a, int ch) {
   extern __shared__ __align__(128) uint8_t bn16_smem[];
   const int col = (threadIdx.x % (a.C >> 3)) * 8;
   pdl_wait();
   pdl_trigger();
   const float inv_p = 1.f / (float)a.P;
-  float cA[8], cBx[8], cK[8];
+  float cA[8], cBx[8], cK[8], fB[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     const float is = a.invstd[col + e], A = a.gamma[col + e] * is;
@@ -331,6 +346,7 @@ __global__ void __launch_bounds__(BN16_THREADS, 2) bn16_bwd_apply_kernel(BnArgs 
     cA[e] = A;
     cBx[e] = A * is * dg;
     cK[e] = A * (db - a.mean[col + e] * is * dg);
+    if (XMASK) fB[e] = a.beta[col + e] - a.mean[col + e] * A;
   }
   uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
   uint8_t* out2 = reinterpret_cast<uint8_t*>(a.out2);
@@ -357,6 +373,7 @@ __global__ void __launch_bounds__(BN16_THREADS, 2) bn16_bwd_apply_kernel(BnArgs 
       for (int e = 0; e < 8; ++e) {
         float gg = gv.v[e];
         if (T >= 3) gg = yv.v[e] > 0.f ? gg : 0.f;
+        if (XMASK) gg = fmaf(xv.v[e], cA[e], fB[e]) > 0.f ? gg : 0.f;
         g.v[e] = gg;
         dx.v[e] = gg * cA[e] - xv.v[e] * cBx[e] - cK[e];
       }
@@ -459,19 +476,25 @@ extern "C" int bn16_forward(const BnArgs* args, cudaStream_t st) {
   return rc ? rc : (int)cudaGetLastError();
 }
 
-// x, dy, y, out (dx), out2 (dresidual, optional): bf16 [P, C]
+// x, dy, y, out (dx), out2 (dresidual, optional): bf16 [P, C]; relu: 0 none, 1 mask from y, 2 mask from x
 extern "C" int bn16_backward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (!bn16_supported(a.P, a.C) || a.partial == nullptr || bn16_error_word() == nullptr) return -1;
-  static int occ_r2 = 0, occ_r3 = 0, occ_a2 = 0, occ_a3 = 0;
+  static int occ_r2 = 0, occ_r3 = 0, occ_a2 = 0, occ_a3 = 0, occ_rx = 0, occ_ax = 0;
+  const bool xmask = a.relu == 2;      // ReLU without a residual: the mask comes from x (beta must be given)
+  if (xmask && (a.beta == nullptr || a.out2 != nullptr)) return -1;
   int rc;
-  if (a.relu)
+  if (xmask)
+    rc = bn16_launch(bn16_reduce_kernel<true, 2, true>, bn16_smem_bytes<2>(), occ_rx, a, true, &a.n_partials, st);
+  else if (a.relu)
     rc = bn16_launch(bn16_reduce_kernel<true, 3>, bn16_smem_bytes<3>(), occ_r3, a, true, &a.n_partials, st);
   else
     rc = bn16_launch(bn16_reduce_kernel<true, 2>, bn16_smem_bytes<2>(), occ_r2, a, true, &a.n_partials, st);
   if (rc) return rc;
   launch_k(bn16_finalize_kernel<true>, dim3((a.C + BN16_FIN_CH - 1) / BN16_FIN_CH), dim3(BN16_THREADS), 0, st, a);
-  if (a.relu)
+  if (xmask)
+    rc = bn16_launch(bn16_bwd_apply_kernel<2, true>, bn16_smem_bytes<2>(), occ_ax, a, false, nullptr, st);
+  else if (a.relu)
     rc = bn16_launch(bn16_bwd_apply_kernel<3>, bn16_smem_bytes<3>(), occ_a3, a, false, nullptr, st);
   else
     rc = bn16_launch(bn16_bwd_apply_kernel<2>, bn16_smem_bytes<2>(), occ_a2, a, false, nullptr, st);

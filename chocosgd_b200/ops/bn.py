@@ -107,14 +107,14 @@ class _BnAct16Fn(torch.autograd.Function):
         if rc != 0:
             raise RuntimeError(f"bn16_forward failed ({rc})")
         _lib.count(3)
-        ctx.save_for_backward(x, y, gamma, mean, invstd)
+        ctx.save_for_backward(x, y, gamma, beta, mean, invstd)
         ctx.relu, ctx.has_res = bool(relu), residual is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
         lib = _lib_bn()
-        x, y, gamma, mean, invstd = ctx.saved_tensors
+        x, y, gamma, beta, mean, invstd = ctx.saved_tensors
         N, C, H, W = x.shape
         if dy.dtype != x.dtype:
             dy = dy.to(x.dtype)
@@ -128,7 +128,9 @@ class _BnAct16Fn(torch.autograd.Function):
         a.out, a.out2 = dx.data_ptr(), dres.data_ptr() if dres is not None else 0
         a.mean, a.invstd, a.dgamma, a.dbeta = mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr()
         a.partial = _get_scratch16(x.device, lib).data_ptr()
-        a.P, a.C, a.relu = N * H * W, C, int(ctx.relu)
+        a.beta = beta.data_ptr()
+        # ReLU without a residual: the kernels recompute the mask from x and never read y
+        a.P, a.C, a.relu = N * H * W, C, (2 if (ctx.relu and not ctx.has_res) else int(ctx.relu))
         rc = lib.bn16_backward(ctypes.byref(a), _lib.stream_ptr())
         if rc != 0:
             raise RuntimeError(f"bn16_backward failed ({rc})")
