@@ -450,8 +450,17 @@ __global__ void __launch_bounds__(256) stem7_wgrad_reduce_kernel(const float* __
   if (i >= ST_COUT * 147) return;
   const int co = i / 147, e = i % 147, r = e / 21, sc = e % 21;
   const float* src = partial + (size_t)co * ST_K + 24 * r + 3 + sc;
+  // eight independent loads per trip, added in slice order
   float acc = 0.f;
-  for (int g = 0; g < parts; ++g) acc += src[(size_t)g * ST_COUT * ST_K];
+  int g = 0;
+  for (; g + 7 < parts; g += 8) {
+    float v[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) v[q] = __ldcg(src + (size_t)(g + q) * ST_COUT * ST_K);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc += v[q];
+  }
+  for (; g < parts; ++g) acc += __ldcg(src + (size_t)g * ST_COUT * ST_K);
   dw[i] = acc;
 }
 
