@@ -73,7 +73,10 @@ template <int T> constexpr int bn16_smem_bytes() { return Bn16Ring<T>::S * T * B
 // body(slot, byte offset of the chunk, bytes of the chunk) for every chunk of this CTA; slot + t * BN16_STAGE
 // is operand t.  Returns false when a wait ran out (the error word is set and the copies in flight are
 // waited for once more before the CTA goes on to exit).
-template <int T, typename Body>
+// REVERSE: the chunks are taken from the end of the arrays backwards.  The reductions run that way and the
+// elementwise kernels forwards, so each kernel starts on the part of the tensor that its predecessor touched
+// last and that is still in L2 (a producer leaves the tail of what it wrote, a backward reader the head).
+template <int T, bool REVERSE, typename Body>
 __device__ __forceinline__ bool bn16_stream(const void* s0, const void* s1, const void* s2, size_t total, int ch,
                                             uint8_t* smem, int* error, Body&& body) {
   constexpr int S = Bn16Ring<T>::S;
@@ -82,8 +85,12 @@ __device__ __forceinline__ bool bn16_stream(const void* s0, const void* s1, cons
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * T * BN16_STAGE);
   const size_t n_chunks = (total + ch - 1) / ch;
   const int n_mine = blockIdx.x < n_chunks ? (int)((n_chunks - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+  auto chunk_off = [&](int it) {
+    const size_t k = (size_t)blockIdx.x + (size_t)it * gridDim.x;
+    return (REVERSE ? n_chunks - 1 - k : k) * (size_t)ch;
+  };
   auto issue = [&](int it) {
-    const size_t off = ((size_t)blockIdx.x + (size_t)it * gridDim.x) * ch;
+    const size_t off = chunk_off(it);
     const uint32_t bytes = (uint32_t)(total - off < (size_t)ch ? total - off : (size_t)ch);
     const int s = it % S;
     mbar_expect_tx(full + s, T * bytes);
@@ -113,7 +120,7 @@ __device__ __forceinline__ bool bn16_stream(const void* s0, const void* s1, cons
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       issue(it - 1 + S);
     }
-    const size_t off = ((size_t)blockIdx.x + (size_t)it * gridDim.x) * ch;
+    const size_t off = chunk_off(it);
     const uint32_t bytes = (uint32_t)(total - off < (size_t)ch ? total - off : (size_t)ch);
     body(smem + s * T * BN16_STAGE, off, bytes);
   }
@@ -165,7 +172,7 @@ __global__ void __launch_bounds__(BN16_THREADS, T == 1 ? 3 : 2) bn16_reduce_kern
       fB[e] = a.beta[col + e] - mu[e] * fA[e];
     }
   }
-  const bool ok = bn16_stream<T>(a.x, a.dy, a.y, (size_t)a.P * C * 2, ch, bn16_smem, bn16_error_word_dev,
+  const bool ok = bn16_stream<T, true>(a.x, a.dy, a.y, (size_t)a.P * C * 2, ch, bn16_smem, bn16_error_word_dev,
                                  [&](const uint8_t* slot, size_t, uint32_t bytes) {
     uint4 xr[BN16_PPT], gr[BN16_PPT], yr[BN16_PPT];
 #pragma unroll
@@ -300,7 +307,7 @@ __global__ void __launch_bounds__(BN16_THREADS, 2) bn16_fwd_apply_kernel(BnArgs 
   }
   uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
   const bool relu = a.relu != 0;
-  bn16_stream<T>(a.x, a.residual, nullptr, (size_t)a.P * a.C * 2, ch, bn16_smem, bn16_error_word_dev,
+  bn16_stream<T, false>(a.x, a.residual, nullptr, (size_t)a.P * a.C * 2, ch, bn16_smem, bn16_error_word_dev,
                  [&](const uint8_t* slot, size_t off, uint32_t bytes) {
     uint4 xr[BN16_PPT], rr[BN16_PPT];
 #pragma unroll
@@ -350,7 +357,7 @@ __global__ void __launch_bounds__(BN16_THREADS, 2) bn16_bwd_apply_kernel(BnArgs 
   }
   uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
   uint8_t* out2 = reinterpret_cast<uint8_t*>(a.out2);
-  bn16_stream<T>(a.x, a.dy, a.y, (size_t)a.P * a.C * 2, ch, bn16_smem, bn16_error_word_dev,
+  bn16_stream<T, false>(a.x, a.dy, a.y, (size_t)a.P * a.C * 2, ch, bn16_smem, bn16_error_word_dev,
                  [&](const uint8_t* slot, size_t off, uint32_t bytes) {
     uint4 xr[BN16_PPT], gr[BN16_PPT], yr[BN16_PPT];
 #pragma unroll
