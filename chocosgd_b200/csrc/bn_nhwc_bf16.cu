@@ -240,10 +240,11 @@ __global__ void __launch_bounds__(BN16_THREADS, T == 1 ? 3 : 2) bn16_reduce_kern
   }
 }
 
-// A CTA finalizes 16 channels: 16 threads per channel add strided subsets of the G partial rows (four
-// independent loads per trip), then the 16 sub-sums are added in order (double accumulation, a fixed
+// A CTA finalizes 4 channels: 64 threads per channel, each with at most 8 of the G <= 4 * SMs partial rows per
+// trip and all their loads issued before the first add (the kernel is a chain of L2 round trips and nothing
+// else: one trip instead of seven), then the 64 sub-sums are added in order (double accumulation, a fixed
 // order: reproducible).
-#define BN16_FIN_CH 16
+#define BN16_FIN_CH 4
 #define BN16_FIN_SUB (BN16_THREADS / BN16_FIN_CH)
 template <bool BACKWARD>
 __global__ void __launch_bounds__(BN16_THREADS) bn16_finalize_kernel(BnArgs a) {
@@ -255,23 +256,19 @@ __global__ void __launch_bounds__(BN16_THREADS) bn16_finalize_kernel(BnArgs a) {
   const int C2 = 2 * a.C, G = a.n_partials;
   double t0 = 0.0, t1 = 0.0;
   if (c < a.C) {
-    int b = sub;
-    for (; b + 3 * BN16_FIN_SUB < G; b += 4 * BN16_FIN_SUB) {
-      float u0[4], u1[4];
+    for (int b = sub; b < G; b += 8 * BN16_FIN_SUB) {
+      float u0[8], u1[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        u0[q] = __ldcg(a.partial + (size_t)(b + q * BN16_FIN_SUB) * C2 + c);
-        u1[q] = __ldcg(a.partial + (size_t)(b + q * BN16_FIN_SUB) * C2 + a.C + c);
+      for (int q = 0; q < 8; ++q) {
+        const int r = b + q * BN16_FIN_SUB;
+        u0[q] = r < G ? __ldcg(a.partial + (size_t)r * C2 + c) : 0.f;
+        u1[q] = r < G ? __ldcg(a.partial + (size_t)r * C2 + a.C + c) : 0.f;
       }
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < 8; ++q) {
         t0 += (double)u0[q];
         t1 += (double)u1[q];
       }
-    }
-    for (; b < G; b += BN16_FIN_SUB) {
-      t0 += (double)__ldcg(a.partial + (size_t)b * C2 + c);
-      t1 += (double)__ldcg(a.partial + (size_t)b * C2 + a.C + c);
     }
   }
   sh0[sub][cl] = t0;
