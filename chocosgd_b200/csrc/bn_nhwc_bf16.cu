@@ -465,10 +465,14 @@ extern "C" int bn16_reduce_grid(int P, int C) {
   return 4 * bn16_sm_count();
 }
 
+// a bulk copy wants 16-byte aligned addresses (null: operand not used)
+static bool bn16_aligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 // x, residual, out: bf16 [P, C]; partial: 4 * SMs * 2 C floats
 extern "C" int bn16_forward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (!bn16_supported(a.P, a.C) || a.partial == nullptr || bn16_error_word() == nullptr) return -1;
+  if (!bn16_aligned(a.x) || !bn16_aligned(a.residual) || !bn16_aligned(a.out)) return -4;
   static int occ_red = 0, occ_a1 = 0, occ_a2 = 0;
   int rc = bn16_launch(bn16_reduce_kernel<false, 1>, bn16_smem_bytes<1>(), occ_red, a, true, &a.n_partials, st);
   if (rc) return rc;
@@ -484,6 +488,7 @@ extern "C" int bn16_forward(const BnArgs* args, cudaStream_t st) {
 extern "C" int bn16_backward(const BnArgs* args, cudaStream_t st) {
   BnArgs a = *args;
   if (!bn16_supported(a.P, a.C) || a.partial == nullptr || bn16_error_word() == nullptr) return -1;
+  if (!bn16_aligned(a.x) || !bn16_aligned(a.dy) || !bn16_aligned(a.y) || !bn16_aligned(a.out) || !bn16_aligned(a.out2)) return -4;
   static int occ_r2 = 0, occ_r3 = 0, occ_a2 = 0, occ_a3 = 0, occ_rx = 0, occ_ax = 0;
   const bool xmask = a.relu == 2;      // ReLU without a residual: the mask comes from x (beta must be given)
   if (xmask && (a.beta == nullptr || a.out2 != nullptr)) return -1;

@@ -80,7 +80,7 @@ def _get_scratch16(device, lib):
 def supported16(x, C) -> bool:
     """bf16 activations (an autocast ImageNet ResNet): ``csrc/bn_nhwc_bf16.cu``."""
     return (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and x.numel() < 2 ** 31
-            and x.is_contiguous(memory_format=torch.channels_last)
+            and x.is_contiguous(memory_format=torch.channels_last) and x.data_ptr() % 16 == 0
             and bool(_lib_bn().bn16_supported(x.numel() // C, C)))
 
 
