@@ -142,15 +142,37 @@ __global__ void __launch_bounds__(CF_THREADS) conv_first_wgrad_kernel(ConvFirstA
   }
 }
 
-__global__ void conv_first_reduce_kernel(const float* __restrict__ partial, int n_parts, int n, float* __restrict__ dw) {
+// dw[i] = sum over slices of partial[slice][i]: 16 outputs per CTA, 16 threads per output (slices q, q + 16, ...
+// in order, eight loads in flight per trip; then the sixteen sub-sums in order).  The first layer's weight
+// gradient is the last thing a backward pass computes, so this kernel's latency is not hidden by anything.
+__global__ void __launch_bounds__(256) conv_first_reduce_kernel(const float* __restrict__ partial, int n_parts, int n,
+                                                                float* __restrict__ dw) {
   pdl_wait();
   pdl_trigger();
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
+  __shared__ float sub[16][16];
+  const int il = threadIdx.x & 15, q = threadIdx.x >> 4;
+  const int i = blockIdx.x * 16 + il;
   float acc = 0.f;
-#pragma unroll 8
-  for (int s = 0; s < n_parts; ++s) acc += __ldcg(partial + (size_t)s * n + i);
-  dw[i] = acc;
+  if (i < n) {
+    for (int s0 = q; s0 < n_parts; s0 += 16 * 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int sl = s0 + 16 * u;
+        v[u] = sl < n_parts ? __ldcg(partial + (size_t)sl * n + i) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc += v[u];
+    }
+  }
+  sub[q][il] = acc;
+  __syncthreads();
+  if (q == 0 && i < n) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) t += sub[j][il];
+    dw[i] = t;
+  }
 }
 
 extern "C" int conv_first_supported(int Cin, int Cout) { return Cin == 3 && (Cout == 16 || Cout == 32 || Cout == 64); }
@@ -215,7 +237,7 @@ extern "C" int conv_first_wgrad(const void* x, const void* dy, void* dw, void* s
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   const int n = Cout * 27;
-  launch_k(conv_first_reduce_kernel, dim3((n + 127) / 128), dim3(128), 0, st, reinterpret_cast<const float*>(scratch), grid, n,
+  launch_k(conv_first_reduce_kernel, dim3((n + 15) / 16), dim3(256), 0, st, reinterpret_cast<const float*>(scratch), grid, n,
                                                            reinterpret_cast<float*>(dw));
   return (int)cudaGetLastError();
 }
