@@ -287,6 +287,9 @@ def run_ours(args, rank, world, local):
     torch.manual_seed(6)
     torch.backends.cudnn.benchmark = True
     native_nn.configure_native("auto" if args.native_layers == "on" else args.native_layers)
+    from chocosgd_b200.ops import _lib as native_lib
+
+    pdl = native_lib.configure_pdl(conf.pdl, bf16=args.model == "resnet50")   # before the library's first launch
     loader = {"n_tokens": 33278} if args.model == "lstm" else None
     model = define_model(conf, graph, data_loader=loader, device=device, verbose=False)
     if args.trajectory:
@@ -347,7 +350,8 @@ def run_ours(args, rank, world, local):
     return dev_ms, e2e_ms, clocks, launches, float(losses[-1]), step.h2d_bytes, {
         "graph": step.use_graph, "native_layers": args.native_layers,
         "gossip_kernels_per_step": optimizer.engine.launches_per_step, "native_kernels_per_step": per_step,
-        "gossip_buckets": len(optimizer.bucket_plan(step._bucket_bytes)) if step._bucket_bytes else 0}
+        "gossip_buckets": len(optimizer.bucket_plan(step._bucket_bytes)) if step._bucket_bytes else 0,
+        "programmatic_dependent_launch": bool(pdl)}
 
 
 def run_reference(args, rank, world, local):

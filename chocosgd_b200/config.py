@@ -251,6 +251,8 @@ def build_parser() -> argparse.ArgumentParser:
         "nccl = torch.distributed send/recv (baseline path, also used on CPU/gloo)",
     )
     p.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
+    p.add_argument("--pdl", default="auto", choices=("auto", "on", "off"),
+                   help="programmatic dependent launch between the library's kernels (auto: on with --dtype bf16)")
     p.add_argument("--steps", default=None, type=int, help="stop after this many local steps")
     p.add_argument("--wait_budget_ms", default=2000.0, type=float,
                    help="upper bound of every in-kernel wait on a peer flag")

@@ -41,6 +41,9 @@ def init_config(conf, rank, world):
     torch.manual_seed(conf.manual_seed)
     np.random.seed(conf.manual_seed)
     if on_cuda:
+        from .ops import _lib as native_lib
+
+        native_lib.configure_pdl(conf.pdl, bf16=conf.dtype == "bf16")
         torch.cuda.manual_seed(conf.manual_seed)
         torch.backends.cudnn.benchmark = not conf.train_fast or True
     ckpt.init_checkpoint(conf, graph, run)
