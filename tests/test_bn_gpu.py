@@ -135,3 +135,43 @@ def test_bf16_bn_act_matches_fp32_reference(shape, use_res, relu):
     torch.testing.assert_close(bn_b.running_mean, bn_a.running_mean, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(bn_b.running_var, bn_a.running_var, rtol=1e-4, atol=1e-5)
     assert int(bn_b.num_batches_tracked) == 1
+
+
+_PDL_CODE = """
+import sys, torch
+from chocosgd_b200.ops import nn as nnn
+from chocosgd_b200.ops.bn import bn_act, last_error16
+from chocosgd_b200.ops.conv import stem_last_error
+nnn.set_native(True, which=("conv", "bn", "pool"))
+torch.manual_seed(0)
+x = torch.randn(8, 3, 64, 64, device="cuda").contiguous(memory_format=torch.channels_last)
+conv = nnn.Conv2d(3, 64, kernel_size=7, stride=2, padding=3, bias=False).cuda().to(memory_format=torch.channels_last)
+bn, bn2, pool = nnn.BatchNorm2d(64).cuda(), nnn.BatchNorm2d(64).cuda(), nnn.MaxPool2d(3, 2, 1)
+with torch.autocast("cuda", dtype=torch.bfloat16):
+    y = pool(bn_act(bn, conv(x), None, True))
+    z = bn_act(bn2, y, y, True)
+z.float().square().mean().backward()
+torch.cuda.synchronize()
+assert last_error16() == 0 and stem_last_error() == 0
+out = torch.cat([z.float().flatten(), conv.weight.grad.flatten(), bn.weight.grad, bn.bias.grad, bn2.weight.grad])
+torch.save(out.cpu(), sys.argv[1])
+"""
+
+
+def test_bf16_chain_is_bitwise_the_same_with_programmatic_dependent_launch(tmp_path):
+    """Stem convolution -> batch-norm -> max pooling -> batch-norm with residual, forward and backward, with
+    the kernels launched in plain stream order and with programmatic dependencies (each kernel may become
+    resident while its predecessor drains): same bits."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    outs = []
+    for pdl in ("0", "1"):
+        path = str(tmp_path / f"pdl{pdl}.pt")
+        r = subprocess.run([sys.executable, "-c", _PDL_CODE, path], env=dict(os.environ, CHOCO_PDL=pdl), cwd=root,
+                           capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs.append(torch.load(path))
+    assert torch.isfinite(outs[0]).all() and torch.equal(outs[0], outs[1])
