@@ -64,3 +64,29 @@ def test_plain_cross_entropy_detection():
     assert not criterion_is_plain_ce(torch.nn.CrossEntropyLoss(label_smoothing=0.1))
     assert not criterion_is_plain_ce(torch.nn.CrossEntropyLoss(weight=torch.ones(3)))
     assert not criterion_is_plain_ce(torch.nn.MSELoss())
+
+
+def test_pdl_choice_follows_the_dtype_unless_the_environment_says_otherwise(monkeypatch):
+    from chocosgd_b200.config import get_args
+    from chocosgd_b200.ops import _lib
+
+    assert get_args([]).pdl == "auto"
+    for mode, bf16, want in (("auto", False, "0"), ("auto", True, "1"), ("on", False, "1"), ("off", True, "0")):
+        monkeypatch.delenv("CHOCO_PDL", raising=False)
+        assert _lib.configure_pdl(mode, bf16=bf16) == (want == "1")
+        import os
+
+        assert os.environ["CHOCO_PDL"] == want
+    monkeypatch.setenv("CHOCO_PDL", "0")
+    assert _lib.configure_pdl("on", bf16=True) is False          # an explicit environment setting wins
+
+
+def test_stem_and_bf16_kernels_are_not_chosen_on_cpu():
+    from chocosgd_b200.ops import nn as nnn
+    from chocosgd_b200.ops.conv import stem_conv_supported
+
+    conv = nnn.Conv2d(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
+    x = torch.randn(2, 3, 32, 32)
+    assert not stem_conv_supported(conv, x)
+    y = conv(x)                                                    # library path
+    assert y.shape == (2, 64, 16, 16)
