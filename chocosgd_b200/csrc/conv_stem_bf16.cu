@@ -170,6 +170,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem7_fwd_kernel(StemArgs a) {
     int ok = 1;
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x, ++lt) {
       const uint32_t buf = lt & 1;
+      // the loads do not depend on the slot: they are issued before the wait for it, so their latency runs
+      // under the tensor core's and the epilogue's work on the two tiles before
+      const StemPix s = stem_pixel(a, (long long)tile * 128 + row);
+      float2 v[2][12];
+      stem_load_row(a, s, 2 * quarter, v[0]);
+      if (quarter < 3) stem_load_row(a, s, 2 * quarter + 1, v[1]);
       if (lane == 0) {
         if (lt >= 2 && !mbar_wait(empty + buf, ((lt >> 1) - 1) & 1)) ok = 0;
         if (*abort_flag) ok = 0;
@@ -178,10 +184,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem7_fwd_kernel(StemArgs a) {
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       uint8_t* A = sA + buf * L::A_BYTES;
-      const StemPix s = stem_pixel(a, (long long)tile * 128 + row);
-      float2 v[2][12];
-      stem_load_row(a, s, 2 * quarter, v[0]);
-      if (quarter < 3) stem_load_row(a, s, 2 * quarter + 1, v[1]);
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         if (u == 1 && quarter == 3) break;
@@ -351,6 +353,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem7_wgrad_kernel(StemArgs a) 
     int ok = 1;
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x, ++lt) {
       const uint32_t buf = lt & 1;
+      const long long p = (long long)tile * 128 + col;
+      const StemPix s = stem_pixel(a, p);
+      // every global load of the tile is issued before the wait for the slot and before the first store
+      uint4 d[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        d[j] = s.valid ? __ldg(reinterpret_cast<const uint4*>(a.dy + p * ST_COUT + quarter * 16 + j * 8)) : make_uint4(0, 0, 0, 0);
+      float2 v[2][12];
+      stem_load_row(a, s, 2 * quarter, v[0]);
+      if (quarter < 3) stem_load_row(a, s, 2 * quarter + 1, v[1]);
       if (lane == 0) {
         if (lt >= 2 && !mbar_wait(empty + buf, ((lt >> 1) - 1) & 1)) ok = 0;
         if (*abort_flag) ok = 0;
@@ -360,16 +372,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem7_wgrad_kernel(StemArgs a) 
       if (!ok) break;
       uint8_t* A = sA + buf * L::WA_BYTES + col_slab * L::WA_SLAB + col_byte;
       uint8_t* B = sB + buf * L::WB_BYTES + col_slab * L::WB_SLAB + col_byte;
-      const long long p = (long long)tile * 128 + col;
-      const StemPix s = stem_pixel(a, p);
-      // every global load of the tile is issued before the first store
-      uint4 d[2];
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-        d[j] = s.valid ? __ldg(reinterpret_cast<const uint4*>(a.dy + p * ST_COUT + quarter * 16 + j * 8)) : make_uint4(0, 0, 0, 0);
-      float2 v[2][12];
-      stem_load_row(a, s, 2 * quarter, v[0]);
-      if (quarter < 3) stem_load_row(a, s, 2 * quarter + 1, v[1]);
       // dy^T: rows co = 16 q .. 16 q + 15
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
