@@ -45,7 +45,10 @@ def init_config(conf, rank, world):
 
         native_lib.configure_pdl(conf.pdl, bf16=conf.dtype == "bf16")
         torch.cuda.manual_seed(conf.manual_seed)
-        torch.backends.cudnn.benchmark = not conf.train_fast or True
+        # the library convolutions that remain pick their algorithm by measurement, with or without
+        # --train_fast (the reference ties cudnn.deterministic to that flag, dl_code/main.py:177-179; the
+        # native kernels are reproducible either way)
+        torch.backends.cudnn.benchmark = True
     ckpt.init_checkpoint(conf, graph, run)
     run.logger = Logger(run.checkpoint_dir)
     display_args(conf, graph)
