@@ -141,7 +141,9 @@ def main(argv=None):
         ms_lib = timed(lib, a.iters)
         nbytes = x.numel() * 2
         out.update(batch=a.batch, hw=a.hw, channels=c, ms=ms, ms_library=ms_lib, tensor_MB=nbytes / 1e6,
-                   io_GBps=(1 + 2 + 3 + 4) * nbytes / ms / 1e6)   # reduce 1, apply 2, backward reduce 3, backward apply 4
+                   # tensors moved: reduce 1, apply 2, backward reduce 2, backward apply 3 (ReLU without a
+                   # residual: the backward recomputes the mask from x and never reads y)
+                   io_GBps=(1 + 2 + 2 + 3) * nbytes / ms / 1e6)
     elif a.case == "wgrad_gen":
         from ..ops.conv import conv_wgrad_gen, last_error
 
