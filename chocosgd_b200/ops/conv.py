@@ -646,9 +646,10 @@ class _ConvFirstFn(torch.autograd.Function):
             _lib.count(2)
             return dw
 
-        fork = _WGRAD_STREAM.enabled and weight.grad is None and not torch.is_grad_enabled()
-        dw = _WGRAD_STREAM.run(fn, (x, dy), x.device) if fork else fn()
-        return None, dw, None
+        # not forked to the weight-gradient stream: this is the last gradient of a backward pass, nothing is
+        # left on the main stream for it to overlap with, and there it runs beside whatever the second stream
+        # still has queued instead of behind it
+        return None, fn(), None
 
 
 def _declare_stem():
