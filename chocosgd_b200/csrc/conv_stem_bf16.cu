@@ -12,7 +12,8 @@
 //   forward   D[pixel, co] = A[pixel, k] B[co, k]: M = 128 output pixels per tile, N = 64.  Persistent CTAs;
 //             sixteen producer warps build tile t+1 while the tensor core works on tile t and four epilogue
 //             warps write tile t-1 (TMEM -> bf16 -> shared staging -> one contiguous 16 KB block of y).
-//             Optional per-CTA (sum, sum of squares) rows for the batch-norm that follows.
+//             Optional per-CTA (sum, sum of squares) rows for the batch-norm that follows (the bf16
+//             batch-norm does not take them yet: the Python side passes no buffer).
 //   wgrad     D[co, k] = dy^T[co, pixel] P^T[k, pixel]: the pixel is the contraction index, so producers
 //             write both operands TRANSPOSED (2-byte stores, consecutive lanes = consecutive pixels of one
 //             row: conflict-free).  M = 128 (rows 64..127 stay zero), N = 176, one accumulator per CTA over
